@@ -1,0 +1,91 @@
+// Shared helpers of every kernel file: element types, error reporting, launch checks.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and
+// a stream, and returns 0 or an LLMB_ERR_* code; the text of the last error of
+// the calling thread is read with <file prefix>_last_error(). Kernels read
+// positions, lengths and page tables from device arrays, never from launch
+// arguments, so that a captured step replays on new values (the device-side
+// [position, visible] words of MythEclipse/llm, apps/engine/src/cuda/mod.rs:184-195,
+// generalised to arrays).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+#define LLMB_OK 0
+#define LLMB_ERR_ARGUMENT 1    // a size or option this kernel refuses
+#define LLMB_ERR_CUDA 2        // a CUDA call failed
+#define LLMB_ERR_TIMEOUT 3     // a bounded device-side wait ran out
+
+#define LLMB_DTYPE_F32 0
+#define LLMB_DTYPE_BF16 1
+
+#define LLMB_PAGE 64           // positions per cache page
+
+namespace llmb {
+
+inline char* error_buffer() {
+    static thread_local char buffer[512] = {0};
+    return buffer;
+}
+
+template <typename... Args>
+inline int fail(int code, const char* format, Args... args) {
+    snprintf(error_buffer(), 512, format, args...);
+    return code;
+}
+inline int fail(int code, const char* text) {
+    snprintf(error_buffer(), 512, "%s", text);
+    return code;
+}
+
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(LLMB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return LLMB_OK;
+}
+
+#define LLMB_REQUIRE(cond, ...)                                              \
+    do {                                                                     \
+        if (!(cond)) return llmb::fail(LLMB_ERR_ARGUMENT, __VA_ARGS__);      \
+    } while (0)
+
+#define LLMB_CUDA(call)                                                      \
+    do {                                                                     \
+        cudaError_t e_ = (call);                                             \
+        if (e_ != cudaSuccess)                                               \
+            return llmb::fail(LLMB_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+    return v;
+}
+
+inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+}  // namespace llmb
+
+#define LLMB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Each .cu file is built into a library of its own and defines its own reader
+// of the calling thread's last error text.
+#define LLMB_DEFINE_LAST_ERROR(prefix) \
+    LLMB_EXPORT const char* prefix##_last_error() { return llmb::error_buffer(); }

@@ -1,0 +1,196 @@
+// Row-wise kernels of the decoder: embedding gather, RMSNorm, rotary encoding
+// fused with the write of keys and values into the paged cache, and the gated
+// activation. Every kernel exists for 32-bit and for bfloat16 activations;
+// sums, angles and the residual stream are 32-bit in both.
+#include "common.cuh"
+
+using namespace llmb;
+
+LLMB_DEFINE_LAST_ERROR(llmb_elementwise)
+
+// ----------------------------------------------------------------------------- embedding
+// x[t, :] = table[token[t], :], widened to 32-bit (the residual stream).
+// Formula: apps/engine/kernels/gpu.cu:1752-1766 of MythEclipse/llm (one thread per
+// (token, column)); here one block per token, columns strided over the threads.
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                             float* __restrict__ x, int hidden, int vocab) {
+    int t = blockIdx.x;
+    int token = tokens[t];
+    if (token < 0 || token >= vocab) token = 0;   // host checks ids; device-sampled ids are in range
+    const T* row = table + (size_t)token * hidden;
+    float* out = x + (size_t)t * hidden;
+    for (int e = threadIdx.x; e < hidden; e += blockDim.x) out[e] = to_float(row[e]);
+}
+
+LLMB_EXPORT int llmb_embed(const int* tokens, const void* table, int table_dtype, float* x,
+                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+    if (n_tokens == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
+    if (table_dtype == LLMB_DTYPE_F32)
+        embed_kernel<float><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, x, hidden, vocab);
+    else if (table_dtype == LLMB_DTYPE_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, hidden, vocab);
+    else
+        return fail(LLMB_ERR_ARGUMENT, "embed: unknown dtype %d", table_dtype);
+    return check_launch("embed");
+}
+
+// ----------------------------------------------------------------------------- RMSNorm
+// out[r, :] = x[row(r), :] * (1 / sqrt(mean(x^2) + eps)) * gain, eps inside the root
+// (apps/engine/src/ops.rs:4-12, apps/engine/kernels/gpu.cu:266-316). One block per
+// row; the sum of squares is 32-bit and is reduced in a fixed order, so a row's
+// result does not depend on the batch it is in. `rows` (optional) gathers rows.
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                               const int* __restrict__ rows, TOut* __restrict__ out,
+                               int hidden, float eps) {
+    int r = blockIdx.x;
+    int src = rows ? rows[r] : r;
+    const float* in = x + (size_t)src * hidden;
+    float sum = 0.f;
+    for (int e = threadIdx.x; e < hidden; e += blockDim.x) {
+        float v = in[e];
+        sum = fmaf(v, v, sum);
+    }
+    __shared__ float partial[32];
+    __shared__ float scale_shared;
+    sum = warp_sum(sum);
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) partial[warp] = sum;
+    __syncthreads();
+    if (warp == 0) {
+        int n_warps = blockDim.x >> 5;
+        float v = lane < n_warps ? partial[lane] : 0.f;
+        v = warp_sum(v);
+        if (lane == 0) scale_shared = 1.0f / sqrtf(v / (float)hidden + eps);
+    }
+    __syncthreads();
+    float scale = scale_shared;
+    TOut* o = out + (size_t)r * hidden;
+    for (int e = threadIdx.x; e < hidden; e += blockDim.x)
+        o[e] = from_float<TOut>(in[e] * scale * gain[e]);
+}
+
+LLMB_EXPORT int llmb_rmsnorm(const float* x, const float* gain, const int* rows, void* out,
+                             int out_dtype, int n_rows, int hidden, float eps,
+                             cudaStream_t stream) {
+    if (n_rows == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_rows > 0 && hidden > 0, "rmsnorm: bad sizes");
+    if (out_dtype == LLMB_DTYPE_F32)
+        rmsnorm_kernel<float><<<n_rows, 256, 0, stream>>>(x, gain, rows, (float*)out, hidden, eps);
+    else if (out_dtype == LLMB_DTYPE_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>(x, gain, rows, (__nv_bfloat16*)out, hidden, eps);
+    else
+        return fail(LLMB_ERR_ARGUMENT, "rmsnorm: unknown dtype %d", out_dtype);
+    return check_launch("rmsnorm");
+}
+
+// ----------------------------------------------------------------------------- rotary + cache write
+// One launch per layer: rotate the queries in place, rotate the keys and store
+// them into the paged cache, copy the values into the cache (the job of
+// rope_append, apps/engine/kernels/gpu.cu:525-581). Angles come from a 32-bit
+// table [max_positions, head_dim] (cos in the first half of a row, sin in the
+// second) built once on the host; `interleaved` chooses the pairs (2p, 2p+1) of
+// MythEclipse/llm (apps/engine/src/ops.rs:152-165), otherwise (p, p + D/2).
+// With table == nullptr nothing is rotated (a mixer without position encoding).
+// A token's position and sequence come from device arrays; position p of
+// sequence b lives in page block_table[b][(p / 64) % ring_pages], row p % 64.
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__ table,
+                                  const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                  const int* __restrict__ block_table, int table_stride,
+                                  int ring_pages, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                  int n_heads, int n_kv_heads, int head_dim, int interleaved,
+                                  int write_cache) {
+    int t = blockIdx.x;
+    int head = blockIdx.y;               // [0, Hq): q; [Hq, Hq+Hkv): k; then v
+    int pos = tok_pos[t];
+    int half = head_dim >> 1;
+    size_t row_stride = (size_t)(n_heads + 2 * n_kv_heads) * head_dim;
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * head_dim;
+    bool is_q = head < n_heads;
+    bool is_k = !is_q && head < n_heads + n_kv_heads;
+    T* dst = nullptr;
+    if (!is_q) {
+        if (!write_cache) return;
+        int kv_head = is_k ? head - n_heads : head - n_heads - n_kv_heads;
+        int b = tok_seq[t];
+        int page = block_table[(size_t)b * table_stride + ((pos / LLMB_PAGE) % ring_pages)];
+        size_t offset = (((size_t)page * n_kv_heads + kv_head) * LLMB_PAGE + (pos % LLMB_PAGE)) * head_dim;
+        dst = (is_k ? k_cache : v_cache) + offset;
+    }
+    if (is_q || is_k) {
+        const float* angles = table ? table + (size_t)pos * head_dim : nullptr;
+        T* out = is_q ? src : dst;
+        for (int p = threadIdx.x; p < half; p += blockDim.x) {
+            int i0 = interleaved ? 2 * p : p;
+            int i1 = interleaved ? 2 * p + 1 : p + half;
+            float low = to_float(src[i0]), high = to_float(src[i1]);
+            float c = angles ? angles[p] : 1.f, s = angles ? angles[half + p] : 0.f;
+            out[i0] = from_float<T>(low * c - high * s);
+            out[i1] = from_float<T>(low * s + high * c);
+        }
+    } else {
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
+    }
+}
+
+LLMB_EXPORT int llmb_rope_cache_write(void* qkv, int dtype, const float* table,
+                                      const int* tok_pos, const int* tok_seq,
+                                      const int* block_table, int table_stride, int ring_pages,
+                                      void* k_cache, void* v_cache, int n_tokens, int n_heads,
+                                      int n_kv_heads, int head_dim, int interleaved,
+                                      int write_cache, cudaStream_t stream) {
+    if (n_tokens == 0) return LLMB_OK;
+    LLMB_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "rope: head_dim %d must be even", head_dim);
+    LLMB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && ring_pages > 0, "rope: bad sizes");
+    LLMB_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope: too many heads");
+    dim3 grid(n_tokens, n_heads + 2 * n_kv_heads);
+    int threads = head_dim / 2 >= 64 ? 64 : 32;
+    if (dtype == LLMB_DTYPE_F32)
+        rope_cache_kernel<float><<<grid, threads, 0, stream>>>(
+            (float*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
+            (float*)k_cache, (float*)v_cache, n_heads, n_kv_heads, head_dim, interleaved, write_cache);
+    else if (dtype == LLMB_DTYPE_BF16)
+        rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+            (__nv_bfloat16*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim,
+            interleaved, write_cache);
+    else
+        return fail(LLMB_ERR_ARGUMENT, "rope: unknown dtype %d", dtype);
+    return check_launch("rope_cache_write");
+}
+
+// ----------------------------------------------------------------------------- gated activation
+// act[t, f] = silu(gu[t, f]) * gu[t, F + f], silu(z) = z / (1 + exp(-z))
+// (apps/engine/kernels/gpu.cu:409-418, apps/engine/src/ops.rs:33-35). The gate
+// and up projections are one matrix product whose row holds [gate | up].
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, long long total,
+                              int width) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        long long t = i / width;
+        int f = (int)(i - t * width);
+        float g = to_float(gu[t * 2 * width + f]);
+        float u = to_float(gu[t * 2 * width + width + f]);
+        act[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+LLMB_EXPORT int llmb_swiglu(const void* gu, void* act, int dtype, int n_tokens, int width,
+                            cudaStream_t stream) {
+    if (n_tokens == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_tokens > 0 && width > 0, "swiglu: bad sizes");
+    long long total = (long long)n_tokens * width;
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == LLMB_DTYPE_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)act, total, width);
+    else if (dtype == LLMB_DTYPE_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act, total, width);
+    else
+        return fail(LLMB_ERR_ARGUMENT, "swiglu: unknown dtype %d", dtype);
+    return check_launch("swiglu");
+}

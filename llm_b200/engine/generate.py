@@ -1,0 +1,162 @@
+"""The generation loop over batches of requests.
+
+Per sequence the order is that of MythEclipse/llm's loop
+(apps/engine/src/generate.rs:78-127): prefill; then sample from the current
+logits; a stop token ends the sequence without being emitted or fed; else emit,
+stop if the context is full, and feed the token for the next logits. Here a
+batch of requests with unequal prompts starts together (one prefill step),
+every live sequence then advances by one token per step, sequences that end
+leave the batch (their slot goes back to the cache) and the rest go on; when
+the batch is empty the next batch starts. Stop reasons and the timing fields
+are those of generate.rs:20-49,129-160.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+from ..errors import ContextFull, FormatError
+from ..sampling import BatchSampler, SamplingParams
+from .step import Entry
+
+
+@dataclass
+class GenerationRequest:
+    prompt: list
+    max_tokens: int = 256
+    params: SamplingParams = field(default_factory=SamplingParams)
+    stop_tokens: tuple = ()
+
+
+@dataclass
+class GenerationResult:
+    tokens: list
+    stop_reason: str                 # 'eos', 'max_tokens', 'cancelled', 'context_full'
+    prompt_tokens: int
+    generated_tokens: int = 0
+    prefill_ms: float = 0.0
+    ttft_ms: float = 0.0
+    decode_ms: float = 0.0
+    total_ms: float = 0.0
+    tokens_per_second: float = 0.0
+
+
+def plan_batches(requests, fits, max_batch: int) -> list:
+    """Cut the requests, in their order, into batches: a batch takes requests
+    while it has fewer than `max_batch` and `fits(list of final lengths)` says
+    the cache can hold them all to their end. A request that does not fit even
+    alone is an error."""
+    batches, current, lengths = [], [], []
+    for index, final_length in requests:
+        if current and (len(current) >= max_batch or not fits(lengths + [final_length])):
+            batches.append(current)
+            current, lengths = [], []
+        if not fits([final_length]):
+            raise ContextFull(final_length, 0)
+        current.append(index)
+        lengths.append(final_length)
+    if current:
+        batches.append(current)
+    return batches
+
+
+def generate(engine, requests, max_batch: int | None = None, on_token=None, cancel=None) -> list:
+    """Run every request to its end and return one GenerationResult each, in
+    the order of the requests. `on_token(request index, token)` is called for
+    every emitted token; `cancel()` returning True ends all live sequences with
+    reason 'cancelled'."""
+    requests = list(requests)
+    context = engine.max_seq_len
+    for i, r in enumerate(requests):
+        if len(r.prompt) == 0:
+            raise FormatError(f"request {i} has an empty prompt")
+        if len(r.prompt) > context:
+            raise ContextFull(len(r.prompt), context)
+        r.params.check(engine.vocab)
+    results = [None] * len(requests)
+    final = [(i, min(len(r.prompt) + max(r.max_tokens, 0), context)) for i, r in enumerate(requests)]
+    batches = plan_batches(final, engine.cache.can_hold, max_batch or engine.max_slots)
+    for batch in batches:
+        _run_batch(engine, requests, batch, results, on_token, cancel)
+    return results
+
+
+def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
+    started = time.perf_counter()
+    slots = engine.acquire(len(batch))
+    live = list(range(len(batch)))                      # indices into `batch`
+    reqs = [requests[i] for i in batch]
+    emitted = [[] for _ in batch]
+    reason = ["max_tokens"] * len(batch)
+    first_token_at = [None] * len(batch)
+    sampler = BatchSampler([r.params for r in reqs], engine.vocab, engine.device)
+    released = set()
+
+    def finish(b, why):
+        reason[b] = why
+        if b not in released:
+            engine.release([slots[b]])
+            released.add(b)
+
+    try:
+        logits = engine.step([Entry(slots[b], reqs[b].prompt, [len(reqs[b].prompt) - 1])
+                              for b in live])
+        prefill_done = None
+        while live:
+            if cancel is not None and cancel():
+                for b in live:
+                    finish(b, "cancelled")
+                break
+            # sequences that may not emit anything leave before sampling
+            keep = [b for b in live if len(emitted[b]) < reqs[b].max_tokens]
+            if len(keep) != len(live):
+                rows = [k for k, b in enumerate(live) if b in set(keep)]
+                for b in live:
+                    if b not in keep:
+                        finish(b, "max_tokens")
+                logits = logits[rows] if keep else logits[:0]
+                live = keep
+                if not live:
+                    break
+            tokens = sampler.sample(logits, live).tolist()      # one small device-to-host copy
+            now = time.perf_counter()
+            if prefill_done is None:
+                prefill_done = now
+            going, feed = [], []
+            for b, token in zip(live, tokens):
+                if token in reqs[b].stop_tokens:
+                    finish(b, "eos")
+                    continue
+                emitted[b].append(token)
+                if first_token_at[b] is None:
+                    first_token_at[b] = now
+                if on_token is not None:
+                    on_token(batch[b], token)
+                if engine.length(slots[b]) >= engine.max_seq_len:
+                    finish(b, "context_full")
+                elif len(emitted[b]) >= reqs[b].max_tokens:
+                    finish(b, "max_tokens")
+                else:
+                    going.append(b)
+                    feed.append(token)
+            live = going
+            if live:
+                logits = engine.step([Entry(slots[b], [t], [0]) for b, t in zip(live, feed)])
+        sampler.check_status()
+    finally:
+        for b in range(len(batch)):
+            if b not in released:
+                engine.release([slots[b]])
+                released.add(b)
+    ended = time.perf_counter()
+    for b, index in enumerate(batch):
+        n = len(emitted[b])
+        first = first_token_at[b] if first_token_at[b] is not None else ended
+        total_ms = (ended - started) * 1e3
+        ttft_ms = (first - started) * 1e3
+        decode_ms = max(total_ms - ttft_ms, 0.0)
+        results[index] = GenerationResult(
+            tokens=emitted[b], stop_reason=reason[b], prompt_tokens=len(reqs[b].prompt),
+            generated_tokens=n, prefill_ms=((prefill_done or ended) - started) * 1e3,
+            ttft_ms=ttft_ms, decode_ms=decode_ms, total_ms=total_ms,
+            tokens_per_second=((n - 1) * 1e3 / decode_ms) if n > 1 and decode_ms > 0 else 0.0)

@@ -1,0 +1,153 @@
+"""The decoder as a list of blocks run in the order of a schedule."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..errors import FormatError
+from ..parts import build_block, build_norm
+from ..parts.base import to_run_dtype
+from ..weights.loader import ParamSpec, load_checkpoint
+
+
+class DecoderModel:
+    """Embedding, blocks in schedule order, final norm and head, built from a
+    ModelSpec. The layer loop and the head on the wanted rows only follow the
+    forward pass of MythEclipse/llm (apps/engine/src/model.rs:755-825); which
+    parts a layer has and in which order layers run is data of the spec."""
+
+    def __init__(self, spec):
+        self.spec = spec
+        self.blocks = [build_block(b) for b in spec.blocks]
+        self.final_norm = build_norm(spec.final_norm)
+        for i, item in enumerate(spec.schedule):
+            if not 0 <= item.layer < len(self.blocks):
+                raise FormatError(f"schedule entry {i} names layer {item.layer} of {len(self.blocks)}")
+            if item.cache_of is not None and not (
+                    0 <= item.cache_of < i and spec.schedule[item.cache_of].cache_of is None):
+                raise FormatError(f"schedule entry {i} reads the cache of entry {item.cache_of}, "
+                                  "which is not an earlier entry with a cache of its own")
+        self.embedding = None
+        self.head = None
+        self.dtype = None
+        self.device = None
+
+    # ------------------------------------------------------------------ weights
+
+    def parameters(self) -> dict:
+        out = {self.spec.embedding: ParamSpec((self.spec.vocab, self.spec.hidden))}
+        for block in self.blocks:
+            out.update(block.parameters())
+        out.update(self.final_norm.parameters())
+        if self.spec.head is not None:
+            out[self.spec.head] = ParamSpec((self.spec.vocab, self.spec.hidden))
+        return out
+
+    def libraries(self) -> list:
+        names = ["elementwise", "gemm_simt"]
+        for block in self.blocks:
+            names += list(block.libraries)
+        names += list(self.final_norm.libraries)
+        return list(dict.fromkeys(names))
+
+    def bind(self, tensors: dict, dtype, device) -> "DecoderModel":
+        """Move the tensors to the device in the run's dtype; parts may fuse
+        them. `tensors` may hold CPU or device tensors; entries are dropped as
+        they are consumed so that a large model is not held twice."""
+        self.dtype, self.device = dtype, torch.device(device)
+        self.embedding = to_run_dtype(tensors[self.spec.embedding], dtype, device)
+        self.head = (self.embedding if self.spec.head is None
+                     else to_run_dtype(tensors[self.spec.head], dtype, device))
+        for block in self.blocks:
+            block.bind(tensors, dtype, device)
+            for name in block.parameters():
+                tensors.pop(name, None)
+        self.final_norm.bind(tensors, dtype, device)
+        return self
+
+    def prepare(self, max_positions: int) -> None:
+        for block in self.blocks:
+            block.prepare(max_positions, self.device)
+
+    def weight_bytes(self) -> int:
+        """Bytes of every matrix a decode step reads once (the embedding table
+        is read row by row and counted only as the head when tied)."""
+        seen, total = set(), 0
+        def add(t):
+            nonlocal total
+            if t is not None and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        add(self.head)
+        for item in self.spec.schedule:
+            block = self.blocks[item.layer]
+            for part in block.parts:
+                for value in part.weights():
+                    add(value)
+        return total
+
+    # ------------------------------------------------------------------ cache needs
+
+    def cache_requests(self):
+        """Per schedule entry: the KvRequest of runs that own keys and values
+        (None for runs that read another entry's), and the StateRequest."""
+        kv, states = [], []
+        for item in self.spec.schedule:
+            mixer = self.blocks[item.layer].mixer
+            kv.append(mixer.kv_request() if item.cache_of is None else None)
+            states.append(mixer.state_request())
+        return kv, states
+
+    # ------------------------------------------------------------------ forward
+
+    def forward(self, tokens, ctx, logit_rows):
+        """tokens int32 [T] on the device; logit_rows int32 [R]: packed token
+        indices whose logits are wanted. Returns float32 [R, vocab]."""
+        x = ops.embed(tokens, self.embedding)
+        for entry, item in enumerate(self.spec.schedule):
+            cache_entry = entry if item.cache_of is None else item.cache_of
+            self.blocks[item.layer].forward(x, ctx, entry, cache_entry)
+        if logit_rows.numel() == 0:
+            return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=x.device)
+        z = self.final_norm.forward(x, ctx.dtype, rows=logit_rows)
+        return ops.linear(z, self.head, out_dtype=torch.float32)
+
+
+def declared_parameters(spec) -> dict:
+    """Every tensor name a model of this spec binds, with shape and role."""
+    return DecoderModel(spec).parameters()
+
+
+def load_model(folder, dtype=torch.bfloat16, device="cuda:0") -> DecoderModel:
+    """Read `folder`/config.json, pick the configuration class by its
+    architecture name, check the checkpoint's tensors against what the model
+    declares (one error for everything that is wrong) and bind them."""
+    from ..config import load_config
+    config = load_config(folder)
+    model = DecoderModel(config.model_spec())
+    model.config = config
+    tensors = load_checkpoint(folder, model.parameters())
+    return model.bind(tensors, dtype, device)
+
+
+def random_model(config, seed: int, dtype=torch.bfloat16, device="cuda:0", std: float = 0.02,
+                 gain_noise: float = 0.02) -> DecoderModel:
+    """A model with random weights made on `device`, without a model folder."""
+    from ..weights.random_init import random_tensors
+    model = DecoderModel(config.model_spec())
+    model.config = config
+    model.dtype, model.device = dtype, torch.device(device)
+    expected = model.parameters()
+    # layer by layer, so that a large model is never held twice
+    def make(names):
+        return random_tensors({n: expected[n] for n in names}, seed, torch.bfloat16, std,
+                              gain_noise, device)
+    top = [model.spec.embedding] + ([model.spec.head] if model.spec.head else [])
+    tensors = make(top)
+    model.embedding = to_run_dtype(tensors[model.spec.embedding], dtype, device)
+    model.head = (model.embedding if model.spec.head is None
+                  else to_run_dtype(tensors[model.spec.head], dtype, device))
+    for block in model.blocks:
+        block.bind(make(list(block.parameters())), dtype, device)
+    model.final_norm.bind(make(list(model.final_norm.parameters())), dtype, device)
+    return model

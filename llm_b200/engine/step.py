@@ -1,0 +1,179 @@
+"""The step function: a batch of sequences, the tokens each brings, logits out.
+
+MythEclipse/llm has two entry points for one sequence, `forward` for a chunk
+and `forward_decode` for one token, over a shared body
+(apps/engine/src/model.rs:652-730, 755-825). Here one `Engine.step` serves a
+batch: every sequence brings its next tokens (all of its prompt in the first
+step, one token in each later step), tokens are packed without padding,
+positions come from each sequence's own length, and logits are returned for
+the places the caller asks for. A step runs only the tokens it is given, on
+top of what earlier steps left in the cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..cache import PAGE, PagedCache, round_up
+from ..errors import ContextFull, FormatError, LlmError
+from ..parts.base import StepContext
+
+
+@dataclass
+class Entry:
+    """One sequence's share of a step."""
+    slot: int
+    tokens: list                 # its next tokens (at least one)
+    want: list                   # indices into `tokens` whose logits are wanted
+
+
+class Engine:
+    """A bound model, its cache and the step function.
+
+    max_tokens: tokens that all live sequences hold together, each rounded up
+        to a multiple of 64 (sizes the page pools).
+    max_seq_len: longest single sequence (default: the model's limit, capped
+        by max_tokens).
+    max_slots: most sequences alive at once (default: max_tokens / 64).
+    step_tokens: most new tokens of one sequence in one pass over the layers;
+        longer prompts are cut into passes (each attends to everything cached
+        before it, as the chunks of apps/engine/src/session.rs:109-130 do).
+    """
+
+    def __init__(self, model, max_tokens: int, max_seq_len: int | None = None,
+                 max_slots: int | None = None, step_tokens: int | None = None):
+        if model.embedding is None:
+            raise LlmError("the model has no weights bound")
+        self.model = model
+        self.dtype = model.dtype
+        self.device = model.device
+        max_tokens = round_up(max(int(max_tokens), PAGE))
+        limit = model.spec.max_positions
+        self.max_seq_len = min(max_seq_len or limit, limit, max_tokens)
+        self.max_slots = max_slots or max(1, max_tokens // PAGE)
+        self.step_tokens = step_tokens or self.max_seq_len
+        ops.ensure_built(model.libraries())
+        model.prepare(self.max_seq_len)
+        kv, states = model.cache_requests()
+        self.cache = PagedCache(kv, states, max_tokens, self.max_seq_len, self.max_slots,
+                                self.dtype, self.device, self.step_tokens)
+        self.vocab = model.spec.vocab
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ sequences
+
+    def acquire(self, count: int = 1) -> list:
+        return [self.cache.acquire() for _ in range(count)]
+
+    def release(self, slots) -> None:
+        for slot in slots:
+            self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ------------------------------------------------------------------ the step
+
+    def step(self, entries) -> torch.Tensor:
+        """Run the new tokens of every entry as one batch and return float32
+        logits [wanted, vocab] on the device, in the order of the entries and of
+        each entry's `want`. Everything is checked before anything is launched
+        or changed: empty token lists, ids outside the vocabulary, wanted places
+        outside the tokens, sequences that would outgrow the context, pages that
+        are not there."""
+        entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        if not entries:
+            return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if e.slot in seen:
+                raise FormatError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if len(e.tokens) == 0:
+                raise FormatError(f"slot {e.slot} brings no token")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab:
+                    raise FormatError(f"token id {t} is outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise FormatError(f"wanted place {w} is outside the {len(e.tokens)} tokens "
+                                      f"of slot {e.slot}")
+            new_length = self.cache.length(e.slot) + len(e.tokens)
+            if new_length > self.max_seq_len:
+                raise ContextFull(new_length, self.max_seq_len)
+        # pages for the whole step, all or nothing
+        self.cache.reserve_many([(e.slot, self.cache.length(e.slot) + len(e.tokens))
+                                 for e in entries])
+        longest = max(len(e.tokens) for e in entries)
+        if longest <= self.step_tokens:
+            return self._pass(entries)
+        # cut long prompts into passes; keep the caller's order of wanted rows
+        pieces, order = [], []
+        for start in range(0, longest, self.step_tokens):
+            part, keys = [], []
+            for i, e in enumerate(entries):
+                chunk = e.tokens[start:start + self.step_tokens]
+                if not chunk:
+                    continue
+                want = [(j, w - start) for j, w in enumerate(e.want) if start <= w < start + len(chunk)]
+                part.append(Entry(e.slot, chunk, [w for _, w in want]))
+                keys += [(i, j) for j, _ in want]
+            pieces.append(self._pass(part))
+            order += keys
+        logits = torch.cat(pieces)
+        wanted = sorted(range(len(order)), key=lambda r: order[r])
+        return logits[torch.tensor(wanted, dtype=torch.long, device=self.device)]
+
+    def _pass(self, entries) -> torch.Tensor:
+        cache = self.cache
+        tokens, tok_pos, tok_seq, cu, seq_lens, rows, starts, counts = [], [], [], [0], [], [], [], []
+        for b, e in enumerate(entries):
+            start = cache.length(e.slot)
+            n = len(e.tokens)
+            base = len(tokens)
+            tokens += [int(t) for t in e.tokens]
+            tok_pos += range(start, start + n)
+            tok_seq += [b] * n
+            cu.append(base + n)
+            seq_lens.append(start + n)
+            rows += [base + int(w) for w in e.want]
+            starts.append(start)
+            counts.append(n)
+        slots = [e.slot for e in entries]
+        tables = [cache.block_table_rows(g, slots) for g in range(len(cache.groups))]
+        ctx, tokens_dev, rows_dev = self._upload(tokens, tok_pos, tok_seq, cu, seq_lens, slots,
+                                                 rows, tables, starts, counts)
+        logits = self.model.forward(tokens_dev, ctx, rows_dev)
+        for e, new_length in zip(entries, seq_lens):
+            cache.set_length(e.slot, new_length)
+        self.steps_run += 1
+        return logits
+
+    def _upload(self, tokens, tok_pos, tok_seq, cu, seq_lens, slots, rows, tables, starts, counts):
+        """One host buffer, one copy: every integer array of the step."""
+        sections = [tokens, tok_pos, tok_seq, cu, seq_lens, slots, rows]
+        flat_tables = [[p for row in t for p in row] for t in tables]
+        sections += flat_tables
+        offsets, total = [], 0
+        for s in sections:
+            offsets.append(total)
+            total += (len(s) + 3) // 4 * 4          # keep every section 16-byte aligned
+        host = torch.zeros(max(total, 4), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        for s, at in zip(sections, offsets):
+            if s:
+                host[at:at + len(s)] = torch.tensor(s, dtype=torch.int32)
+        dev = host.to(self.device, non_blocking=True)
+
+        def view(i):
+            return dev[offsets[i]:offsets[i] + len(sections[i])]
+        n_seqs = len(slots)
+        block_tables = [view(7 + g).view(n_seqs, -1) for g in range(len(tables))]
+        ctx = StepContext(
+            n_tokens=len(tokens), n_seqs=n_seqs, dtype=self.dtype, device=self.device,
+            tok_pos=view(1), tok_seq=view(2), cu_seqlens=view(3), seq_lens=view(4),
+            slot_ids=view(5).long(), block_tables=block_tables, cache=self.cache,
+            decode=all(c == 1 for c in counts), new_counts=counts, starts=starts,
+            max_len=max(seq_lens))
+        return ctx, view(0), view(6)

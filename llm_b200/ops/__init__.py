@@ -1,0 +1,198 @@
+"""Python bindings of the CUDA kernels in `llm_b200/csrc`.
+
+Every function takes torch tensors that live on the GPU, checks what the
+kernel cannot check itself, picks the kernel variant for the shape
+(`tactics`) and launches on torch's current stream. There is no CPU path
+and no library fallback: a missing or failing library raises KernelError.
+
+The parts call these functions as attributes of this module
+(`ops.rmsnorm(...)`).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..errors import KernelError
+from . import tactics
+from .build import all_sources, ensure_built, load_library
+
+PAGE = 64   # positions per cache page (LLMB_PAGE in csrc/common.cuh)
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+
+def _code(dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} has no kernel (float32 and bfloat16 are built)") from None
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("llm_b200 kernels need tensors on a CUDA device; there is no CPU path")
+
+
+def _call(lib_name: str, fn_name: str, *args):
+    lib = load_library(lib_name)
+    code = getattr(lib, fn_name)(*args)
+    if code != 0:
+        reader = getattr(lib, f"llmb_{lib_name}_last_error")
+        reader.restype = ctypes.c_char_p
+        raise KernelError(f"{fn_name}: {reader().decode('utf-8', 'replace')}")
+
+
+# ----------------------------------------------------------------------------- row-wise
+
+def embed(tokens, table, out=None):
+    """x[t, :] = table[tokens[t], :] as float32 [T, hidden]."""
+    _require_cuda(tokens, table)
+    n, (vocab, hidden) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _call("elementwise", "llmb_embed", _ptr(tokens), _ptr(table), _c_int(_code(table.dtype)),
+          _ptr(out), _c_int(n), _c_int(hidden), _c_int(vocab), _stream())
+    return out
+
+
+def rmsnorm(x, gain, eps, out_dtype, rows=None, out=None):
+    """out[r, :] = x[rows[r] or r, :] / sqrt(mean(x^2) + eps) * gain; x and gain float32."""
+    _require_cuda(x, gain, rows)
+    hidden = x.shape[-1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if out is None:
+        out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+    _call("elementwise", "llmb_rmsnorm", _ptr(x), _ptr(gain), _ptr(rows), _ptr(out),
+          _c_int(_code(out_dtype)), _c_int(n), _c_int(hidden), _c_float(eps), _stream())
+    return out
+
+
+def swiglu(gate_up, out=None):
+    """act[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+    _require_cuda(gate_up)
+    n, two_f = gate_up.shape
+    width = two_f // 2
+    if out is None:
+        out = torch.empty((n, width), dtype=gate_up.dtype, device=gate_up.device)
+    _call("elementwise", "llmb_swiglu", _ptr(gate_up), _ptr(out), _c_int(_code(gate_up.dtype)),
+          _c_int(n), _c_int(width), _stream())
+    return out
+
+
+def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages, k_cache, v_cache,
+                     n_heads, n_kv_heads, head_dim, interleaved=False, write_cache=True):
+    """Rotate q (in place) and k of the fused [T, (Hq + 2 Hkv) D] projection by the
+    angles of `rope_table` [positions, D] (None: no rotation) and store k and v
+    of every token into the paged cache [pages, Hkv, 64, D]."""
+    _require_cuda(qkv, tok_pos, tok_seq, block_table, k_cache, v_cache)
+    n = qkv.shape[0]
+    _call("elementwise", "llmb_rope_cache_write", _ptr(qkv), _c_int(_code(qkv.dtype)),
+          _ptr(rope_table), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
+          _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(k_cache), _ptr(v_cache),
+          _c_int(n), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+          _c_int(1 if interleaved else 0), _c_int(1 if write_cache else 0), _stream())
+
+
+# ----------------------------------------------------------------------------- matrix product
+
+def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
+    """a [M, K] . w [N, K]^T (+ bias [N], float32). With `residual` (float32
+    [M, N]) the product is added to it in place and it is returned; otherwise a
+    new [M, N] tensor of `out_dtype` (default: a's dtype)."""
+    _require_cuda(a, w, bias, residual)
+    (m, k), (n, k2) = a.shape, w.shape
+    if k != k2 or a.dtype != w.dtype:
+        raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype} does not fit w {tuple(w.shape)} {w.dtype}")
+    if a.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError("linear: operands must be row-major")
+    if residual is not None:
+        target_dtype, result = torch.float32, residual
+        if residual.shape != (m, n) or residual.dtype != torch.float32 or not residual.is_contiguous():
+            raise KernelError("linear: residual must be contiguous float32 [M, N]")
+    else:
+        target_dtype = out_dtype or a.dtype
+        result = out if out is not None else torch.empty((m, n), dtype=target_dtype, device=a.device)
+    variant = tactics.choose_linear(m, n, k, a.dtype, target_dtype, a.stride(0))
+    if variant == "gemm_simt":
+        _call("gemm_simt", "llmb_gemm_simt", _ptr(a), _ptr(w), _ptr(bias),
+              _ptr(result if residual is None else None), _ptr(residual),
+              _c_int(_code(a.dtype)), _c_int(_code(target_dtype)), _c_int(m), _c_int(n), _c_int(k),
+              _c_int(a.stride(0)), _c_int(n), _stream())
+    else:
+        raise KernelError(f"linear: no kernel named {variant}")
+    return result
+
+
+# ----------------------------------------------------------------------------- attention
+
+def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
+              n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
+              max_len=0):
+    """Causal grouped-query attention of the new tokens' queries (the first
+    Hq * D columns of `qkv`) over the paged cache, which already holds the new
+    tokens' keys and values. Returns [T, Hq * D] in qkv's dtype."""
+    _require_cuda(qkv, k_cache, v_cache, block_table, tok_pos, tok_seq)
+    n = qkv.shape[0]
+    if out is None:
+        out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window)
+    if variant == "attention_generic":
+        _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
+              _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
+              _c_int(ring_pages), _ptr(tok_pos), _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)),
+              _c_int(_code(qkv.dtype)), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
+              _c_int(head_dim), _c_float(scale), _c_int(window), _stream())
+    else:
+        raise KernelError(f"attention: no kernel named {variant}")
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+
+def argmax_rows(logits, out=None):
+    """First maximum of every row of float32 logits [B, V] as int32 [B]."""
+    _require_cuda(logits)
+    n, vocab = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _call("sampling", "llmb_argmax_rows", _ptr(logits), _c_int(logits.stride(0)), _c_int(n),
+          _c_int(vocab), _ptr(out), _stream())
+    return out
+
+
+def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, status):
+    """The whole sampling chain for every row; see csrc/sampling.cu. `logits`
+    (float32 [B, V]) is overwritten. params float32 [B, 4], iparams int32 [B, 2],
+    recent int32 [B, cap] or None, recent_len int32 [B], rng_state int64 [B],
+    out int32 [B], status int32 [B]."""
+    _require_cuda(logits, params, iparams, recent, rng_state, out, status)
+    n, vocab = logits.shape
+    _call("sampling", "llmb_sample_rows", _ptr(logits), _c_int(logits.stride(0)), _c_int(n),
+          _c_int(vocab), _ptr(params), _ptr(iparams), _ptr(recent), _ptr(recent_len),
+          _c_int(recent.shape[1] if recent is not None else 0), _ptr(rng_state), _ptr(out),
+          _ptr(status), _stream())
+    return out
+
+
+def required_libraries() -> list:
+    """Names of the kernel files the decoder parts of this package use."""
+    return ["elementwise", "gemm_simt", "attention_generic", "sampling"]
+
+
+__all__ = ["PAGE", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
+           "argmax_rows", "sample_rows", "ensure_built", "load_library", "all_sources",
+           "required_libraries", "tactics"]

@@ -1,0 +1,150 @@
+"""Building and loading the CUDA libraries of `llm_b200/csrc`.
+
+Every `.cu` file becomes one shared library, compiled for sm_100a with nvcc
+the first time an operation from it is needed (the engine of MythEclipse/llm
+compiles its one kernel file at build time instead, apps/engine/build.rs:66-72).
+A library's file name carries a hash of its sources and flags, so a changed
+source is rebuilt and an unchanged one is loaded as it is. Libraries are kept
+in `llm_b200/csrc/_build/`; if that folder cannot be written, in a per-user
+folder under the system's temporary directory.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+from ..errors import KernelError
+
+CSRC = Path(__file__).resolve().parent.parent / "csrc"
+# no fast-math flag: expf, sqrtf and division keep their precise forms everywhere
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared"]
+
+_loaded: dict = {}
+_lock = threading.Lock()
+
+
+def _nvcc() -> str:
+    for candidate in (os.environ.get("LLMB_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if candidate and Path(candidate).is_file():
+            return candidate
+    raise KernelError("nvcc was not found (looked at $LLMB_NVCC, PATH and /usr/local/cuda/bin); "
+                      "the CUDA libraries of llm_b200 cannot be built")
+
+
+def _headers() -> list:
+    return sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+
+
+def _digest(source: Path) -> str:
+    h = hashlib.sha256()
+    for path in [source] + _headers():
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def _build_dirs() -> list:
+    dirs = []
+    if os.environ.get("LLMB_BUILD_DIR"):
+        dirs.append(Path(os.environ["LLMB_BUILD_DIR"]))
+    dirs.append(CSRC / "_build")
+    dirs.append(Path(tempfile.gettempdir()) / f"llm_b200-build-{os.getuid()}")
+    return dirs
+
+
+def _writable_dir() -> Path:
+    for d in _build_dirs():
+        try:
+            d.mkdir(parents=True, exist_ok=True)
+            probe = d / f".probe-{os.getpid()}"
+            probe.write_bytes(b"")
+            probe.unlink()
+            return d
+        except OSError:
+            continue
+    raise KernelError("no writable folder for the compiled CUDA libraries")
+
+
+def library_path(name: str) -> Path | None:
+    """The built library of csrc/<name>.cu if it exists already."""
+    file_name = f"llmb_{name}-{_digest(CSRC / (name + '.cu'))}.so"
+    for d in _build_dirs():
+        if (d / file_name).is_file():
+            return d / file_name
+    return None
+
+
+def _say(text: str) -> None:
+    print(f"[llm_b200] {text}", file=sys.stderr, flush=True)
+
+
+def compile_library(name: str) -> Path:
+    source = CSRC / (name + ".cu")
+    if not source.is_file():
+        raise KernelError(f"no kernel source {source}")
+    existing = library_path(name)
+    if existing is not None:
+        return existing
+    out_dir = _writable_dir()
+    target = out_dir / f"llmb_{name}-{_digest(source)}.so"
+    scratch = out_dir / f".{target.name}.{os.getpid()}.{threading.get_ident()}.tmp"
+    command = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(scratch), str(source), "-lcuda"]
+    started = time.time()
+    _say(f"compiling {source.name} for sm_100a ...")
+    process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                               cwd=str(out_dir))
+    while True:
+        try:
+            output, _ = process.communicate(timeout=10)
+            break
+        except subprocess.TimeoutExpired:
+            _say(f"still compiling {source.name} ({time.time() - started:.0f} s)")
+    if process.returncode != 0:
+        try:
+            scratch.unlink()
+        except OSError:
+            pass
+        raise KernelError(f"nvcc failed on {source.name}:\n{output}")
+    os.replace(scratch, target)
+    _say(f"built {target.name} in {time.time() - started:.1f} s")
+    return target
+
+
+def ensure_built(names) -> None:
+    """Compile, in parallel, every library of `names` that is not built yet."""
+    todo = [n for n in dict.fromkeys(names) if n not in _loaded and library_path(n) is None]
+    if not todo:
+        return
+    with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 2)) as pool:
+        list(pool.map(compile_library, todo))
+
+
+def load_library(name: str) -> ctypes.CDLL:
+    """The loaded library of csrc/<name>.cu, compiled first if need be. Fails
+    with KernelError (never falls back to another implementation)."""
+    with _lock:
+        lib = _loaded.get(name)
+        if lib is not None:
+            return lib
+        path = compile_library(name)
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as error:
+            raise KernelError(f"cannot load {path}: {error}") from None
+        _loaded[name] = lib
+        return lib
+
+
+def all_sources() -> list:
+    return sorted(p.stem for p in CSRC.glob("*.cu"))

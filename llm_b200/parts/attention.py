@@ -1,0 +1,78 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache import KvRequest
+from ..weights.loader import ParamSpec
+from .base import Mixer, build_position, register_mixer, to_float32, to_run_dtype
+
+
+class AttentionMixer(Mixer):
+    """q, k, v projections as one matrix product, rotation of q and k fused with
+    the cache write, attention of the new tokens over the cache, and the output
+    projection added to the residual stream in its epilogue: the dense attention
+    of MythEclipse/llm (apps/engine/src/model.rs:930-1040), with the sizes, the
+    scale, the window, the biases and the position encoding as parameters."""
+    libraries = ("elementwise", "gemm_simt", "attention_generic")
+
+    def __init__(self, spec):
+        self.spec = spec
+        self.position = build_position(spec.position)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    @property
+    def q_width(self):
+        return self.spec.n_heads * self.spec.head_dim
+
+    @property
+    def kv_width(self):
+        return self.spec.n_kv_heads * self.spec.head_dim
+
+    def parameters(self):
+        s, t = self.spec, self.spec.tensor
+        out = {t["q"]: ParamSpec((self.q_width, s.hidden)),
+               t["k"]: ParamSpec((self.kv_width, s.hidden)),
+               t["v"]: ParamSpec((self.kv_width, s.hidden)),
+               t["o"]: ParamSpec((s.hidden, self.q_width))}
+        if s.bias:
+            out[t["q_bias"]] = ParamSpec((self.q_width,), "bias")
+            out[t["k_bias"]] = ParamSpec((self.kv_width,), "bias")
+            out[t["v_bias"]] = ParamSpec((self.kv_width,), "bias")
+            out[t["o_bias"]] = ParamSpec((s.hidden,), "bias")
+        return out
+
+    def bind(self, tensors, dtype, device):
+        t = self.spec.tensor
+        self.w_qkv = torch.cat([to_run_dtype(tensors[t[r]], dtype, device) for r in ("q", "k", "v")])
+        self.w_o = to_run_dtype(tensors[t["o"]], dtype, device)
+        if self.spec.bias:
+            self.b_qkv = torch.cat([to_float32(tensors[t[r + "_bias"]], device) for r in ("q", "k", "v")])
+            self.b_o = to_float32(tensors[t["o_bias"]], device)
+
+    def prepare(self, max_positions, device):
+        if self.position is not None:
+            self.position.prepare(max_positions, device)
+
+    def kv_request(self):
+        return KvRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def forward(self, h, ctx, entry, cache_entry, residual):
+        s = self.spec
+        group, keys, values = ctx.cache.layer_view(cache_entry)
+        table = ctx.block_tables[group]
+        ring = ctx.cache.table_width(group)
+        qkv = ops.linear(h, self.w_qkv, self.b_qkv)
+        ops.rope_cache_write(
+            qkv, self.position.table if self.position is not None else None, ctx.tok_pos,
+            ctx.tok_seq, table, ring, keys, values, s.n_heads, s.n_kv_heads, s.head_dim,
+            interleaved=self.position.interleaved if self.position is not None else False,
+            write_cache=(entry == cache_entry))
+        mixed = ops.attention(qkv, keys, values, table, ring, ctx.tok_pos, ctx.tok_seq, s.n_heads,
+                              s.n_kv_heads, s.head_dim, s.scale, s.window, decode=ctx.decode,
+                              seq_lens=ctx.seq_lens, max_len=ctx.max_len)
+        ops.linear(mixed, self.w_o, self.b_o, residual=residual)
+
+
+register_mixer("attention", AttentionMixer)

@@ -1,0 +1,41 @@
+"""Dense gated feed-forward."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..errors import Unsupported
+from ..weights.loader import ParamSpec
+from .base import FeedForward, register_feed_forward, to_run_dtype
+
+
+class GatedMlp(FeedForward):
+    """down(silu(gate h) * (up h)) added to the residual stream, gate and up as
+    one matrix product (apps/engine/src/model.rs:1180-1216 of MythEclipse/llm)."""
+    libraries = ("elementwise", "gemm_simt")
+
+    def __init__(self, spec):
+        if spec.activation != "silu":
+            raise Unsupported(f"activation '{spec.activation}' in a gated feed-forward")
+        self.spec = spec
+        self.w_gate_up = self.w_down = None
+
+    def parameters(self):
+        s, t = self.spec, self.spec.tensor
+        return {t["gate"]: ParamSpec((s.intermediate, s.hidden)),
+                t["up"]: ParamSpec((s.intermediate, s.hidden)),
+                t["down"]: ParamSpec((s.hidden, s.intermediate))}
+
+    def bind(self, tensors, dtype, device):
+        t = self.spec.tensor
+        self.w_gate_up = torch.cat([to_run_dtype(tensors[t["gate"]], dtype, device),
+                                    to_run_dtype(tensors[t["up"]], dtype, device)])
+        self.w_down = to_run_dtype(tensors[t["down"]], dtype, device)
+
+    def forward(self, h, ctx, residual):
+        gate_up = ops.linear(h, self.w_gate_up)
+        act = ops.swiglu(gate_up)
+        ops.linear(act, self.w_down, residual=residual)
+
+
+register_feed_forward("gated_mlp", GatedMlp)

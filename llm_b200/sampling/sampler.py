@@ -1,0 +1,83 @@
+"""The device sampler: per-sequence parameters, recent-token windows and
+generator states, and one kernel launch per step for all live sequences."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..errors import KernelError
+from .params import SamplingParams
+
+MASK64 = (1 << 64) - 1
+
+
+def _as_signed(value: int) -> int:
+    value &= MASK64
+    return value - (1 << 64) if value >= (1 << 63) else value
+
+
+class BatchSampler:
+    """State for one batch: row i belongs to the batch's i-th sequence for its
+    whole life, whichever rows of logits it later appears in.
+
+    The generator of a sequence starts at `seed | 1` and advances once per
+    drawn token, as one `Sampler` per request does in MythEclipse/llm
+    (apps/engine/src/sampler.rs:43-48); the window holds generated tokens only
+    (apps/engine/src/generate.rs:84-89)."""
+
+    def __init__(self, params: list, vocab: int, device):
+        for p in params:
+            p.check(vocab)
+        self.n = len(params)
+        self.vocab = vocab
+        self.device = torch.device(device)
+        self.params = params
+        self.all_greedy = all(p.temperature <= 0.0 and
+                              (p.repeat_penalty == 1.0 or p.repeat_last_n == 0) for p in params)
+        cap = max([p.repeat_last_n for p in params] + [1])
+        f = torch.tensor([[p.temperature, p.top_p, p.min_p, p.repeat_penalty] for p in params],
+                         dtype=torch.float32)
+        i = torch.tensor([[p.top_k, p.repeat_last_n] for p in params], dtype=torch.int32)
+        rng = torch.tensor([_as_signed(p.seed | 1) for p in params], dtype=torch.int64)
+        self.fparams = f.to(self.device)
+        self.iparams = i.to(self.device)
+        self.rng = rng.to(self.device)
+        self.recent = torch.zeros((self.n, cap), dtype=torch.int32, device=self.device)
+        self.recent_len = torch.zeros((self.n,), dtype=torch.int32, device=self.device)
+        self.status = torch.zeros((self.n,), dtype=torch.int32, device=self.device)
+
+    def sample(self, logits: torch.Tensor, rows: list) -> torch.Tensor:
+        """One token for every row of `logits` (float32 [len(rows), vocab],
+        overwritten); rows[i] is the batch index of the sequence in row i.
+        Returns int32 [len(rows)] on the device and records the tokens in the
+        sequences' windows."""
+        if logits.shape[0] != len(rows):
+            raise KernelError("sample: one logits row per live sequence is needed")
+        if self.all_greedy:
+            return ops.argmax_rows(logits)
+        index = None
+        if len(rows) != self.n or rows != list(range(self.n)):
+            index = torch.tensor(rows, dtype=torch.long, device=self.device)
+        take = (lambda t: t) if index is None else (lambda t: t[index].contiguous())
+        fparams, iparams, rng = take(self.fparams), take(self.iparams), take(self.rng)
+        recent, recent_len, status = take(self.recent), take(self.recent_len), take(self.status)
+        out = torch.empty((len(rows),), dtype=torch.int32, device=self.device)
+        ops.sample_rows(logits, fparams, iparams, recent, recent_len, rng, out, status)
+        # record the drawn tokens in the windows (a ring over the generated tokens)
+        cap = self.recent.shape[1]
+        where = (recent_len % cap).long()
+        recent[torch.arange(len(rows), device=self.device), where] = out
+        recent_len = recent_len + 1
+        if index is None:
+            self.rng, self.recent, self.recent_len, self.status = rng, recent, recent_len, status
+        else:
+            self.rng[index] = rng
+            self.recent[index] = recent
+            self.recent_len[index] = recent_len
+            self.status[index] = status
+        return out
+
+    def check_status(self) -> None:
+        if bool((self.status != 0).any()):
+            raise KernelError("the device sampler refused a row's parameters "
+                              "(top_k beyond its limit, or too many equal logits at the cut)")
