@@ -1,0 +1,280 @@
+"""Every CUDA kernel alone against its plain PyTorch statement (tests/plain_ops.py),
+at sizes other than the tiny models': widths that are no power of two, head
+sizes 16 to 256, group sizes 1 to 8, shuffled pages, a window, and inputs made
+so that a wrong key, page or row shows."""
+import math
+
+import pytest
+import torch
+
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    import llm_b200.ops as o
+    return o
+
+
+def tol(dtype, scale=1.0):
+    return dict(atol=(2e-5 if dtype == torch.float32 else 2e-2) * scale,
+                rtol=1e-5 if dtype == torch.float32 else 2e-2)
+
+
+def randn(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=gen) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    table = randn(301, 72, dtype=dtype)
+    tokens = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops().embed(tokens, table), plain_ops.embed(tokens, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [64, 96, 1000, 4096])
+def test_rmsnorm(dtype, hidden):
+    x = randn(7, hidden, seed=1, scale=3.0)
+    x[3] *= 1e-3                         # a row where eps matters
+    gain = 1.0 + randn(hidden, seed=2, scale=0.1)
+    rows = torch.tensor([6, 0, 3, 3], dtype=torch.int32, device=DEV)
+    for r in (None, rows):
+        got = ops().rmsnorm(x, gain, 1e-5, dtype, r)
+        want = plain_ops.rmsnorm(x, gain, 1e-5, dtype, r)
+        assert torch.allclose(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    gu = randn(5, 2 * 172, dtype=dtype, seed=3, scale=2.0)
+    got = ops().swiglu(gu)
+    assert torch.allclose(got.float(), plain_ops.swiglu(gu).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 96, 64), (7, 172, 64), (65, 100, 172), (129, 384, 96),
+                                   (193, 130, 250), (33, 1000, 80)])
+def test_linear(dtype, m, n, k):
+    a = randn(m, k, dtype=dtype, seed=4)
+    w = randn(n, k, dtype=dtype, seed=5, scale=0.1)
+    bias = randn(n, seed=6)
+    got = ops().linear(a, w, bias)
+    want = plain_ops.linear(a, w, bias)
+    assert torch.allclose(got.float(), want.float(), **tol(dtype, math.sqrt(k) / 8))
+    # 32-bit output (the head) and accumulation into the residual stream
+    got32 = ops().linear(a, w, out_dtype=torch.float32)
+    assert torch.allclose(got32, plain_ops.linear(a, w, out_dtype=torch.float32), **tol(torch.float32, math.sqrt(k)))
+    residual = randn(m, n, seed=7)
+    expect = plain_ops.linear(a, w, bias, residual=residual.clone())
+    ops().linear(a, w, bias, residual=residual)
+    assert torch.allclose(residual, expect, **tol(torch.float32, math.sqrt(k)))
+
+
+def test_linear_rows_do_not_depend_on_the_batch():
+    """32-bit: a row's product is bit-equal whether it is computed alone or among 200 rows."""
+    a = randn(200, 172, seed=8)
+    w = randn(300, 172, seed=9)
+    whole = ops().linear(a, w)
+    for row in (0, 63, 64, 199):
+        assert torch.equal(ops().linear(a[row:row + 1].contiguous(), w)[0], whole[row])
+
+
+def make_cache(n_seqs, lens, n_kv_heads, head_dim, dtype, seed, ring_pages=None):
+    """A shuffled page pool, block tables, and keys/values written position by position."""
+    width = ring_pages or max((n + 63) // 64 for n in lens) + 1
+    n_pages = n_seqs * width + 3
+    gen = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=gen)
+    table = perm[:n_seqs * width].view(n_seqs, width).to(torch.int32).to(DEV)
+    k_cache = torch.full((n_pages, n_kv_heads, 64, head_dim), 7.0, dtype=dtype, device=DEV)
+    v_cache = torch.full((n_pages, n_kv_heads, 64, head_dim), -9.0, dtype=dtype, device=DEV)
+    return table, width, k_cache, v_cache
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,interleaved", [(4, 2, 16, False), (3, 1, 32, True),
+                                                            (8, 8, 64, False), (16, 2, 128, False),
+                                                            (2, 1, 256, False), (6, 2, 48, False)])
+def test_rope_cache_write(dtype, heads, kv_heads, dim, interleaved):
+    starts, counts = [0, 70, 5], [9, 1, 130]
+    lens = [s + c for s, c in zip(starts, counts)]
+    table, width, k_cache, v_cache = make_cache(3, lens, kv_heads, dim, dtype, 10)
+    tok_pos = torch.tensor([p for s, c in zip(starts, counts) for p in range(s, s + c)],
+                           dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([b for b, c in enumerate(counts) for _ in range(c)],
+                           dtype=torch.int32, device=DEV)
+    n = tok_pos.numel()
+    qkv = randn(n, (heads + 2 * kv_heads) * dim, dtype=dtype, seed=11)
+    angle = torch.arange(256, dtype=torch.float64)[:, None] * (
+        10000.0 ** (-2.0 * torch.arange(dim // 2, dtype=torch.float64) / dim))[None, :]
+    rope = torch.cat([angle.cos(), angle.sin()], 1).float().to(DEV)
+    expect_qkv, expect_k, expect_v = qkv.clone(), k_cache.clone(), v_cache.clone()
+    plain_ops.rope_cache_write(expect_qkv, rope, tok_pos, tok_seq, table, width, expect_k,
+                               expect_v, heads, kv_heads, dim, interleaved)
+    ops().rope_cache_write(qkv, rope, tok_pos, tok_seq, table, width, k_cache, v_cache, heads,
+                           kv_heads, dim, interleaved)
+    t = tol(dtype)
+    assert torch.allclose(qkv.float(), expect_qkv.float(), **t)
+    assert torch.allclose(k_cache.float(), expect_k.float(), **t)     # untouched rows keep 7.0
+    assert torch.allclose(v_cache.float(), expect_v.float(), **t)
+    # without a table nothing turns; without write_cache the cache stays
+    q2, k2, v2 = qkv.clone(), k_cache.clone(), v_cache.clone()
+    ops().rope_cache_write(q2, None, tok_pos, tok_seq, table, width, k2, v2, heads, kv_heads, dim,
+                           interleaved, write_cache=False)
+    assert torch.equal(q2, qkv) and torch.equal(k2, k_cache) and torch.equal(v2, v_cache)
+
+
+def fill_cache(table, width, k_cache, v_cache, lens, seed):
+    """Random keys and values at every position < len of every sequence."""
+    kv_heads, dim = k_cache.shape[1], k_cache.shape[3]
+    keys, values = [], []
+    for b, n in enumerate(lens):
+        k = randn(n, kv_heads, dim, seed=seed + 2 * b)
+        v = randn(n, kv_heads, dim, seed=seed + 2 * b + 1)
+        pos = torch.arange(n, device=DEV)
+        pages = table[b].long()[(pos // 64) % width]
+        k_cache[pages, :, pos % 64, :] = k.to(k_cache.dtype)
+        v_cache[pages, :, pos % 64, :] = v.to(v_cache.dtype)
+        keys.append(k)
+        values.append(v)
+    return keys, values
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,window", [(4, 2, 16, 0), (3, 1, 32, 0), (8, 1, 64, 0),
+                                                       (8, 2, 128, 0), (2, 2, 256, 0),
+                                                       (6, 2, 48, 0), (4, 2, 32, 37)])
+def test_attention_prefill_and_decode(dtype, heads, kv_heads, dim, window):
+    lens = [130, 1, 77, 300]
+    table, width, k_cache, v_cache = make_cache(4, lens, kv_heads, dim, dtype, 20)
+    fill_cache(table, width, k_cache, v_cache, lens, 21)
+    scale = 1.0 / math.sqrt(dim)
+    # prefill: every position of every sequence is a query
+    tok_pos = torch.tensor([p for n in lens for p in range(n)], dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([b for b, n in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    qkv = randn(tok_pos.numel(), (heads + 2 * kv_heads) * dim, dtype=dtype, seed=22)
+    got = ops().attention(qkv, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads,
+                          dim, scale, window)
+    want = plain_ops.attention(qkv, k_cache, v_cache, table, width, tok_pos, tok_seq, heads,
+                               kv_heads, dim, scale, window)
+    assert torch.allclose(got.float(), want.float(), **tol(dtype))
+    # decode: one query per sequence at its last position
+    last = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seqs = torch.arange(4, dtype=torch.int32, device=DEV)
+    q1 = randn(4, (heads + 2 * kv_heads) * dim, dtype=dtype, seed=23)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    got = ops().attention(q1, k_cache, v_cache, table, width, last, seqs, heads, kv_heads, dim,
+                          scale, window, decode=True, seq_lens=seq_lens, max_len=max(lens))
+    want = plain_ops.attention(q1, k_cache, v_cache, table, width, last, seqs, heads, kv_heads,
+                               dim, scale, window)
+    assert torch.allclose(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """Among 500 keys one early key matches the query; the output must be its
+    value, and with a window that excludes it, must not be."""
+    heads, kv_heads, dim, n = 4, 2, 64, 500
+    table, width, k_cache, v_cache = make_cache(1, [n], kv_heads, dim, dtype, 30)
+    keys, values = fill_cache(table, width, k_cache, v_cache, [n], 31)
+    far = 3
+    direction = torch.zeros(dim, device=DEV)
+    direction[5] = 40.0
+    page = int(table[0, far // 64])
+    k_cache[page, :, far % 64, :] = direction.to(dtype)
+    qkv = torch.zeros(1, (heads + 2 * kv_heads) * dim, dtype=dtype, device=DEV)
+    qkv[0, :heads * dim] = direction.repeat(heads).to(dtype)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = ops().attention(qkv, k_cache, v_cache, table, width, pos, seq, heads, kv_heads, dim,
+                          1.0 / math.sqrt(dim), 0, decode=True,
+                          seq_lens=torch.tensor([n], dtype=torch.int32, device=DEV), max_len=n)
+    got = got.float().view(heads, dim)
+    for h in range(heads):
+        expect = values[0][far, h // 2].to(dtype).float()
+        assert torch.allclose(got[h], expect, atol=2e-2)
+    windowed = ops().attention(qkv, k_cache, v_cache, table, width, pos, seq, heads, kv_heads,
+                               dim, 1.0 / math.sqrt(dim), 100).float().view(heads, dim)
+    assert not torch.allclose(windowed[0], values[0][far, 0].to(dtype).float(), atol=0.1)
+
+
+def test_attention_window_edge():
+    """The key at position p - window is out, the key at p - window + 1 is in."""
+    heads, kv_heads, dim, n, window = 2, 1, 32, 200, 64
+    dtype = torch.float32
+    table, width, k_cache, v_cache = make_cache(1, [n], kv_heads, dim, dtype, 40)
+    keys, values = fill_cache(table, width, k_cache, v_cache, [n], 41)
+    direction = torch.zeros(dim, device=DEV)
+    direction[0] = 50.0
+    qkv = torch.zeros(1, (heads + 2) * dim, device=DEV)
+    qkv[0, :heads * dim] = direction.repeat(heads)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for key_pos, inside in ((n - 1 - window, False), (n - window, True)):
+        kc = k_cache.clone()
+        kc[int(table[0, key_pos // 64]), :, key_pos % 64, :] = direction
+        got = ops().attention(qkv, kc, v_cache, table, width, pos, seq, heads, kv_heads, dim,
+                              1.0 / math.sqrt(dim), window).view(heads, dim)
+        hit = torch.allclose(got[0], values[0][key_pos, 0], atol=1e-3)
+        assert hit == inside
+
+
+def test_argmax_first_maximum_wins():
+    logits = randn(5, 1000, seed=50)
+    logits[1, 700] = logits[1, 20] = 9.0
+    logits[2] = 0.0
+    got = ops().argmax_rows(logits)
+    assert got.tolist() == plain_ops.argmax_rows(logits).tolist()
+    assert got[1] == 20 and got[2] == 0
+
+
+def _sampler_state(n, params, iparams, seeds, cap=8):
+    f = torch.tensor(params, dtype=torch.float32, device=DEV)
+    i = torch.tensor(iparams, dtype=torch.int32, device=DEV)
+    rng = torch.tensor([(s | 1) - (1 << 64) if (s | 1) >= (1 << 63) else (s | 1) for s in seeds],
+                       dtype=torch.int64, device=DEV)
+    recent = torch.zeros((n, cap), dtype=torch.int32, device=DEV)
+    recent_len = torch.zeros((n,), dtype=torch.int32, device=DEV)
+    out = torch.zeros((n,), dtype=torch.int32, device=DEV)
+    status = torch.zeros((n,), dtype=torch.int32, device=DEV)
+    return f, i, recent, recent_len, rng, out, status
+
+
+@pytest.mark.parametrize("vocab", [384, 5000])
+def test_sample_rows_matches_plain_chain(vocab):
+    """Greedy, temperature with top-k / top-p / min-p, penalty, and no top-k at all:
+    the same tokens and generator states as the plain chain, over several draws."""
+    params = [[0.0, 0.75, 0.25, 1.0], [0.8, 0.75, 0.25, 1.1], [1.5, 0.95, 0.0, 1.3],
+              [1.0, 1.0, 0.0, 1.0], [0.7, 2.0, 0.05, 1.0]]
+    iparams = [[40, 64], [40, 64], [7, 4], [0, 0], [0, 0]]
+    seeds = [1, 1, 0x5EED1234ABCD0001, 99, 12345]
+    n = len(params)
+    state_gpu = _sampler_state(n, params, iparams, seeds)
+    state_cpu = [t.cpu().clone() for t in state_gpu]
+    state_gpu[2][:, :3] = torch.tensor([3, 3, 10], dtype=torch.int32)
+    state_cpu[2][:, :3] = torch.tensor([3, 3, 10], dtype=torch.int32)
+    state_gpu[3][:] = 3
+    state_cpu[3][:] = 3
+    for draw in range(6):
+        logits = randn(n, vocab, seed=60 + draw, scale=2.5)
+        logits[:, 3] = 4.0            # a penalised token that matters
+        cpu_logits = logits.cpu().clone()
+        ops().sample_rows(logits, *state_gpu)
+        plain_ops.sample_rows(cpu_logits, *state_cpu)
+        assert state_gpu[5].tolist() == state_cpu[5].tolist(), f"draw {draw}"
+        assert state_gpu[4].tolist() == state_cpu[4].tolist()
+        assert state_gpu[6].tolist() == [0] * n
+
+
+def test_sample_rows_refuses_what_it_cannot_rank():
+    f, i, recent, recent_len, rng, out, status = _sampler_state(
+        2, [[1.0, 0.9, 0.0, 1.0], [1.0, 1.0, 0.0, 1.0]], [[0, 0], [2000, 0]], [1, 2])
+    logits = randn(2, 5000, seed=70)
+    ops().sample_rows(logits, f, i, recent, recent_len, rng, out, status)
+    assert status.tolist() == [1, 1]

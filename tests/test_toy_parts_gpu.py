@@ -1,0 +1,172 @@
+"""Parts defined here, outside the library, can be registered, built and
+stepped: a mixer that keeps state of its own (a decaying sum per sequence), in
+one model with attention layers, a layer that runs twice, and a layer that
+reads another layer's cache. No file of the library knows these."""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+from tiny import random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@dataclass(frozen=True)
+class DecaySpec:
+    hidden: int
+    decay: float
+    weight: str
+    kind: str = "toy_decay"
+
+
+def define_toy():
+    from llm_b200.cache import StateRequest
+    from llm_b200.config import ConfigReader, register_architecture
+    from llm_b200.parts import Mixer, register_mixer
+    from llm_b200.parts.spec import (AttentionSpec, BlockSpec, GatedMlpSpec, ModelSpec, NormSpec,
+                                     PositionSpec, ScheduleEntry, names)
+    from llm_b200.weights import ParamSpec
+
+    class DecayMixer(Mixer):
+        """state <- decay * state + h_t; output = (state) W^T, token after token."""
+
+        def __init__(self, spec):
+            self.spec = spec
+            self.w = None
+
+        def parameters(self):
+            return {self.spec.weight: ParamSpec((self.spec.hidden, self.spec.hidden))}
+
+        def bind(self, tensors, dtype, device):
+            self.w = tensors[self.spec.weight].to(device=device, dtype=torch.float32)
+
+        def state_request(self):
+            return StateRequest((self.spec.hidden,), torch.float32)
+
+        def forward(self, h, ctx, entry, cache_entry, residual):
+            state = ctx.cache.state_view(entry)
+            at = 0
+            for b, n in enumerate(ctx.new_counts):
+                s = state[ctx.slot_ids[b]].clone()
+                for t in range(at, at + n):
+                    s = self.spec.decay * s + h[t].float()
+                    residual[t] += s @ self.w.T
+                state[ctx.slot_ids[b]] = s
+                at += n
+
+    register_mixer("toy_decay", DecayMixer)
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        hidden: int
+        vocab: int
+        decay: float
+
+        @classmethod
+        def from_dict(cls, raw, where="config.json"):
+            r = ConfigReader(raw, where)
+            return cls(r.integer("hidden"), r.integer("vocab"), r.number("decay"))
+
+        def to_dict(self):
+            return {"architectures": ["ToyHybrid"], "hidden": self.hidden, "vocab": self.vocab,
+                    "decay": self.decay}
+
+        def model_spec(self):
+            h = self.hidden
+            rope = PositionSpec(head_dim=16, theta=10000.0, max_positions=512)
+            def attention(i):
+                p = f"layers.{i}.attn."
+                return AttentionSpec(hidden=h, n_heads=4, n_kv_heads=2, head_dim=16, scale=0.25,
+                                     bias=False, window=0, position=rope,
+                                     names=names(q=p + "q", k=p + "k", v=p + "v", o=p + "o"))
+            def mlp(i):
+                p = f"layers.{i}.mlp."
+                return GatedMlpSpec(hidden=h, intermediate=40, activation="silu",
+                                    names=names(gate=p + "gate", up=p + "up", down=p + "down"))
+            def block(i, mixer):
+                return BlockSpec(NormSpec(h, 1e-5, f"layers.{i}.n1"), mixer,
+                                 NormSpec(h, 1e-5, f"layers.{i}.n2"), mlp(i))
+            blocks = (block(0, attention(0)), block(1, DecaySpec(h, self.decay, "layers.1.mix")),
+                      block(2, attention(2)))
+            # layer 0, the stateful layer, layer 0 again (a cache of its own), then
+            # layer 2 reading the keys and values of the first run of layer 0
+            schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0),
+                        ScheduleEntry(2, cache_of=0))
+            return ModelSpec("ToyHybrid", self.vocab, h, 512, "embed", blocks, schedule,
+                             NormSpec(h, 1e-5, "final_norm"), None)
+
+    register_architecture("ToyHybrid", ToyConfig)
+    return ToyConfig
+
+
+def plain_toy(config, w, tokens):
+    """The toy model on whole sequences with the plain parts."""
+    import plain_llama as P
+    h, n = config.hidden, len(tokens)
+    x = P.embedding(w["embed"], tokens)
+    inv_freq = P.rope_inverse_frequencies(16, 10000.0)
+    positions = list(range(n))
+    first_kv = {}
+    def attention(i, x, shared=None):
+        p = f"layers.{i}.attn."
+        hn = P.rms_norm(x, w[f"layers.{i}.n1"], 1e-5)
+        q = P.rope_rotate((hn @ w[p + "q"].T).view(n, 4, 16), positions, inv_freq)
+        if shared is None:
+            k = P.rope_rotate((hn @ w[p + "k"].T).view(n, 2, 16), positions, inv_freq)
+            v = (hn @ w[p + "v"].T).view(n, 2, 16)
+        else:
+            k, v = shared
+        a = P.causal_attention(q, k, v, 0.25).reshape(n, 64)
+        return x + a @ w[p + "o"].T, (k, v)
+    def mlp(i, x):
+        p = f"layers.{i}.mlp."
+        hn = P.rms_norm(x, w[f"layers.{i}.n2"], 1e-5)
+        return x + P.gated_mlp(hn, w[p + "gate"], w[p + "up"], w[p + "down"])
+    x, kv0 = attention(0, x)
+    x = mlp(0, x)
+    hn = P.rms_norm(x, w["layers.1.n1"], 1e-5)
+    s = torch.zeros(h)
+    mixed = torch.zeros_like(x)
+    for t in range(n):
+        s = config.decay * s + hn[t]
+        mixed[t] = s @ w["layers.1.mix"].T
+    x = mlp(1, x + mixed)
+    x, _ = attention(0, x)
+    x = mlp(0, x)
+    x, _ = attention(2, x, shared=kv0)
+    x = mlp(2, x)
+    return P.rms_norm(x, w["final_norm"], 1e-5) @ w["embed"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_model_with_state_steps_like_its_plain_form(tmp_path, dtype):
+    import plain_llama
+    from llm_b200.engine import Engine, Entry, load_model
+    from llm_b200.weights import write_random_model
+    ToyConfig = define_toy()
+    config = ToyConfig(hidden=64, vocab=200, decay=0.5)
+    folder = write_random_model(tmp_path / "toy", config, seed=3, dtype=torch.bfloat16, std=0.08)
+    _, weights = plain_llama.read_model_folder(folder)
+    model = load_model(folder, dtype, DEV)
+    engine = Engine(model, max_tokens=1024)
+    seqs = [random_tokens(n, 200, n) for n in (20, 5, 70)]
+    expected = [plain_toy(config, weights, s) for s in seqs]
+    for round_index in range(2):          # the second round reuses slots: state must restart at zero
+        slots = engine.acquire(3)
+        heads = [len(s) - 4 for s in seqs]
+        logits = engine.step([Entry(sl, s[:n], [n - 1]) for sl, s, n in zip(slots, seqs, heads)])
+        got = [[logits[b]] for b in range(3)]
+        for k in range(4):
+            logits = engine.step([Entry(sl, [s[n + k]], [0]) for sl, s, n in zip(slots, seqs, heads)])
+            for b in range(3):
+                got[b].append(logits[b])
+        for b in range(3):
+            g = torch.stack(got[b]).float().cpu()
+            want = expected[b][heads[b] - 1:]
+            scale = float(want.abs().max())
+            limit = 2e-4 if dtype == torch.float32 else 0.04
+            assert float((g - want).abs().max()) <= limit * max(scale, 1.0), (round_index, b)
+        engine.release(slots)
+        engine.cache.check()
