@@ -47,8 +47,24 @@ def _require_cuda(*tensors):
             raise KernelError("llm_b200 kernels need tensors on a CUDA device; there is no CPU path")
 
 
-def _call(lib_name: str, fn_name: str, *args):
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process. A step that is
+    replayed from a CUDA graph adds the kernels the graph holds."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _call(lib_name: str, fn_name: str, *args, kernels: int = 1):
+    global _launches
     lib = load_library(lib_name)
+    _launches += kernels
     code = getattr(lib, fn_name)(*args)
     if code != 0:
         reader = getattr(lib, f"llmb_{lib_name}_last_error")
@@ -194,5 +210,5 @@ def required_libraries() -> list:
 
 
 __all__ = ["PAGE", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
-           "argmax_rows", "sample_rows", "ensure_built", "load_library", "all_sources",
+           "argmax_rows", "sample_rows", "launch_count", "count_launches", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]
