@@ -125,6 +125,27 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
 
 # ----------------------------------------------------------------------------- matrix product
 
+_scratch: dict = {}
+
+
+def _skinny_scratch(device, m, n, k):
+    """Partial sums and tile counters of the split-K decode product, one pair per
+    device, shared by every call on the stream (calls run one after the other).
+    It grows when a call needs more; it never shrinks."""
+    lib = load_library("gemm_skinny")
+    lib.llmb_gemm_skinny_scratch_bytes.restype = ctypes.c_longlong
+    need = lib.llmb_gemm_skinny_scratch_bytes(_c_int(m), _c_int(n), _c_int(k))
+    tiles = (n + 15) // 16
+    held = _scratch.get(device)
+    if held is None or held[0].numel() * 4 < need or held[1].numel() < tiles:
+        floats = max(need // 4, held[0].numel() if held else 0, 1 << 22)
+        count = max(tiles, held[1].numel() if held else 0, 1 << 14)
+        held = (torch.empty(floats, dtype=torch.float32, device=device),
+                torch.zeros(count, dtype=torch.int32, device=device))
+        _scratch[device] = held
+    return held
+
+
 def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
     """a [M, K] . w [N, K]^T (+ bias [N], float32). With `residual` (float32
     [M, N]) the product is added to it in place and it is returned; otherwise a
@@ -143,7 +164,14 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
         target_dtype = out_dtype or a.dtype
         result = out if out is not None else torch.empty((m, n), dtype=target_dtype, device=a.device)
     variant = tactics.choose_linear(m, n, k, a.dtype, target_dtype, a.stride(0))
-    if variant == "gemm_simt":
+    if variant == "gemm_skinny":
+        partials, counters = _skinny_scratch(a.device, m, n, k)
+        _call("gemm_skinny", "llmb_gemm_skinny", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),
+              _ptr(result if residual is None else None), _c_int(_code(target_dtype)),
+              _ptr(residual), _ptr(partials), ctypes.c_longlong(partials.numel() * 4),
+              _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k), _c_int(n),
+              _stream())
+    elif variant == "gemm_simt":
         _call("gemm_simt", "llmb_gemm_simt", _ptr(a), _ptr(w), _ptr(bias),
               _ptr(result if residual is None else None), _ptr(residual),
               _c_int(_code(a.dtype)), _c_int(_code(target_dtype)), _c_int(m), _c_int(n), _c_int(k),
@@ -154,6 +182,23 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
 
 
 # ----------------------------------------------------------------------------- attention
+
+_attention_scratch: dict = {}
+
+
+def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
+    """Into how many slices the keys of every sequence are cut for decode
+    attention: enough blocks to fill the GPU (two per SM), a power of two (so
+    that captured steps fall into few shapes), at most one slice per page."""
+    pages = max(1, (max_len + PAGE - 1) // PAGE)
+    want = max(1, -(-296 // max(1, n_seqs * n_kv_heads)))
+    splits = 1
+    while splits < want and splits < 64:
+        splits *= 2
+    while splits > pages:
+        splits //= 2
+    return max(splits, 1)
+
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
@@ -166,7 +211,23 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window)
-    if variant == "attention_generic":
+    if variant == "attention_decode":
+        splits = decode_splits(n, n_kv_heads, max_len)
+        lib = load_library("attention_decode")
+        lib.llmb_attention_decode_scratch_floats.restype = ctypes.c_longlong
+        need = lib.llmb_attention_decode_scratch_floats(_c_int(n), _c_int(n_heads), _c_int(head_dim),
+                                                        _c_int(splits))
+        scratch = _attention_scratch.get(qkv.device)
+        if scratch is None or scratch.numel() < need:
+            scratch = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=qkv.device)
+            _attention_scratch[qkv.device] = scratch
+        _call("attention_decode", "llmb_attention_decode", _ptr(qkv), _c_int(qkv.stride(0)),
+              _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
+              _c_int(ring_pages), _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)), _ptr(scratch),
+              ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
+              _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream(),
+              kernels=2)
+    elif variant == "attention_generic":
         _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
               _c_int(ring_pages), _ptr(tok_pos), _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)),
@@ -206,7 +267,8 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 
 def required_libraries() -> list:
     """Names of the kernel files the decoder parts of this package use."""
-    return ["elementwise", "gemm_simt", "attention_generic", "sampling"]
+    return ["elementwise", "gemm_simt", "gemm_skinny", "attention_generic", "attention_decode",
+            "sampling"]
 
 
 __all__ = ["PAGE", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",

@@ -27,13 +27,43 @@ def _always(**_):
     return None
 
 
+def _skinny_guard(m, n, k, in_dtype, out_dtype, lda, **_):
+    if in_dtype != torch.bfloat16:
+        return "bfloat16 operands only"
+    if m > 64:
+        return f"{m} rows exceed 64"
+    if k % 8 or lda % 8:
+        return f"K {k} or the row stride {lda} is no multiple of 8 elements (16-byte loads)"
+    return None
+
+
 LINEAR = [
+    Tactic("gemm_skinny", 20, _skinny_guard,
+           "decode product for up to 64 rows: W streamed once with 128-bit loads into "
+           "mma.sync fragments, K split over warps with an ordered last-arriver sum"),
     Tactic("gemm_simt", 0, _always,
            "CUDA-core product with a fixed summation order; any shape and stride; the only "
            "variant of the 32-bit path"),
 ]
 
+def _decode_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, **_):
+    if not decode:
+        return "serves steps in which every sequence brings one token"
+    if dtype != torch.bfloat16:
+        return "bfloat16 caches only"
+    if window:
+        return "no window"
+    if n_heads // n_kv_heads > 8:
+        return f"group of {n_heads // n_kv_heads} query heads exceeds 8"
+    if head_dim not in (32, 64, 96, 128):
+        return f"head_dim {head_dim} (served: 32, 64, 96, 128)"
+    return None
+
+
 ATTENTION = [
+    Tactic("attention_decode", 20, _decode_guard,
+           "split-KV decode attention: pages through shared memory with cp.async, the query "
+           "heads of a group as rows of mma.sync tiles, partials merged by a second kernel"),
     Tactic("attention_generic", 0, _always,
            "one block per (token, head), 32-bit arithmetic, any head size up to 256, any group, "
            "window and ring; the only variant of the 32-bit path"),

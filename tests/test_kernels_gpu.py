@@ -76,6 +76,33 @@ def test_linear(dtype, m, n, k):
     assert torch.allclose(residual, expect, **tol(torch.float32, math.sqrt(k)))
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 6144, 4096), (8, 1000, 200), (5, 72, 1032),
+                                   (16, 4096, 14336), (17, 100, 1024), (33, 520, 2048),
+                                   (64, 4100, 4096)])
+def test_linear_decode_kernel(m, n, k):
+    """The split-K decode product: sizes with one and many splits, tails in N, K and M,
+    called twice so that the tile counters must have been left at zero."""
+    from llm_b200.ops import tactics
+    assert tactics.choose_linear(m, n, k, torch.bfloat16, torch.bfloat16, k) == "gemm_skinny"
+    a = randn(m, k, dtype=torch.bfloat16, seed=80)
+    w = randn(n, k, dtype=torch.bfloat16, seed=81, scale=0.05)
+    bias = randn(n, seed=82)
+    want = plain_ops.linear(a, w, bias, out_dtype=torch.float32)
+    scale = float(want.abs().max())
+    for _ in range(2):
+        got = ops().linear(a, w, bias, out_dtype=torch.float32)
+        assert float((got - want).abs().max()) <= 2e-3 * scale
+    got16 = ops().linear(a, w, bias)
+    assert float((got16.float() - want).abs().max()) <= 1e-2 * scale
+    residual = randn(m, n, seed=83)
+    expect = residual + want
+    ops().linear(a, w, bias, residual=residual)
+    assert float((residual - expect).abs().max()) <= 2e-3 * scale
+    # the same rows alone and in the batch: the same split and order, bit-equal
+    alone = ops().linear(a[:1].contiguous(), w, bias, out_dtype=torch.float32)
+    assert torch.equal(alone[0], got[0])
+
+
 def test_linear_rows_do_not_depend_on_the_batch():
     """32-bit: a row's product is bit-equal whether it is computed alone or among 200 rows."""
     a = randn(200, 172, seed=8)
@@ -174,6 +201,29 @@ def test_attention_prefill_and_decode(dtype, heads, kv_heads, dim, window):
     want = plain_ops.attention(q1, k_cache, v_cache, table, width, last, seqs, heads, kv_heads,
                                dim, scale, window)
     assert torch.allclose(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim", [(32, 8, 128), (8, 1, 64), (6, 2, 96), (4, 4, 32),
+                                                (3, 1, 128)])
+def test_attention_decode_kernel_long_contexts(heads, kv_heads, dim):
+    """The split-KV decode kernel at lengths from 1 to 3000 in one batch (page edges,
+    empty slices, many slices), twice in a row on the same scratch."""
+    from llm_b200.ops import tactics
+    dtype = torch.bfloat16
+    assert tactics.choose_attention(True, dtype, heads, kv_heads, dim, 0) == "attention_decode"
+    lens = [3000, 1, 64, 65, 1000, 127]
+    table, width, k_cache, v_cache = make_cache(len(lens), lens, kv_heads, dim, dtype, 90)
+    fill_cache(table, width, k_cache, v_cache, lens, 91)
+    last = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seqs = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    q = randn(len(lens), (heads + 2 * kv_heads) * dim, dtype=dtype, seed=92)
+    want = plain_ops.attention(q, k_cache, v_cache, table, width, last, seqs, heads, kv_heads, dim,
+                               dim ** -0.5)
+    for _ in range(2):
+        got = ops().attention(q, k_cache, v_cache, table, width, last, seqs, heads, kv_heads, dim,
+                              dim ** -0.5, 0, decode=True, seq_lens=seq_lens, max_len=max(lens))
+        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

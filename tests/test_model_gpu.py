@@ -45,7 +45,7 @@ def engine_for(folder, dtype, **options):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "D"])
 def test_whole_request(folders, plain, dtype, which):
     from llm_b200.engine import Entry
     config, weights = plain[which]
@@ -60,7 +60,7 @@ def test_whole_request(folders, plain, dtype, which):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "D"])
 def test_last_32_tokens_one_by_one(folders, plain, dtype, which):
     from llm_b200.engine import Entry
     config, weights = plain[which]
@@ -76,13 +76,13 @@ def test_last_32_tokens_one_by_one(folders, plain, dtype, which):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "D"])
 def test_unequal_batches_with_slot_reuse(folders, plain, dtype, which):
     """Two batches one after the other on a cache that holds only one of them:
     the second batch gets the first one's slots and pages back."""
     from llm_b200.engine import Entry
     config, weights = plain[which]
-    lengths = [5, 9, 17, 70] if which == "A" else [1, 7, 33, 64]
+    lengths = [1, 7, 33, 64] if which == "B" else [5, 9, 17, 70]
     extra = [3, 10, 6, 10]
     engine = engine_for(folders[which], dtype, max_tokens=64 * 5, max_slots=4)
     for batch in range(2):
@@ -109,12 +109,13 @@ def test_unequal_batches_with_slot_reuse(folders, plain, dtype, which):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(folders, plain, dtype):
+@pytest.mark.parametrize("which", ["C", "D"])
+def test_long_decoding(folders, plain, dtype, which):
     """300 decode steps after a 40-token prompt, across several pages, beside a
     second sequence that grows from 1 token."""
     from llm_b200.engine import Entry
-    config, weights = plain["C"]
-    engine = engine_for(folders["C"], dtype)
+    config, weights = plain[which]
+    engine = engine_for(folders[which], dtype)
     a = random_tokens(340, config["vocab_size"], 1)
     b = random_tokens(301, config["vocab_size"], 2)
     expect_a = plain_llama.forward(config, weights, a)

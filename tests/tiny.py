@@ -38,7 +38,16 @@ TINY_C = {
     "attention_bias": False, "max_position_embeddings": 1024, "hidden_act": "silu",
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# sizes the tensor-core kernels serve: head size 64, widths that are multiples of 64
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 320, "vocab_size": 512,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "attention_bias": True, "max_position_embeddings": 1024, "hidden_act": "silu",
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def make_folder(tmp_path, which: str, dtype=torch.bfloat16, std=None):
