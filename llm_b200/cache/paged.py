@@ -63,6 +63,7 @@ class Group:
     pool: FreeList | None = None
     storage: torch.Tensor | None = None               # [entries, 2, pages, Hkv, PAGE, D]
     slot_pages: dict = field(default_factory=dict)    # slot -> list of physical pages
+    host_table: torch.Tensor | None = None            # int32 [slots, ring_pages], mirrors slot_pages
 
 
 class PagedCache:
@@ -109,6 +110,7 @@ class PagedCache:
                 group.ring_pages = seq_pages
                 n_pages = total_pages
             group.pool = FreeList(n_pages, f"page of the {group.kind} group")
+            group.host_table = torch.zeros((max_slots, group.ring_pages), dtype=torch.int32)
             group.storage = torch.zeros(
                 (len(group.entries), 2, n_pages, group.n_kv_heads, PAGE, group.head_dim),
                 dtype=dtype, device=self.device)
@@ -128,6 +130,7 @@ class PagedCache:
         self.lengths[slot] = 0
         for group in self.groups:
             group.slot_pages[slot] = []
+            group.host_table[slot].zero_()
         for state in self.states:
             if state is not None:
                 state[slot].zero_()
@@ -160,7 +163,9 @@ class PagedCache:
             needs.append(extra)
         for group, extra in zip(self.groups, needs):
             for _ in range(max(extra, 0)):
-                group.slot_pages[slot].append(group.pool.take())
+                page = group.pool.take()
+                group.host_table[slot, len(group.slot_pages[slot])] = page
+                group.slot_pages[slot].append(page)
 
     def reserve_many(self, wanted) -> None:
         """`reserve` for several (slot, new_length) pairs: all of them or none."""
@@ -201,15 +206,10 @@ class PagedCache:
     def table_width(self, group_index: int) -> int:
         return self.groups[group_index].ring_pages
 
-    def block_table_rows(self, group_index: int, slots) -> list:
-        """One row of physical pages per slot, padded with 0 to the group's width."""
-        group = self.groups[group_index]
-        width = group.ring_pages
-        rows = []
-        for slot in slots:
-            pages = group.slot_pages[slot]
-            rows.append(pages + [0] * (width - len(pages)))
-        return rows
+    def block_table_rows(self, group_index: int, slots) -> torch.Tensor:
+        """int32 [len(slots), width] on the host: one row of physical pages per
+        slot, 0 where the slot has no page yet."""
+        return self.groups[group_index].host_table[torch.as_tensor(slots, dtype=torch.long)]
 
     def layer_view(self, entry: int):
         """(group index, keys, values) of the schedule entry that owns storage:

@@ -50,6 +50,9 @@ class DecoderModel:
         names += list(self.final_norm.libraries)
         return list(dict.fromkeys(names))
 
+    def graph_safe(self) -> bool:
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+
     def bind(self, tensors: dict, dtype, device) -> "DecoderModel":
         """Move the tensors to the device in the run's dtype; parts may fuse
         them. `tensors` may hold CPU or device tensors; entries are dropped as

@@ -21,6 +21,9 @@ from ..errors import ContextFull, FormatError, LlmError
 from ..parts.base import StepContext
 
 
+GRAPH_AFTER_STEPS = 2      # plain steps of a shape before it is captured
+
+
 @dataclass
 class Entry:
     """One sequence's share of a step."""
@@ -40,10 +43,13 @@ class Engine:
     step_tokens: most new tokens of one sequence in one pass over the layers;
         longer prompts are cut into passes (each attends to everything cached
         before it, as the chunks of apps/engine/src/session.rs:109-130 do).
+    use_graphs: replay decode steps from CUDA graphs (only if every part of the
+        model says it can be captured).
     """
 
     def __init__(self, model, max_tokens: int, max_seq_len: int | None = None,
-                 max_slots: int | None = None, step_tokens: int | None = None):
+                 max_slots: int | None = None, step_tokens: int | None = None,
+                 use_graphs: bool = True):
         if model.embedding is None:
             raise LlmError("the model has no weights bound")
         self.model = model
@@ -61,6 +67,10 @@ class Engine:
                                 self.dtype, self.device, self.step_tokens)
         self.vocab = model.spec.vocab
         self.steps_run = 0
+        self.use_graphs = (use_graphs and self.device.type == "cuda"
+                           and getattr(model, "graph_safe", lambda: False)())
+        self._graphs, self._graph_seen, self._graph_pool = {}, {}, None
+        self._ring, self._ring_at = [(None, None)] * 4, 0
 
     # ------------------------------------------------------------------ sequences
 
@@ -93,11 +103,13 @@ class Engine:
             seen.add(e.slot)
             if len(e.tokens) == 0:
                 raise FormatError(f"slot {e.slot} brings no token")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab:
-                    raise FormatError(f"token id {t} is outside the vocabulary of {self.vocab}")
+            e.tokens = [int(t) for t in e.tokens]
+            e.want = [int(w) for w in e.want]
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+                bad = next(t for t in e.tokens if not 0 <= t < self.vocab)
+                raise FormatError(f"token id {bad} is outside the vocabulary of {self.vocab}")
             for w in e.want:
-                if not 0 <= int(w) < len(e.tokens):
+                if not 0 <= w < len(e.tokens):
                     raise FormatError(f"wanted place {w} is outside the {len(e.tokens)} tokens "
                                       f"of slot {e.slot}")
             new_length = self.cache.length(e.slot) + len(e.tokens)
@@ -133,47 +145,113 @@ class Engine:
             start = cache.length(e.slot)
             n = len(e.tokens)
             base = len(tokens)
-            tokens += [int(t) for t in e.tokens]
+            tokens += e.tokens
             tok_pos += range(start, start + n)
             tok_seq += [b] * n
             cu.append(base + n)
             seq_lens.append(start + n)
-            rows += [base + int(w) for w in e.want]
+            rows += [base + w for w in e.want]
             starts.append(start)
             counts.append(n)
         slots = [e.slot for e in entries]
+        sections = [tokens, tok_pos, tok_seq, cu, seq_lens, slots, rows]
         tables = [cache.block_table_rows(g, slots) for g in range(len(cache.groups))]
-        ctx, tokens_dev, rows_dev = self._upload(tokens, tok_pos, tok_seq, cu, seq_lens, slots,
-                                                 rows, tables, starts, counts)
-        logits = self.model.forward(tokens_dev, ctx, rows_dev)
+        offsets, total = [], 0
+        for size in [len(s) for s in sections] + [t.numel() for t in tables]:
+            offsets.append(total)
+            total += (size + 3) // 4 * 4            # every section starts 16-byte aligned
+        host = self._host_buffer(max(total, 4))
+        flat = torch.tensor([v for s in sections for v in s], dtype=torch.int32)
+        at = 0
+        for s, offset in zip(sections, offsets):
+            host[offset:offset + len(s)] = flat[at:at + len(s)]
+            at += len(s)
+        for t, offset in zip(tables, offsets[len(sections):]):
+            host[offset:offset + t.numel()] = t.reshape(-1)
+        sizes = [len(s) for s in sections] + [t.numel() for t in tables]
+        decode = all(c == 1 for c in counts)
+        max_len = max(seq_lens)
+
+        def context(dev):
+            def view(i):
+                return dev[offsets[i]:offsets[i] + sizes[i]]
+            n_seqs = len(slots)
+            ctx = StepContext(
+                n_tokens=len(tokens), n_seqs=n_seqs, dtype=self.dtype, device=self.device,
+                tok_pos=view(1), tok_seq=view(2), cu_seqlens=view(3), seq_lens=view(4),
+                slot_ids=view(5), cache=self.cache,
+                block_tables=[view(7 + g).view(n_seqs, -1) for g in range(len(tables))],
+                decode=decode, new_counts=counts, starts=starts, max_len=max_len)
+            return ctx, view(0), view(6)
+
+        logits = None
+        if self.use_graphs and decode and all(e.want == [0] for e in entries):
+            logits = self._replay(len(entries), max_len, host, total, context)
+        if logits is None:
+            dev = host[:max(total, 4)].to(self.device, non_blocking=True)
+            self._host_done(host)
+            ctx, tokens_dev, rows_dev = context(dev)
+            logits = self.model.forward(tokens_dev, ctx, rows_dev)
         for e, new_length in zip(entries, seq_lens):
             cache.set_length(e.slot, new_length)
         self.steps_run += 1
         return logits
 
-    def _upload(self, tokens, tok_pos, tok_seq, cu, seq_lens, slots, rows, tables, starts, counts):
-        """One host buffer, one copy: every integer array of the step."""
-        sections = [tokens, tok_pos, tok_seq, cu, seq_lens, slots, rows]
-        flat_tables = [[p for row in t for p in row] for t in tables]
-        sections += flat_tables
-        offsets, total = [], 0
-        for s in sections:
-            offsets.append(total)
-            total += (len(s) + 3) // 4 * 4          # keep every section 16-byte aligned
-        host = torch.zeros(max(total, 4), dtype=torch.int32, pin_memory=self.device.type == "cuda")
-        for s, at in zip(sections, offsets):
-            if s:
-                host[at:at + len(s)] = torch.tensor(s, dtype=torch.int32)
-        dev = host.to(self.device, non_blocking=True)
+    # ------------------------------------------------------------------ host staging
 
-        def view(i):
-            return dev[offsets[i]:offsets[i] + len(sections[i])]
-        n_seqs = len(slots)
-        block_tables = [view(7 + g).view(n_seqs, -1) for g in range(len(tables))]
-        ctx = StepContext(
-            n_tokens=len(tokens), n_seqs=n_seqs, dtype=self.dtype, device=self.device,
-            tok_pos=view(1), tok_seq=view(2), cu_seqlens=view(3), seq_lens=view(4),
-            slot_ids=view(5).long(), block_tables=block_tables, cache=self.cache,
-            decode=all(c == 1 for c in counts), new_counts=counts, starts=starts,
-            max_len=max(seq_lens))
-        return ctx, view(0), view(6)
+    def _host_buffer(self, n_ints: int) -> torch.Tensor:
+        """A pinned staging buffer that no copy in flight still reads: a ring of
+        four, each guarded by the event recorded after its last copy."""
+        if self.device.type != "cuda":
+            return torch.zeros(n_ints, dtype=torch.int32)
+        self._ring_at = (self._ring_at + 1) % len(self._ring)
+        buffer, event = self._ring[self._ring_at]
+        if buffer is None or buffer.numel() < n_ints:
+            buffer = torch.zeros(max(n_ints, 4096), dtype=torch.int32, pin_memory=True)
+            event = torch.cuda.Event()
+            self._ring[self._ring_at] = (buffer, event)
+        else:
+            event.synchronize()
+        return buffer
+
+    def _host_done(self, buffer) -> None:
+        if self.device.type == "cuda":
+            self._ring[self._ring_at][1].record()
+
+    # ------------------------------------------------------------------ captured decode steps
+
+    def _replay(self, n_seqs, max_len, host, total, context):
+        """Decode steps of one shape (sequences, power-of-two bucket of pages)
+        run from a CUDA graph once that shape has been seen GRAPH_AFTER_STEPS
+        times, as the decode graphs of apps/engine/src/model.rs:699-729 are
+        keyed by split count and captured after some plain steps. Every value
+        that changes between steps (tokens, positions, lengths, pages) is read
+        by the kernels from one device buffer that is refreshed before the
+        replay."""
+        pages = max(1, (max_len + PAGE - 1) // PAGE)
+        key = (n_seqs, pages.bit_length())
+        graph = self._graphs.get(key)
+        if graph is None:
+            seen = self._graph_seen.get(key, 0) + 1
+            self._graph_seen[key] = seen
+            if seen <= GRAPH_AFTER_STEPS:
+                return None
+            meta = torch.zeros(total, dtype=torch.int32, device=self.device)
+            meta.copy_(host[:total], non_blocking=True)
+            ctx, tokens_dev, rows_dev = context(meta)
+            before = ops.launch_count()
+            torch.cuda.synchronize(self.device)
+            cuda_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cuda_graph, pool=self._graph_pool):
+                out = self.model.forward(tokens_dev, ctx, rows_dev)
+            if self._graph_pool is None:
+                self._graph_pool = cuda_graph.pool()
+            graph = (cuda_graph, meta, out, ops.launch_count() - before)
+            ops.count_launches(-graph[3])            # capturing ran nothing
+            self._graphs[key] = graph
+        cuda_graph, meta, out, kernels = graph
+        meta.copy_(host[:total], non_blocking=True)
+        self._host_done(host)
+        cuda_graph.replay()
+        ops.count_launches(kernels)
+        return out.clone()

@@ -126,6 +126,7 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
 # ----------------------------------------------------------------------------- matrix product
 
 _scratch: dict = {}
+_retired: list = []      # outgrown scratch buffers, kept alive for CUDA graphs that hold their address
 
 
 def _skinny_scratch(device, m, n, k):
@@ -138,8 +139,10 @@ def _skinny_scratch(device, m, n, k):
     tiles = (n + 15) // 16
     held = _scratch.get(device)
     if held is None or held[0].numel() * 4 < need or held[1].numel() < tiles:
-        floats = max(need // 4, held[0].numel() if held else 0, 1 << 22)
+        floats = max(need // 4, held[0].numel() if held else 0, 1 << 23)
         count = max(tiles, held[1].numel() if held else 0, 1 << 14)
+        if held is not None:
+            _retired.append(held)       # a captured step may still point at it
         held = (torch.empty(floats, dtype=torch.float32, device=device),
                 torch.zeros(count, dtype=torch.int32, device=device))
         _scratch[device] = held
@@ -184,6 +187,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
 # ----------------------------------------------------------------------------- attention
 
 _attention_scratch: dict = {}
+_retired: list = []      # outgrown scratch buffers, kept alive for CUDA graphs that hold their address
 
 
 def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
@@ -219,7 +223,9 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
                                                         _c_int(splits))
         scratch = _attention_scratch.get(qkv.device)
         if scratch is None or scratch.numel() < need:
-            scratch = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=qkv.device)
+            if scratch is not None:
+                _retired.append(scratch)
+            scratch = torch.empty(max(need, 1 << 23), dtype=torch.float32, device=qkv.device)
             _attention_scratch[qkv.device] = scratch
         _call("attention_decode", "llmb_attention_decode", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),

@@ -31,6 +31,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 
 _loaded: dict = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 def _nvcc() -> str:
@@ -63,16 +64,25 @@ def _build_dirs() -> list:
     return dirs
 
 
+_chosen_dir = None
+
+
 def _writable_dir() -> Path:
-    for d in _build_dirs():
-        try:
-            d.mkdir(parents=True, exist_ok=True)
-            probe = d / f".probe-{os.getpid()}"
-            probe.write_bytes(b"")
-            probe.unlink()
-            return d
-        except OSError:
-            continue
+    """The first build folder that can be written, found once per process."""
+    global _chosen_dir
+    with _dir_lock:
+        if _chosen_dir is not None:
+            return _chosen_dir
+        for d in _build_dirs():
+            try:
+                d.mkdir(parents=True, exist_ok=True)
+                probe = d / f".probe-{os.getpid()}-{threading.get_ident()}"
+                probe.write_bytes(b"")
+                probe.unlink()
+                _chosen_dir = d
+                return d
+            except OSError:
+                continue
     raise KernelError("no writable folder for the compiled CUDA libraries")
 
 

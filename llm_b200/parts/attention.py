@@ -15,7 +15,8 @@ class AttentionMixer(Mixer):
     projection added to the residual stream in its epilogue: the dense attention
     of MythEclipse/llm (apps/engine/src/model.rs:930-1040), with the sizes, the
     scale, the window, the biases and the position encoding as parameters."""
-    libraries = ("elementwise", "gemm_simt", "attention_generic")
+    graph_safe = True
+    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "attention_generic", "attention_decode")
 
     def __init__(self, spec):
         self.spec = spec

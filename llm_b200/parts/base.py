@@ -34,7 +34,7 @@ class StepContext:
     tok_seq: torch.Tensor          # [T] index in the batch of each token's sequence
     cu_seqlens: torch.Tensor       # [B + 1] first packed token of each sequence
     seq_lens: torch.Tensor         # [B] length of each sequence after this step
-    slot_ids: torch.Tensor         # [B] cache slot of each sequence (int64, for indexing state)
+    slot_ids: torch.Tensor         # [B] cache slot of each sequence
     block_tables: list             # per cache group: [B, width] physical pages
     cache: object                  # the PagedCache
     decode: bool                   # every sequence brings exactly one token
@@ -49,6 +49,10 @@ class Part:
 
     #: names of the csrc files whose kernels this part launches
     libraries: tuple = ()
+    #: True if `forward` only launches work on the current stream and reads every
+    #: per-step value from the context's device tensors, so that a decode step
+    #: can be captured in a CUDA graph and replayed
+    graph_safe: bool = False
 
     def parameters(self) -> dict:
         """tensor name -> ParamSpec of everything this part binds."""

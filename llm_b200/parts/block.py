@@ -21,6 +21,10 @@ class PreNormBlock(Block):
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
 
     @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
+    @property
     def libraries(self):
         return tuple(lib for p in self.parts for lib in p.libraries)
 

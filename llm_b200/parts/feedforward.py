@@ -12,7 +12,8 @@ from .base import FeedForward, register_feed_forward, to_run_dtype
 class GatedMlp(FeedForward):
     """down(silu(gate h) * (up h)) added to the residual stream, gate and up as
     one matrix product (apps/engine/src/model.rs:1180-1216 of MythEclipse/llm)."""
-    libraries = ("elementwise", "gemm_simt")
+    graph_safe = True
+    libraries = ("elementwise", "gemm_simt", "gemm_skinny")
 
     def __init__(self, spec):
         if spec.activation != "silu":

@@ -9,6 +9,7 @@ from .base import Norm, register_norm, to_float32
 class RmsNorm(Norm):
     """x / sqrt(mean(x^2) + eps) * weight, the norm of MythEclipse/llm
     (apps/engine/src/ops.rs:4-12). The weight is held in 32-bit."""
+    graph_safe = True
     libraries = ("elementwise",)
 
     def __init__(self, spec):

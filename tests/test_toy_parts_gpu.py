@@ -49,11 +49,12 @@ def define_toy():
             state = ctx.cache.state_view(entry)
             at = 0
             for b, n in enumerate(ctx.new_counts):
-                s = state[ctx.slot_ids[b]].clone()
+                slot = int(ctx.slot_ids[b])
+                s = state[slot].clone()
                 for t in range(at, at + n):
                     s = self.spec.decay * s + h[t].float()
                     residual[t] += s @ self.w.T
-                state[ctx.slot_ids[b]] = s
+                state[slot] = s
                 at += n
 
     register_mixer("toy_decay", DecayMixer)
