@@ -125,6 +125,7 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=8192)
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-prefill", action="store_true")
     parser.add_argument("--e2e-context", type=int, default=None,
                         help="context of the run through the entry point (default: --context)")
     parser.add_argument("--dtype", default="bfloat16")
@@ -202,35 +203,40 @@ def main() -> int:
     main_run = time_decode(args.batch, args.context, args.steps, args.warmup)
 
     # prefill of 2,048 tokens, one sequence, logits at the last place
-    n_prefill = 2048
-    engine = Engine(model, max_tokens=n_prefill + 64, max_seq_len=n_prefill + 64, max_slots=1)
-    prompt = torch.randint(0, config.vocab_size, (n_prefill,),
-                           generator=torch.Generator().manual_seed(1)).tolist()
-    times = []
-    for k in range(3 + 3):
-        (slot,) = engine.acquire()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        begin.record()
-        engine.step([Entry(slot, prompt, [n_prefill - 1])])
-        end.record()
-        torch.cuda.synchronize()
-        if k >= 3:
-            times.append(begin.elapsed_time(end))
-        engine.release([slot])
-    prefill_ms = sum(times) / len(times)
     c = config
-    linear_flops = 2 * n_prefill * args.layers * (
-        c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
-        + c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
-    attention_flops = 2 * n_prefill * n_prefill * c.head_dim * c.num_attention_heads * args.layers
-    head_flops = 2 * c.hidden_size * c.vocab_size
-    prefill_flops = linear_flops + attention_flops + head_flops
-    prefill = {"value": round(n_prefill * 1e3 / prefill_ms, 1), "tokens": n_prefill,
-               "ms": round(prefill_ms, 3),
-               "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
-    del engine
-    torch.cuda.empty_cache()
+
+    def time_prefill(n_prefill=2048, repeats=3):
+        engine = Engine(model, max_tokens=n_prefill + 64, max_seq_len=n_prefill + 64, max_slots=1)
+        prompt = torch.randint(0, config.vocab_size, (n_prefill,),
+                               generator=torch.Generator().manual_seed(1)).tolist()
+        times = []
+        for k in range(3 + repeats):
+            (slot,) = engine.acquire()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record()
+            engine.step([Entry(slot, prompt, [n_prefill - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            if k >= 3:
+                times.append(begin.elapsed_time(end))
+            engine.release([slot])
+        prefill_ms = sum(times) / len(times)
+        linear_flops = 2 * n_prefill * args.layers * (
+            c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+            + c.num_attention_heads * c.head_dim * c.hidden_size
+            + 3 * c.hidden_size * c.intermediate_size)
+        # causal: every query sees half of the keys on average
+        attention_flops = 2 * n_prefill * n_prefill * c.head_dim * c.num_attention_heads * args.layers
+        head_flops = 2 * c.hidden_size * c.vocab_size
+        flops = linear_flops + attention_flops + head_flops
+        del engine
+        torch.cuda.empty_cache()
+        return {"value": round(n_prefill * 1e3 / prefill_ms, 1), "tokens": n_prefill,
+                "ms": round(prefill_ms, 3),
+                "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+
+    prefill = None if args.no_prefill else time_prefill()
 
     points = {}
     if not args.no_points:

@@ -11,6 +11,7 @@ top of what earlier steps left in the cache.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -68,6 +69,7 @@ class Engine:
         self.vocab = model.spec.vocab
         self.steps_run = 0
         self.use_graphs = (use_graphs and self.device.type == "cuda"
+                           and os.environ.get("LLMB_NO_GRAPHS", "0") in ("", "0")
                            and getattr(model, "graph_safe", lambda: False)())
         self._graphs, self._graph_seen, self._graph_pool = {}, {}, None
         self._ring, self._ring_at = [(None, None)] * 4, 0
