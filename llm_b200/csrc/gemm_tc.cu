@@ -1,0 +1,507 @@
+// C = A . B^T on the fifth-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, operands staged in shared memory by TMA.
+//
+// A is [rows_a, K] and B is [rows_b, K], both bfloat16 with K contiguous (the
+// row-major [out, in] weights of MythEclipse/llm, apps/engine/src/tensor.rs:14,91,
+// and activations [tokens, K]). One block computes a 128 x BN tile of
+// D[a_row, b_row] = sum_k A[a_row, k] B[b_row, k]. It replaces the mma.sync prompt
+// kernel q8_matmul_mma (apps/engine/kernels/gpu.cu:907-1212): the tile loop,
+// the token tile running fastest over the grid so that a weight tile is reused
+// from L2 (gpu.cu:942-966) and the bias/residual epilogue (gpu.cu:1194-1209)
+// are kept, the machinery is Blackwell's:
+//
+// * warp 0, one lane: TMA producer. Per k-block of 64 it waits for a free
+//   stage, arms the stage's mbarrier with the byte count and issues two
+//   cp.async.bulk.tensor.2d loads (128-byte swizzle), A rows and B rows.
+// * warp 1: allocates BN columns of tensor memory; one lane issues four
+//   tcgen05.mma (M 128, N BN, K 16) per k-block from shared-memory descriptors,
+//   then tcgen05.commit frees the stage; a last commit signals the epilogue.
+// * warps 2-5: epilogue. Each reads its 32 lanes of the accumulator with
+//   tcgen05.ld, adds the bias, and stores bfloat16 or 32-bit, or adds into the
+//   32-bit residual stream.
+//
+// Two orientations share the kernel. `swap == 0` (prefill): A = activations,
+// B = weights, D[token, out] is stored row by row. `swap == 1` (decode, few
+// tokens): A = weights, B = activations, so that the 128-row side of the
+// instruction is filled by weight rows and the tokens are the narrow N side
+// (16 to 64); D[out, token] is stored transposed. For decode the k-blocks are
+// split over `splits` blocks per tile so that a product with few output tiles
+// still fills 148 SMs: each block writes its partial tile to scratch, and the
+// block that arrives last at the tile's counter adds the partials in split
+// order and runs the epilogue (the counter returns to zero).
+//
+// Every wait on an mbarrier is bounded by a clock limit. A wait that runs out
+// sets a status word that the host can read, raises the block's abort flag so
+// that every role leaves its loop, and the block still frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+using namespace llmb;
+
+LLMB_DEFINE_LAST_ERROR(llmb_gemm_tc)
+
+namespace {
+
+constexpr int BM = 128;             // rows of A per tile = lanes of tensor memory
+constexpr int BK = 64;              // k-values per stage: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;        // producer warp, mma warp, four epilogue warps
+constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: false if the block is aborting or the limit ran out (then the
+// abort flag and the status word are set).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+    long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - start > WAIT_CYCLES) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate),
+          "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (64 bfloat16) with the 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                  // leading byte offset (unused with a swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                  // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
+    return d;
+}
+
+struct Epilogue {
+    const float* bias;       // indexed by the output column n
+    void* out;               // [tokens, ldo]
+    float* residual;         // [tokens, ldo] 32-bit, added into
+    int out_is_bf16;
+    int ldo;
+    int tokens, outs;        // valid tokens and output columns
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               Epilogue ep, int swap, int n_kblocks, int kblocks_per_split, int splits,
+               float* __restrict__ partials, unsigned* __restrict__ counters, int* status, int stages) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    // 1024-byte alignment of every tile is required by the 128-byte swizzle
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_tiles = base;
+    unsigned char* b_tiles = base + (size_t)stages * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_tiles + (size_t)stages * B_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + stages;
+    uint64_t* tmem_full_bar = bars + 2 * stages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    int kb_begin = split * kblocks_per_split;
+    int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
+    int my_kblocks = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(tmem_full_bar), 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < my_kblocks; ++i) {
+                int s = i % stages;
+                uint32_t round = (uint32_t)(i / stages);
+                if (!mbar_wait(smem_u32(&empty_bar[s]), (round & 1) ^ 1, abort_flag, status, 1)) break;
+                uint32_t bar = smem_u32(&full_bar[s]);
+                mbar_expect_tx(bar, A_BYTES + B_BYTES);
+                int k = (kb_begin + i) * BK;
+                tma_load_2d(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a, bar, k, tile_a * BM);
+                tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, k, tile_b * BN);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D 32-bit, A and B bfloat16, both K-major, N = BN, M = 128
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < my_kblocks && ok; ++i) {
+                int s = i % stages;
+                uint32_t round = (uint32_t)(i / stages);
+                ok = mbar_wait(smem_u32(&full_bar[s]), round & 1, abort_flag, status, 2);
+                if (!ok) break;
+                tcgen05_fence_after();
+                uint64_t a_desc = smem_desc(smem_u32(a_tiles + (size_t)s * A_BYTES));
+                uint64_t b_desc = smem_desc(smem_u32(b_tiles + (size_t)s * B_BYTES));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 k-values = 32 bytes further inside the swizzled row: +2 in 16-byte units
+                    tcgen05_mma(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(smem_u32(&empty_bar[s]));
+            }
+            if (ok) tcgen05_commit(smem_u32(tmem_full_bar));
+        }
+    } else {
+        int quarter = warp & 3;                          // the 32 lanes of tensor memory this warp may read
+        int row = quarter * 32 + lane;                   // row of the tile = row of A
+        bool ok = my_kblocks > 0 ? mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, status, 3) : true;
+        tcgen05_fence_after();
+        uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        int a_row = tile_a * BM + row;                   // swap: output column; else: token
+        if (ok && splits > 1) {
+            // partial tile [BN columns][128 rows] of this split
+            size_t tile_id = (size_t)tile_b * gridDim.x + tile_a;
+            float* mine = partials + (tile_id * splits + split) * (size_t)(BN * BM);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                if (my_kblocks > 0) tmem_ld16(taddr + c, r);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    __stcg(mine + (size_t)(c + j) * BM + row, my_kblocks > 0 ? __uint_as_float(r[j]) : 0.f);
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
+            if (threadIdx.x == 64) {
+                unsigned arrived = atomicAdd(&counters[tile_id], 1u);
+                *last_flag = arrived == (unsigned)(splits - 1);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            ok = *last_flag != 0;
+            if (ok) __threadfence();
+        }
+        if (ok) {
+            size_t tile_id = (size_t)tile_b * gridDim.x + tile_a;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v[16];
+                if (splits > 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    for (int s = 0; s < splits; ++s) {
+                        const float* theirs = partials + (tile_id * splits + s) * (size_t)(BN * BM);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] += __ldcg(theirs + (size_t)(c + j) * BM + row);
+                    }
+                } else {
+                    uint32_t r[16];
+                    tmem_ld16(taddr + c, r);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                }
+                if (swap) {
+                    // D[out column a_row, token b]: one token at a time, lanes along the output row
+                    if (a_row < ep.outs) {
+                        float b = ep.bias ? ep.bias[a_row] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            int token = tile_b * BN + c + j;
+                            if (token >= ep.tokens) break;
+                            size_t at = (size_t)token * ep.ldo + a_row;
+                            float value = v[j] + b;
+                            if (ep.residual) ep.residual[at] += value;
+                            else if (ep.out_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(value);
+                            else reinterpret_cast<float*>(ep.out)[at] = value;
+                        }
+                    }
+                } else if (a_row < ep.tokens) {
+                    // D[token a_row, out column]: 16 consecutive columns of this thread's row
+                    int n0 = tile_b * BN + c;
+                    size_t at = (size_t)a_row * ep.ldo + n0;
+                    bool whole = n0 + 16 <= ep.outs;
+                    if (ep.bias) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) v[j] += ep.bias[n0 + j];
+                    }
+                    if (ep.residual) {
+                        if (whole && (ep.ldo & 3) == 0) {
+                            float4* p = reinterpret_cast<float4*>(ep.residual + at);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                float4 old = p[j];
+                                old.x += v[4 * j]; old.y += v[4 * j + 1]; old.z += v[4 * j + 2]; old.w += v[4 * j + 3];
+                                p[j] = old;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) ep.residual[at + j] += v[j];
+                        }
+                    } else if (ep.out_is_bf16) {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + at;
+                        if (whole && (ep.ldo & 7) == 0) {
+                            uint4 packed[2];
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            reinterpret_cast<uint4*>(o)[0] = packed[0];
+                            reinterpret_cast<uint4*>(o)[1] = packed[1];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) o[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    } else {
+                        float* o = reinterpret_cast<float*>(ep.out) + at;
+                        if (whole && (ep.ldo & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                reinterpret_cast<float4*>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) o[j] = v[j];
+                        }
+                    }
+                }
+            }
+            if (splits > 1 && threadIdx.x == 64) counters[tile_id] = 0u;
+        }
+    }
+
+    // teardown: everyone meets, then the allocating warp frees the tensor memory
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // let copies that are still in flight land before shared memory is given up
+        for (int i = 0; i < 100; ++i) __nanosleep(10000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiled>(p);
+    return fn;
+}
+
+// rows x K bfloat16, K contiguous with `ld` elements between rows; box 64 x box_rows, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long k, long long ld, int box_rows) {
+    EncodeTiled encode = encode_fn();
+    if (!encode) return fail(LLMB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                        box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LLMB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return LLMB_OK;
+}
+
+int* status_word() {
+    static int* host = nullptr;
+    if (!host) {
+        if (cudaHostAlloc(&host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return nullptr;
+        *host = 0;
+    }
+    return host;
+}
+
+template <int BN>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& ep, int swap,
+           int tiles_a, int tiles_b, int n_kblocks, int per_split, int splits, float* partials,
+           unsigned* counters, cudaStream_t stream) {
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    int stages = (200 * 1024) / (A_BYTES + B_BYTES);
+    if (stages > 8) stages = 8;
+    if (swap && stages > 6) stages = 6;                 // two blocks per SM for the decode stream
+    size_t smem = 1024 + (size_t)stages * (A_BYTES + B_BYTES) + (2 * stages + 1) * 8 + 16;
+    static size_t configured = 0;
+    if (smem > configured) {
+        LLMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    int* status = status_word();
+    int* status_dev = nullptr;
+    if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
+    dim3 grid(tiles_a, tiles_b, splits);
+    gemm_tc_kernel<BN><<<grid, THREADS, smem, stream>>>(map_a, map_b, ep, swap, n_kblocks, per_split, splits,
+                                                        partials, counters, status_dev, stages);
+    return check_launch("gemm_tc");
+}
+
+struct Plan {
+    int swap, bn, tiles_a, tiles_b, n_kblocks, per_split, splits;
+};
+
+Plan make_plan(int M, int N, int K) {
+    Plan p;
+    p.n_kblocks = (K + BK - 1) / BK;
+    p.swap = M <= 64;
+    if (p.swap) {
+        p.bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+        p.tiles_a = (N + BM - 1) / BM;
+        p.tiles_b = 1;
+        int want = (2 * 148 + p.tiles_a - 1) / p.tiles_a;     // two blocks per SM
+        int most = p.n_kblocks / 4 > 0 ? p.n_kblocks / 4 : 1; // at least four k-blocks a block
+        if (want > most) want = most;
+        if (want > 32) want = 32;
+        if (want < 1) want = 1;
+        p.per_split = (p.n_kblocks + want - 1) / want;
+        p.splits = (p.n_kblocks + p.per_split - 1) / p.per_split;
+    } else {
+        p.bn = N >= 256 ? 256 : N > 64 ? 128 : 64;
+        p.tiles_a = (M + BM - 1) / BM;
+        p.tiles_b = (N + p.bn - 1) / p.bn;
+        p.per_split = p.n_kblocks;
+        p.splits = 1;
+    }
+    return p;
+}
+
+}  // namespace
+
+// 0 if nothing went wrong since the last call of this function; else the code of the
+// wait that ran out (1 producer, 2 mma, 3 epilogue). Call after a synchronisation.
+LLMB_EXPORT int llmb_gemm_tc_status() {
+    int* s = status_word();
+    if (!s) return -1;
+    int v = *s;
+    *s = 0;
+    return v;
+}
+
+// Floats of partial-sum scratch and counters a call needs (0 when it does not split K).
+LLMB_EXPORT long long llmb_gemm_tc_scratch_floats(int M, int N, int K) {
+    Plan p = make_plan(M, N, K);
+    return p.splits > 1 ? (long long)p.tiles_a * p.tiles_b * p.splits * p.bn * BM : 0;
+}
+LLMB_EXPORT int llmb_gemm_tc_counters(int M, int N, int K) {
+    Plan p = make_plan(M, N, K);
+    return p.tiles_a * p.tiles_b;
+}
+
+// out[M, N] = x[M, K] . w[N, K]^T (+ bias[N]); or residual[M, N] += the same.
+LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
+                             int out_dtype, float* residual, float* partials, long long partial_floats,
+                             unsigned* counters, int n_counters, int M, int N, int K, int ldo,
+                             cudaStream_t stream) {
+    if (M == 0 || N == 0) return LLMB_OK;
+    LLMB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes");
+    LLMB_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
+                 "gemm_tc: K %d and the row stride %d must be multiples of 8 (TMA strides of 16 bytes)", K, ldx);
+    LLMB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                 "gemm_tc: operands must be 16-byte aligned");
+    LLMB_REQUIRE((out != nullptr) != (residual != nullptr), "gemm_tc: give out or residual");
+    LLMB_REQUIRE(residual || out_dtype == LLMB_DTYPE_BF16 || out_dtype == LLMB_DTYPE_F32,
+                 "gemm_tc: unknown output dtype %d", out_dtype);
+    LLMB_REQUIRE(ldo >= N, "gemm_tc: bad output stride");
+    Plan p = make_plan(M, N, K);
+    LLMB_REQUIRE(p.tiles_a <= 2147483647 && p.tiles_b <= 65535 && p.splits <= 65535, "gemm_tc: grid too large");
+    if (p.splits > 1) {
+        LLMB_REQUIRE(partials && counters && partial_floats >= llmb_gemm_tc_scratch_floats(M, N, K) &&
+                     n_counters >= p.tiles_a * p.tiles_b, "gemm_tc: scratch is missing or too small");
+    }
+    CUtensorMap map_a, map_b;
+    int code;
+    if (p.swap) {
+        if ((code = make_map(&map_a, w, N, K, K, BM))) return code;
+        if ((code = make_map(&map_b, x, M, K, ldx, p.bn))) return code;
+    } else {
+        if ((code = make_map(&map_a, x, M, K, ldx, BM))) return code;
+        if ((code = make_map(&map_b, w, N, K, K, p.bn))) return code;
+    }
+    Epilogue ep{bias, out, residual, out_dtype == LLMB_DTYPE_BF16, ldo, M, N};
+#define GO(BN) return launch<BN>(map_a, map_b, ep, p.swap, p.tiles_a, p.tiles_b, p.n_kblocks, \
+                                 p.per_split, p.splits, partials, counters, stream)
+    switch (p.bn) {
+        case 16: GO(16);
+        case 32: GO(32);
+        case 64: GO(64);
+        case 128: GO(128);
+        default: GO(256);
+    }
+#undef GO
+}

@@ -44,7 +44,7 @@ class DecoderModel:
         return out
 
     def libraries(self) -> list:
-        names = ["elementwise", "gemm_simt"]
+        names = ["elementwise", "gemm_simt", "gemm_skinny", "gemm_tc"]
         for block in self.blocks:
             names += list(block.libraries)
         names += list(self.final_norm.libraries)

@@ -129,24 +129,41 @@ _scratch: dict = {}
 _retired: list = []      # outgrown scratch buffers, kept alive for CUDA graphs that hold their address
 
 
-def _skinny_scratch(device, m, n, k):
-    """Partial sums and tile counters of the split-K decode product, one pair per
+def _split_scratch(device, floats: int, counters: int):
+    """Partial sums and tile counters of the split-K products, one pair per
     device, shared by every call on the stream (calls run one after the other).
-    It grows when a call needs more; it never shrinks."""
+    It grows when a call needs more; an outgrown pair is kept alive because a
+    captured step may still hold its address."""
+    held = _scratch.get(device)
+    if held is None or held[0].numel() < floats or held[1].numel() < counters:
+        n_floats = max(floats, held[0].numel() if held else 0, 1 << 23)
+        n_counters = max(counters, held[1].numel() if held else 0, 1 << 14)
+        if held is not None:
+            _retired.append(held)
+        held = (torch.empty(n_floats, dtype=torch.float32, device=device),
+                torch.zeros(n_counters, dtype=torch.int32, device=device))
+        _scratch[device] = held
+    return held
+
+
+def _skinny_scratch(device, m, n, k):
     lib = load_library("gemm_skinny")
     lib.llmb_gemm_skinny_scratch_bytes.restype = ctypes.c_longlong
     need = lib.llmb_gemm_skinny_scratch_bytes(_c_int(m), _c_int(n), _c_int(k))
-    tiles = (n + 15) // 16
-    held = _scratch.get(device)
-    if held is None or held[0].numel() * 4 < need or held[1].numel() < tiles:
-        floats = max(need // 4, held[0].numel() if held else 0, 1 << 23)
-        count = max(tiles, held[1].numel() if held else 0, 1 << 14)
-        if held is not None:
-            _retired.append(held)       # a captured step may still point at it
-        held = (torch.empty(floats, dtype=torch.float32, device=device),
-                torch.zeros(count, dtype=torch.int32, device=device))
-        _scratch[device] = held
-    return held
+    return _split_scratch(device, need // 4, (n + 15) // 16)
+
+
+def _tc_scratch(device, m, n, k):
+    lib = load_library("gemm_tc")
+    lib.llmb_gemm_tc_scratch_floats.restype = ctypes.c_longlong
+    floats = lib.llmb_gemm_tc_scratch_floats(_c_int(m), _c_int(n), _c_int(k))
+    return _split_scratch(device, floats, lib.llmb_gemm_tc_counters(_c_int(m), _c_int(n), _c_int(k)))
+
+
+def tensor_core_status() -> int:
+    """0, or the code of a bounded wait that ran out in a tcgen05 kernel since the
+    last call (1 producer, 2 mma issuer, 3 epilogue). Call after a synchronisation."""
+    return load_library("gemm_tc").llmb_gemm_tc_status()
 
 
 def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
@@ -166,8 +183,16 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
     else:
         target_dtype = out_dtype or a.dtype
         result = out if out is not None else torch.empty((m, n), dtype=target_dtype, device=a.device)
-    variant = tactics.choose_linear(m, n, k, a.dtype, target_dtype, a.stride(0))
-    if variant == "gemm_skinny":
+    variant = tactics.choose_linear(m, n, k, a.dtype, target_dtype, a.stride(0),
+                                    a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+    if variant == "gemm_tc":
+        partials, counters = _tc_scratch(a.device, m, n, k)
+        _call("gemm_tc", "llmb_gemm_tc", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),
+              _ptr(result if residual is None else None), _c_int(_code(target_dtype)),
+              _ptr(residual), _ptr(partials), ctypes.c_longlong(partials.numel()),
+              _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k), _c_int(n),
+              _stream())
+    elif variant == "gemm_skinny":
         partials, counters = _skinny_scratch(a.device, m, n, k)
         _call("gemm_skinny", "llmb_gemm_skinny", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),
               _ptr(result if residual is None else None), _c_int(_code(target_dtype)),
@@ -273,10 +298,10 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 
 def required_libraries() -> list:
     """Names of the kernel files the decoder parts of this package use."""
-    return ["elementwise", "gemm_simt", "gemm_skinny", "attention_generic", "attention_decode",
-            "sampling"]
+    return ["elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic",
+            "attention_decode", "sampling"]
 
 
 __all__ = ["PAGE", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
-           "argmax_rows", "sample_rows", "launch_count", "count_launches", "ensure_built", "load_library", "all_sources",
+           "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

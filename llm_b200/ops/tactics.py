@@ -27,17 +27,33 @@ def _always(**_):
     return None
 
 
-def _skinny_guard(m, n, k, in_dtype, out_dtype, lda, **_):
+def _skinny_guard(m, n, k, in_dtype, out_dtype, lda, aligned=True, **_):
     if in_dtype != torch.bfloat16:
         return "bfloat16 operands only"
     if m > 64:
         return f"{m} rows exceed 64"
     if k % 8 or lda % 8:
         return f"K {k} or the row stride {lda} is no multiple of 8 elements (16-byte loads)"
+    if not aligned:
+        return "an operand does not start on a 16-byte boundary"
+    return None
+
+
+def _tc_guard(m, n, k, in_dtype, out_dtype, lda, aligned=True, **_):
+    if in_dtype != torch.bfloat16:
+        return "bfloat16 operands only"
+    if k % 8 or lda % 8:
+        return (f"K {k} or the row stride {lda} is no multiple of 8 elements: a TMA row stride "
+                "must be a multiple of 16 bytes")
+    if not aligned:
+        return "an operand does not start on a 16-byte boundary (TMA base address)"
     return None
 
 
 LINEAR = [
+    Tactic("gemm_tc", 30, _tc_guard,
+           "tcgen05.mma with the accumulator in tensor memory, operands by TMA; weights on the "
+           "128-row side and split K for up to 64 tokens, tokens on it above"),
     Tactic("gemm_skinny", 20, _skinny_guard,
            "decode product for up to 64 rows: W streamed once with 128-bit loads into "
            "mma.sync fragments, K split over warps with an ordered last-arriver sum"),
@@ -94,8 +110,9 @@ def _choose(table, **shape):
     return best.name, reasons
 
 
-def choose_linear(m, n, k, in_dtype, out_dtype, lda) -> str:
-    return _choose(LINEAR, m=m, n=n, k=k, in_dtype=in_dtype, out_dtype=out_dtype, lda=lda)[0]
+def choose_linear(m, n, k, in_dtype, out_dtype, lda, aligned=True) -> str:
+    return _choose(LINEAR, m=m, n=n, k=k, in_dtype=in_dtype, out_dtype=out_dtype, lda=lda,
+                   aligned=aligned)[0]
 
 
 def choose_attention(decode, dtype, n_heads, n_kv_heads, head_dim, window) -> str:

@@ -13,7 +13,7 @@ class GatedMlp(FeedForward):
     """down(silu(gate h) * (up h)) added to the residual stream, gate and up as
     one matrix product (apps/engine/src/model.rs:1180-1216 of MythEclipse/llm)."""
     graph_safe = True
-    libraries = ("elementwise", "gemm_simt", "gemm_skinny")
+    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc")
 
     def __init__(self, spec):
         if spec.activation != "silu":

@@ -79,11 +79,23 @@ def test_linear(dtype, m, n, k):
 @pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (8, 6144, 4096), (8, 1000, 200), (5, 72, 1032),
                                    (16, 4096, 14336), (17, 100, 1024), (33, 520, 2048),
                                    (64, 4100, 4096)])
-def test_linear_decode_kernel(m, n, k):
-    """The split-K decode product: sizes with one and many splits, tails in N, K and M,
-    called twice so that the tile counters must have been left at zero."""
+@pytest.mark.parametrize("variant", ["gemm_skinny", "gemm_tc"])
+def test_linear_decode_kernel(m, n, k, variant):
+    """The split-K decode products (mma.sync and tcgen05): sizes with one and many
+    splits, tails in N, K and M, called twice so that the tile counters must have
+    been left at zero."""
     from llm_b200.ops import tactics
-    assert tactics.choose_linear(m, n, k, torch.bfloat16, torch.bfloat16, k) == "gemm_skinny"
+    if variant == "gemm_skinny":
+        tactics.disable("gemm_tc")
+    try:
+        assert tactics.choose_linear(m, n, k, torch.bfloat16, torch.bfloat16, k) == variant
+        _check_decode_product(m, n, k)
+        assert ops().tensor_core_status() == 0
+    finally:
+        tactics.enable("gemm_tc")
+
+
+def _check_decode_product(m, n, k):
     a = randn(m, k, dtype=torch.bfloat16, seed=80)
     w = randn(n, k, dtype=torch.bfloat16, seed=81, scale=0.05)
     bias = randn(n, seed=82)
@@ -101,6 +113,35 @@ def test_linear_decode_kernel(m, n, k):
     # the same rows alone and in the batch: the same split and order, bit-equal
     alone = ops().linear(a[:1].contiguous(), w, bias, out_dtype=torch.float32)
     assert torch.equal(alone[0], got[0])
+
+
+@pytest.mark.parametrize("m,n,k", [(65, 256, 64), (128, 128, 128), (129, 300, 200), (200, 1000, 520),
+                                   (513, 6144, 4096), (2048, 4096, 1024), (70, 72, 72),
+                                   (300, 4104, 2048)])
+def test_linear_tensor_core_kernel(m, n, k):
+    """tcgen05 product with tokens on the 128-row side: tile edges in M, N and K."""
+    from llm_b200.ops import tactics
+    assert tactics.choose_linear(m, n, k, torch.bfloat16, torch.bfloat16, k) == "gemm_tc"
+    a = randn(m, k, dtype=torch.bfloat16, seed=84)
+    w = randn(n, k, dtype=torch.bfloat16, seed=85, scale=0.05)
+    bias = randn(n, seed=86)
+    want = plain_ops.linear(a, w, bias, out_dtype=torch.float32)
+    scale = float(want.abs().max())
+    got = ops().linear(a, w, bias, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert ops().tensor_core_status() == 0
+    assert float((got - want).abs().max()) <= 2e-3 * scale
+    got16 = ops().linear(a, w, bias)
+    assert float((got16.float() - want).abs().max()) <= 1e-2 * scale
+    residual = randn(m, n, seed=87)
+    expect = residual + want
+    ops().linear(a, w, bias, residual=residual)
+    assert float((residual - expect).abs().max()) <= 2e-3 * scale
+    # a strided view as input (the query part of a fused projection)
+    wide = randn(m, k + 64, dtype=torch.bfloat16, seed=88)
+    view = wide[:, :k]
+    got = ops().linear(view, w, out_dtype=torch.float32)
+    assert float((got - plain_ops.linear(view, w, out_dtype=torch.float32)).abs().max()) <= 2e-3 * scale
 
 
 def test_linear_rows_do_not_depend_on_the_batch():
