@@ -41,17 +41,38 @@ LLMB_EXPORT int llmb_embed(const int* tokens, const void* table, int table_dtype
 // (apps/engine/src/ops.rs:4-12, apps/engine/kernels/gpu.cu:266-316). One block per
 // row; the sum of squares is 32-bit and is reduced in a fixed order, so a row's
 // result does not depend on the batch it is in. `rows` (optional) gathers rows.
-template <typename TOut>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
-                               const int* __restrict__ rows, TOut* __restrict__ out,
-                               int hidden, float eps) {
+template <typename TOut, int PER_THREAD>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+               const int* __restrict__ rows, TOut* __restrict__ out, int hidden, float eps) {
+    // PER_THREAD > 0: hidden is a multiple of 4 and at most 1024 * PER_THREAD; every thread
+    // keeps its PER_THREAD float4 of the row in registers (all loads in flight at once).
+    // PER_THREAD == 0: any width, the row is read twice.
     int r = blockIdx.x;
     int src = rows ? rows[r] : r;
     const float* in = x + (size_t)src * hidden;
     float sum = 0.f;
-    for (int e = threadIdx.x; e < hidden; e += blockDim.x) {
-        float v = in[e];
-        sum = fmaf(v, v, sum);
+    float4 held[PER_THREAD > 0 ? PER_THREAD : 1];
+    if (PER_THREAD > 0) {
+        int quads = hidden >> 2;
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            int q = threadIdx.x + i * 256;
+            held[i] = q < quads ? reinterpret_cast<const float4*>(in)[q] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        // the same order of additions for every row: element order inside a thread
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            sum = fmaf(held[i].x, held[i].x, sum);
+            sum = fmaf(held[i].y, held[i].y, sum);
+            sum = fmaf(held[i].z, held[i].z, sum);
+            sum = fmaf(held[i].w, held[i].w, sum);
+        }
+    } else {
+        for (int e = threadIdx.x; e < hidden; e += blockDim.x) {
+            float v = in[e];
+            sum = fmaf(v, v, sum);
+        }
     }
     __shared__ float partial[32];
     __shared__ float scale_shared;
@@ -68,8 +89,35 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     __syncthreads();
     float scale = scale_shared;
     TOut* o = out + (size_t)r * hidden;
-    for (int e = threadIdx.x; e < hidden; e += blockDim.x)
-        o[e] = from_float<TOut>(in[e] * scale * gain[e]);
+    if (PER_THREAD > 0) {
+        int quads = hidden >> 2;
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            int q = threadIdx.x + i * 256;
+            if (q >= quads) continue;
+            float4 g = reinterpret_cast<const float4*>(gain)[q];
+            float4 v = held[i];
+            o[4 * q] = from_float<TOut>(v.x * scale * g.x);
+            o[4 * q + 1] = from_float<TOut>(v.y * scale * g.y);
+            o[4 * q + 2] = from_float<TOut>(v.z * scale * g.z);
+            o[4 * q + 3] = from_float<TOut>(v.w * scale * g.w);
+        }
+    } else {
+        for (int e = threadIdx.x; e < hidden; e += blockDim.x)
+            o[e] = from_float<TOut>(in[e] * scale * gain[e]);
+    }
+}
+
+template <typename TOut>
+static void launch_rmsnorm(const float* x, const float* gain, const int* rows, TOut* out, int n_rows,
+                           int hidden, float eps, cudaStream_t stream) {
+    bool vector = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(gain) & 15) == 0;
+    if (vector && hidden <= 1024) rmsnorm_kernel<TOut, 1><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
+    else if (vector && hidden <= 2048) rmsnorm_kernel<TOut, 2><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
+    else if (vector && hidden <= 4096) rmsnorm_kernel<TOut, 4><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
+    else if (vector && hidden <= 8192) rmsnorm_kernel<TOut, 8><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
+    else rmsnorm_kernel<TOut, 0><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
 }
 
 LLMB_EXPORT int llmb_rmsnorm(const float* x, const float* gain, const int* rows, void* out,
@@ -78,9 +126,9 @@ LLMB_EXPORT int llmb_rmsnorm(const float* x, const float* gain, const int* rows,
     if (n_rows == 0) return LLMB_OK;
     LLMB_REQUIRE(n_rows > 0 && hidden > 0, "rmsnorm: bad sizes");
     if (out_dtype == LLMB_DTYPE_F32)
-        rmsnorm_kernel<float><<<n_rows, 256, 0, stream>>>(x, gain, rows, (float*)out, hidden, eps);
+        launch_rmsnorm<float>(x, gain, rows, (float*)out, n_rows, hidden, eps, stream);
     else if (out_dtype == LLMB_DTYPE_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>(x, gain, rows, (__nv_bfloat16*)out, hidden, eps);
+        launch_rmsnorm<__nv_bfloat16>(x, gain, rows, (__nv_bfloat16*)out, n_rows, hidden, eps, stream);
     else
         return fail(LLMB_ERR_ARGUMENT, "rmsnorm: unknown dtype %d", out_dtype);
     return check_launch("rmsnorm");

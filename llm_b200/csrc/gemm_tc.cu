@@ -252,12 +252,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c = 0; c < BN; c += 16) {
                 float v[16];
                 if (splits > 1) {
+                    // partials are added in split order; four splits' loads are in flight at once
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                    for (int s = 0; s < splits; ++s) {
-                        const float* theirs = partials + (tile_id * splits + s) * (size_t)(BN * BM);
+                    const float* first = partials + tile_id * splits * (size_t)(BN * BM) + (size_t)c * BM + row;
+                    for (int s0 = 0; s0 < splits; s0 += 4) {
+                        float t[4][16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] += __ldcg(theirs + (size_t)(c + j) * BM + row);
+                        for (int i = 0; i < 4; ++i) {
+                            bool live = s0 + i < splits;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                t[i][j] = live ? __ldcg(first + (size_t)(s0 + i) * (BN * BM) + (size_t)j * BM) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] += t[i][j];
                     }
                 } else {
                     uint32_t r[16];
@@ -396,7 +407,10 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     int stages = (200 * 1024) / (A_BYTES + B_BYTES);
     if (stages > 8) stages = 8;
-    if (swap && stages > 6) stages = 6;                 // two blocks per SM for the decode stream
+    if (swap) {                                         // two blocks per SM for the decode stream
+        stages = (110 * 1024) / (A_BYTES + B_BYTES);
+        if (stages > 6) stages = 6;
+    }
     size_t smem = 1024 + (size_t)stages * (A_BYTES + B_BYTES) + (2 * stages + 1) * 8 + 16;
     static size_t configured = 0;
     if (smem > configured) {
@@ -424,7 +438,9 @@ Plan make_plan(int M, int N, int K) {
         p.bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
         p.tiles_a = (N + BM - 1) / BM;
         p.tiles_b = 1;
-        int want = (2 * 148 + p.tiles_a - 1) / p.tiles_a;     // two blocks per SM
+        // all blocks resident at once (two per SM): a second, partly filled wave would
+        // double the time of a product this short
+        int want = (2 * 148) / p.tiles_a;
         int most = p.n_kblocks / 4 > 0 ? p.n_kblocks / 4 : 1; // at least four k-blocks a block
         if (want > most) want = most;
         if (want > 32) want = 32;

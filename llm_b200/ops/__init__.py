@@ -231,7 +231,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
-              max_len=0):
+              max_len=0, cu_seqlens=None, max_new=0):
     """Causal grouped-query attention of the new tokens' queries (the first
     Hq * D columns of `qkv`) over the paged cache, which already holds the new
     tokens' keys and values. Returns [T, Hq * D] in qkv's dtype."""
@@ -239,8 +239,15 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     n = qkv.shape[0]
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window)
-    if variant == "attention_decode":
+    variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window,
+                                       cu_seqlens is not None and seq_lens is not None)
+    if variant == "attention_prefill":
+        _call("attention_prefill", "llmb_attention_prefill", _ptr(qkv), _c_int(qkv.stride(0)),
+              _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
+              _c_int(ring_pages), _ptr(cu_seqlens), _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)),
+              _c_int(cu_seqlens.numel() - 1), _c_int(max_new), _c_int(n_heads), _c_int(n_kv_heads),
+              _c_int(head_dim), _c_float(scale), _c_int(window), _stream())
+    elif variant == "attention_decode":
         splits = decode_splits(n, n_kv_heads, max_len)
         lib = load_library("attention_decode")
         lib.llmb_attention_decode_scratch_floats.restype = ctypes.c_longlong
@@ -299,7 +306,7 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 def required_libraries() -> list:
     """Names of the kernel files the decoder parts of this package use."""
     return ["elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic",
-            "attention_decode", "sampling"]
+            "attention_decode", "attention_prefill", "sampling"]
 
 
 __all__ = ["PAGE", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",

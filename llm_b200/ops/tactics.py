@@ -76,7 +76,22 @@ def _decode_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, **_):
     return None
 
 
+def _prefill_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed=False, **_):
+    if not packed:
+        return "needs the packed batch description (cu_seqlens and seq_lens)"
+    if dtype != torch.bfloat16:
+        return "bfloat16 caches only"
+    if window:
+        return "no window"
+    if head_dim not in (32, 64, 96, 128):
+        return f"head_dim {head_dim} (served: 32, 64, 96, 128)"
+    return None
+
+
 ATTENTION = [
+    Tactic("attention_prefill", 10, _prefill_guard,
+           "flash attention over the paged cache for steps with several new tokens a sequence: "
+           "64-query tiles, mma.sync, online softmax, heaviest tile first"),
     Tactic("attention_decode", 20, _decode_guard,
            "split-KV decode attention: pages through shared memory with cp.async, the query "
            "heads of a group as rows of mma.sync tiles, partials merged by a second kernel"),
@@ -115,9 +130,9 @@ def choose_linear(m, n, k, in_dtype, out_dtype, lda, aligned=True) -> str:
                    aligned=aligned)[0]
 
 
-def choose_attention(decode, dtype, n_heads, n_kv_heads, head_dim, window) -> str:
+def choose_attention(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed=False) -> str:
     return _choose(ATTENTION, decode=decode, dtype=dtype, n_heads=n_heads, n_kv_heads=n_kv_heads,
-                   head_dim=head_dim, window=window)[0]
+                   head_dim=head_dim, window=window, packed=packed)[0]
 
 
 def explain(family: str, **shape) -> str:

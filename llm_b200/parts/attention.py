@@ -16,7 +16,7 @@ class AttentionMixer(Mixer):
     of MythEclipse/llm (apps/engine/src/model.rs:930-1040), with the sizes, the
     scale, the window, the biases and the position encoding as parameters."""
     graph_safe = True
-    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic", "attention_decode")
+    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic", "attention_decode", "attention_prefill")
 
     def __init__(self, spec):
         self.spec = spec
@@ -72,7 +72,8 @@ class AttentionMixer(Mixer):
             write_cache=(entry == cache_entry))
         mixed = ops.attention(qkv, keys, values, table, ring, ctx.tok_pos, ctx.tok_seq, s.n_heads,
                               s.n_kv_heads, s.head_dim, s.scale, s.window, decode=ctx.decode,
-                              seq_lens=ctx.seq_lens, max_len=ctx.max_len)
+                              seq_lens=ctx.seq_lens, max_len=ctx.max_len,
+                              cu_seqlens=ctx.cu_seqlens, max_new=max(ctx.new_counts))
         ops.linear(mixed, self.w_o, self.b_o, residual=residual)
 
 

@@ -267,6 +267,32 @@ def test_attention_decode_kernel_long_contexts(heads, kv_heads, dim):
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim", [(8, 2, 128), (4, 1, 64), (6, 2, 96), (4, 4, 32),
+                                                (3, 1, 128)])
+def test_attention_prefill_kernel(heads, kv_heads, dim):
+    """The flash prefill kernel: sequences that start at position 0 and sequences that
+    continue (chunked prompts), lengths around tile and page edges, one batch."""
+    from llm_b200.ops import tactics
+    dtype = torch.bfloat16
+    assert tactics.choose_attention(False, dtype, heads, kv_heads, dim, 0, True) == "attention_prefill"
+    starts, counts = [0, 0, 100, 64, 0, 300], [300, 1, 65, 64, 63, 130]
+    lens = [s + c for s, c in zip(starts, counts)]
+    table, width, k_cache, v_cache = make_cache(len(lens), lens, kv_heads, dim, dtype, 93)
+    fill_cache(table, width, k_cache, v_cache, lens, 94)
+    tok_pos = torch.tensor([p for s, c in zip(starts, counts) for p in range(s, s + c)],
+                           dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([b for b, c in enumerate(counts) for _ in range(c)], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    q = randn(tok_pos.numel(), (heads + 2 * kv_heads) * dim, dtype=dtype, seed=95)
+    want = plain_ops.attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads,
+                               dim, dim ** -0.5)
+    got = ops().attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads, dim,
+                          dim ** -0.5, 0, seq_lens=seq_lens, max_len=max(lens), cu_seqlens=cu,
+                          max_new=max(counts))
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(dtype):
     """Among 500 keys one early key matches the query; the output must be its
