@@ -233,3 +233,53 @@ LLMB_EXPORT int llmb_gemm_skinny(const void* x, int ldx, const void* w, const fl
 #undef LAUNCH
     return check_launch("gemm_skinny");
 }
+
+// ------------------------------------------------------------------------- no allocation
+// llmb_gemm_skinny_static (declared and described in gemm_skinny_static.h): the same
+// product with its scratch in this library's own device memory instead of buffers
+// the caller allocates.
+#include "gemm_skinny_static.h"
+
+static __device__ __align__(256) float static_partials[LLMB_GEMM_SKINNY_STATIC_FLOATS];
+static __device__ __align__(256) unsigned static_counters[LLMB_GEMM_SKINNY_STATIC_COUNTERS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* static_partials_at[MAX_DEVICES] = {nullptr};      // device addresses, found once per device
+unsigned* static_counters_at[MAX_DEVICES] = {nullptr};
+}  // namespace
+
+LLMB_EXPORT int llmb_gemm_skinny_static(const void* x, int ldx, const void* w, const float* bias,
+                                        void* out, int out_dtype, float* residual, int M, int N,
+                                        int K, int ldo, cudaStream_t stream) {
+    if (M == 0 || N == 0) return LLMB_OK;
+    LLMB_REQUIRE(M > 0 && M <= 64 && N > 0 && K > 0, "gemm_skinny_static: bad sizes");
+    long long need = llmb_gemm_skinny_scratch_bytes(M, N, K);
+    int row_tiles = (N + 15) / 16;
+    LLMB_REQUIRE(need <= (long long)LLMB_GEMM_SKINNY_STATIC_FLOATS * 4,
+                 "gemm_skinny_static: %d x %d x %d needs %lld bytes of partial sums, the built-in "
+                 "scratch holds %lld; use llmb_gemm_skinny with scratch of your own",
+                 M, N, K, need, (long long)LLMB_GEMM_SKINNY_STATIC_FLOATS * 4);
+    LLMB_REQUIRE(row_tiles <= LLMB_GEMM_SKINNY_STATIC_COUNTERS,
+                 "gemm_skinny_static: %d output rows need %d tile counters, the built-in scratch "
+                 "holds %d", N, row_tiles, LLMB_GEMM_SKINNY_STATIC_COUNTERS);
+    int device = 0;
+    LLMB_CUDA(cudaGetDevice(&device));
+    LLMB_REQUIRE(device >= 0 && device < MAX_DEVICES, "gemm_skinny_static: device %d", device);
+    if (static_partials_at[device] == nullptr) {
+        // Set-up, once per device, with that device current. In host code the names of the
+        // arrays are host-side stand-ins, not device addresses: ask the runtime for the
+        // addresses and hand those to the kernel.
+        float* partials = nullptr;
+        unsigned* counters = nullptr;
+        LLMB_CUDA(cudaGetSymbolAddress((void**)&partials, static_partials));
+        LLMB_CUDA(cudaGetSymbolAddress((void**)&counters, static_counters));
+        // the counters must start at zero (every call leaves them at zero again)
+        LLMB_CUDA(cudaMemsetAsync(counters, 0, sizeof(unsigned) * LLMB_GEMM_SKINNY_STATIC_COUNTERS, stream));
+        static_counters_at[device] = counters;
+        static_partials_at[device] = partials;
+    }
+    return llmb_gemm_skinny(x, ldx, w, bias, out, out_dtype, residual, static_partials_at[device],
+                            (long long)LLMB_GEMM_SKINNY_STATIC_FLOATS * 4, static_counters_at[device],
+                            LLMB_GEMM_SKINNY_STATIC_COUNTERS, M, N, K, ldo, stream);
+}
