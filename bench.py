@@ -25,15 +25,6 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-LLAMA_8B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 32,
-    "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
-    "intermediate_size": 14336, "vocab_size": 128256, "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
-                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
-    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "attention_bias": False,
-    "max_position_embeddings": 131072, "hidden_act": "silu",
-}
 FULL_LAYERS = 32
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -147,7 +138,8 @@ def main() -> int:
     torch.cuda.set_device(0)
     device = "cuda:0"
     dtype = parse_dtype(args.dtype)
-    raw = dict(LLAMA_8B, num_hidden_layers=args.layers)
+    from llm_b200.shapes import shape
+    raw = shape("llama-3.1-8b", args.layers)
     config = config_from_dict(raw)
     peak, peak_source = peaks()
     model = random_model(config, seed=0, dtype=dtype, device=device)

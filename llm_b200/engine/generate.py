@@ -119,6 +119,7 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
                 if not live:
                     break
             tokens = sampler.sample(logits, live).tolist()      # one small device-to-host copy
+            engine.check()
             now = time.perf_counter()
             if prefill_done is None:
                 prefill_done = now

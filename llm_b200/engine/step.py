@@ -86,6 +86,10 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def check(self) -> None:
+        """After a synchronisation: raise if a kernel reported a failed wait."""
+        ops.check_device_status()
+
     # ------------------------------------------------------------------ the step
 
     def step(self, entries) -> torch.Tensor:

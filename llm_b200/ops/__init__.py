@@ -166,6 +166,18 @@ def tensor_core_status() -> int:
     return load_library("gemm_tc").llmb_gemm_tc_status()
 
 
+def check_device_status() -> None:
+    """Raise if a kernel of a loaded library reported a wait that ran out. Cheap (it
+    reads a word of host memory); meaningful after the stream was synchronised."""
+    from .build import _loaded
+    if "gemm_tc" in _loaded:
+        code = _loaded["gemm_tc"].llmb_gemm_tc_status()
+        if code != 0:
+            role = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, str(code))
+            raise KernelError(f"gemm_tc: a bounded wait of the {role} ran out; the results of the "
+                              "last steps are not valid")
+
+
 def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
     """a [M, K] . w [N, K]^T (+ bias [N], float32). With `residual` (float32
     [M, N]) the product is added to it in place and it is returned; otherwise a
@@ -310,5 +322,5 @@ def required_libraries() -> list:
 
 
 __all__ = ["PAGE", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
-           "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "ensure_built", "load_library", "all_sources",
+           "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

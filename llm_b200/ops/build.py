@@ -127,6 +127,12 @@ def compile_library(name: str) -> Path:
             pass
         raise KernelError(f"nvcc failed on {source.name}:\n{output}")
     os.replace(scratch, target)
+    for stale in out_dir.glob(f"llmb_{name}-*.so"):      # earlier builds of this source
+        if stale != target:
+            try:
+                stale.unlink()
+            except OSError:
+                pass
     _say(f"built {target.name} in {time.time() - started:.1f} s")
     return target
 

@@ -209,3 +209,4 @@ def install(monkeypatch):
     for name, fn in OPS.items():
         monkeypatch.setattr(ops, name, fn)
     monkeypatch.setattr(ops, "ensure_built", lambda names: None)
+    monkeypatch.setattr(ops, "check_device_status", lambda: None)
