@@ -30,6 +30,11 @@
 // block that arrives last at the tile's counter adds the partials in split
 // order and runs the epilogue (the counter returns to zero).
 //
+// The kernel is persistent: at most as many blocks as the GPU holds at once, each taking
+// work units (an output tile and one slice of its k-blocks) round robin. The operand ring
+// and two accumulator buffers in tensor memory carry on from unit to unit, so the loads and
+// products of the next unit run under the epilogue of the last.
+//
 // Every wait on an mbarrier is bounded by a clock limit. A wait that runs out
 // sets a status word that the host can read, raises the block's abort flag so
 // that every role leaves its loop, and the block still frees its tensor memory.
@@ -57,6 +62,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
@@ -134,39 +142,126 @@ struct Epilogue {
     int tokens, outs;        // valid tokens and output columns
 };
 
+// One work unit: output tile (tile_a, tile_b) and one slice of its k-blocks.
+struct Unit {
+    int tile_a, tile_b, split;
+};
+__device__ __forceinline__ Unit unit_of(int u, int tiles_a, int splits) {
+    Unit w;
+    w.split = u % splits;
+    int t = u / splits;
+    w.tile_a = t % tiles_a;            // the A tile runs fastest: neighbours share a B tile in L2
+    w.tile_b = t / tiles_a;
+    return w;
+}
+
+// Stores 16 consecutive accumulator columns (c .. c+15) of this thread's row.
+template <int BN>
+__device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int a_row, int tile_b,
+                                              int c, float (&v)[16]) {
+    if (swap) {
+        // D[out column a_row, token]: one token at a time, lanes along the output row
+        if (a_row >= ep.outs) return;
+        float b = ep.bias ? ep.bias[a_row] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            int token = tile_b * BN + c + j;
+            if (token >= ep.tokens) break;
+            size_t at = (size_t)token * ep.ldo + a_row;
+            float value = v[j] + b;
+            if (ep.residual) ep.residual[at] += value;
+            else if (ep.out_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(value);
+            else reinterpret_cast<float*>(ep.out)[at] = value;
+        }
+        return;
+    }
+    if (a_row >= ep.tokens) return;
+    // D[token a_row, out column]: 16 consecutive columns of this thread's row
+    int n0 = tile_b * BN + c;
+    if (n0 >= ep.outs) return;
+    size_t at = (size_t)a_row * ep.ldo + n0;
+    bool whole = n0 + 16 <= ep.outs;
+    if (ep.bias) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) v[j] += ep.bias[n0 + j];
+    }
+    if (ep.residual) {
+        if (whole && (ep.ldo & 3) == 0) {
+            float4* p = reinterpret_cast<float4*>(ep.residual + at);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float4 old = p[j];
+                old.x += v[4 * j]; old.y += v[4 * j + 1]; old.z += v[4 * j + 2]; old.w += v[4 * j + 3];
+                p[j] = old;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) ep.residual[at + j] += v[j];
+        }
+    } else if (ep.out_is_bf16) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + at;
+        if (whole && (ep.ldo & 7) == 0) {
+            uint4 packed[2];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            reinterpret_cast<uint4*>(o)[0] = packed[0];
+            reinterpret_cast<uint4*>(o)[1] = packed[1];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) o[j] = __float2bfloat16_rn(v[j]);
+        }
+    } else {
+        float* o = reinterpret_cast<float*>(ep.out) + at;
+        if (whole && (ep.ldo & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                reinterpret_cast<float4*>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) o[j] = v[j];
+        }
+    }
+}
+
+// Persistent: the grid has at most as many blocks as fit on the GPU at once, and block b
+// takes the units b, b + gridDim.x, ... . The shared-memory ring and the two accumulator
+// buffers in tensor memory run on across units, so the loads and products of the next unit
+// overlap the epilogue of this one.
 template <int BN>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               Epilogue ep, int swap, int n_kblocks, int kblocks_per_split, int splits,
-               float* __restrict__ partials, unsigned* __restrict__ counters, int* status, int stages) {
+               Epilogue ep, int swap, int n_kblocks, int kblocks_per_split, int splits, int tiles_a,
+               int n_units, float* __restrict__ partials, unsigned* __restrict__ counters,
+               int* status, int stages) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulator buffers
     // 1024-byte alignment of every tile is required by the 128-byte swizzle
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* a_tiles = base;
     unsigned char* b_tiles = base + (size_t)stages * A_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(b_tiles + (size_t)stages * B_BYTES);
-    uint64_t* full_bar = bars;
-    uint64_t* empty_bar = bars + stages;
-    uint64_t* tmem_full_bar = bars + 2 * stages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 1);
+    uint64_t* full_bar = bars;                         // [stages] operands landed
+    uint64_t* empty_bar = bars + stages;               // [stages] operands consumed
+    uint64_t* acc_full_bar = bars + 2 * stages;        // [2] accumulator complete
+    uint64_t* acc_empty_bar = bars + 2 * stages + 2;   // [2] accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+    volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
-    int kb_begin = split * kblocks_per_split;
-    int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
-    int my_kblocks = kb_end - kb_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(tmem_full_bar), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full_bar[b]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[b]), 4);          // one arrival per epilogue warp
+        }
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -183,15 +278,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < my_kblocks; ++i) {
-                int s = i % stages;
-                uint32_t round = (uint32_t)(i / stages);
-                if (!mbar_wait(smem_u32(&empty_bar[s]), (round & 1) ^ 1, abort_flag, status, 1)) break;
-                uint32_t bar = smem_u32(&full_bar[s]);
-                mbar_expect_tx(bar, A_BYTES + B_BYTES);
-                int k = (kb_begin + i) * BK;
-                tma_load_2d(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a, bar, k, tile_a * BM);
-                tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, k, tile_b * BN);
+            uint32_t it = 0;                                    // k-blocks issued so far, over all units
+            bool ok = true;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                Unit w = unit_of(u, tiles_a, splits);
+                int kb_begin = w.split * kblocks_per_split;
+                int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                    int s = it % stages;
+                    uint32_t round = it / stages;
+                    ok = mbar_wait(smem_u32(&empty_bar[s]), (round & 1) ^ 1, abort_flag, status, 1);
+                    if (!ok) break;
+                    uint32_t bar = smem_u32(&full_bar[s]);
+                    mbar_expect_tx(bar, A_BYTES + B_BYTES);
+                    tma_load_2d(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a, bar, kb * BK, w.tile_a * BM);
+                    tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, kb * BK, w.tile_b * BN);
+                }
             }
         }
     } else if (warp == 1) {
@@ -199,43 +301,79 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // instruction descriptor: D 32-bit, A and B bfloat16, both K-major, N = BN, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, n_done = 0;
             bool ok = true;
-            for (int i = 0; i < my_kblocks && ok; ++i) {
-                int s = i % stages;
-                uint32_t round = (uint32_t)(i / stages);
-                ok = mbar_wait(smem_u32(&full_bar[s]), round & 1, abort_flag, status, 2);
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++n_done) {
+                Unit w = unit_of(u, tiles_a, splits);
+                int kb_begin = w.split * kblocks_per_split;
+                int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
+                uint32_t buffer = n_done & 1, use = n_done >> 1;
+                // the epilogue must have drained this buffer (its previous use)
+                ok = mbar_wait(smem_u32(&acc_empty_bar[buffer]), (use & 1) ^ 1, abort_flag, status, 4);
                 if (!ok) break;
                 tcgen05_fence_after();
-                uint64_t a_desc = smem_desc(smem_u32(a_tiles + (size_t)s * A_BYTES));
-                uint64_t b_desc = smem_desc(smem_u32(b_tiles + (size_t)s * B_BYTES));
+                uint32_t d_tmem = tmem_base + buffer * BN;
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                    int s = it % stages;
+                    uint32_t round = it / stages;
+                    ok = mbar_wait(smem_u32(&full_bar[s]), round & 1, abort_flag, status, 2);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    uint64_t a_desc = smem_desc(smem_u32(a_tiles + (size_t)s * A_BYTES));
+                    uint64_t b_desc = smem_desc(smem_u32(b_tiles + (size_t)s * B_BYTES));
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 k-values = 32 bytes further inside the swizzled row: +2 in 16-byte units
-                    tcgen05_mma(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 k-values = 32 bytes further inside the swizzled row: +2 in 16-byte units
+                        tcgen05_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                    (kb > kb_begin || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(smem_u32(&empty_bar[s]));
                 }
-                tcgen05_commit(smem_u32(&empty_bar[s]));
+                if (ok) tcgen05_commit(smem_u32(&acc_full_bar[buffer]));
             }
-            if (ok) tcgen05_commit(smem_u32(tmem_full_bar));
         }
     } else {
         int quarter = warp & 3;                          // the 32 lanes of tensor memory this warp may read
         int row = quarter * 32 + lane;                   // row of the tile = row of A
-        bool ok = my_kblocks > 0 ? mbar_wait(smem_u32(tmem_full_bar), 0, abort_flag, status, 3) : true;
-        tcgen05_fence_after();
-        uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        int a_row = tile_a * BM + row;                   // swap: output column; else: token
-        if (ok && splits > 1) {
-            // partial tile [BN columns][128 rows] of this split
-            size_t tile_id = (size_t)tile_b * gridDim.x + tile_a;
-            float* mine = partials + (tile_id * splits + split) * (size_t)(BN * BM);
+        uint32_t n_done = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++n_done) {
+            Unit w = unit_of(u, tiles_a, splits);
+            uint32_t buffer = n_done & 1, use = n_done >> 1;
+            ok = mbar_wait(smem_u32(&acc_full_bar[buffer]), use & 1, abort_flag, status, 3);
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * BN;
+            int a_row = w.tile_a * BM + row;             // swap: output column; else: token
+            size_t tile_id = (size_t)w.tile_b * tiles_a + w.tile_a;
+            if (splits == 1) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t r[16];
+                    float v[16];
+                    tmem_ld16(taddr + c, r);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                    store_columns<BN>(ep, swap, a_row, w.tile_b, c, v);
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buffer]));
+                continue;
+            }
+            // split K: park the partial tile [BN columns][128 rows], free the accumulator, and
+            // let the block that arrives last add all partials in split order
+            float* mine = partials + (tile_id * splits + w.split) * (size_t)(BN * BM);
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 uint32_t r[16];
-                if (my_kblocks > 0) tmem_ld16(taddr + c, r);
+                tmem_ld16(taddr + c, r);
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    __stcg(mine + (size_t)(c + j) * BM + row, my_kblocks > 0 ? __uint_as_float(r[j]) : 0.f);
+                for (int j = 0; j < 16; ++j) __stcg(mine + (size_t)(c + j) * BM + row, __uint_as_float(r[j]));
             }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buffer]));
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
             if (threadIdx.x == 64) {
@@ -243,103 +381,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 *last_flag = arrived == (unsigned)(splits - 1);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            ok = *last_flag != 0;
-            if (ok) __threadfence();
-        }
-        if (ok) {
-            size_t tile_id = (size_t)tile_b * gridDim.x + tile_a;
+            bool last = *last_flag != 0;     // the flag is next written after the next unit's first barrier
+            if (!last) continue;
+            __threadfence();
+            const float* first = partials + tile_id * splits * (size_t)(BN * BM) + row;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v[16];
-                if (splits > 1) {
-                    // partials are added in split order; four splits' loads are in flight at once
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                    const float* first = partials + tile_id * splits * (size_t)(BN * BM) + (size_t)c * BM + row;
-                    for (int s0 = 0; s0 < splits; s0 += 4) {
-                        float t[4][16];
+                for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                // partials are added in split order; four splits' loads are in flight at once
+                for (int s0 = 0; s0 < splits; s0 += 4) {
+                    float t[4][16];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            bool live = s0 + i < splits;
+                    for (int i = 0; i < 4; ++i) {
+                        bool live = s0 + i < splits;
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                t[i][j] = live ? __ldcg(first + (size_t)(s0 + i) * (BN * BM) + (size_t)j * BM) : 0.f;
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] += t[i][j];
+                        for (int j = 0; j < 16; ++j)
+                            t[i][j] = live ? __ldcg(first + (size_t)(s0 + i) * (BN * BM) + (size_t)(c + j) * BM) : 0.f;
                     }
-                } else {
-                    uint32_t r[16];
-                    tmem_ld16(taddr + c, r);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] += t[i][j];
                 }
-                if (swap) {
-                    // D[out column a_row, token b]: one token at a time, lanes along the output row
-                    if (a_row < ep.outs) {
-                        float b = ep.bias ? ep.bias[a_row] : 0.f;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            int token = tile_b * BN + c + j;
-                            if (token >= ep.tokens) break;
-                            size_t at = (size_t)token * ep.ldo + a_row;
-                            float value = v[j] + b;
-                            if (ep.residual) ep.residual[at] += value;
-                            else if (ep.out_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(value);
-                            else reinterpret_cast<float*>(ep.out)[at] = value;
-                        }
-                    }
-                } else if (a_row < ep.tokens) {
-                    // D[token a_row, out column]: 16 consecutive columns of this thread's row
-                    int n0 = tile_b * BN + c;
-                    size_t at = (size_t)a_row * ep.ldo + n0;
-                    bool whole = n0 + 16 <= ep.outs;
-                    if (ep.bias) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) v[j] += ep.bias[n0 + j];
-                    }
-                    if (ep.residual) {
-                        if (whole && (ep.ldo & 3) == 0) {
-                            float4* p = reinterpret_cast<float4*>(ep.residual + at);
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                float4 old = p[j];
-                                old.x += v[4 * j]; old.y += v[4 * j + 1]; old.z += v[4 * j + 2]; old.w += v[4 * j + 3];
-                                p[j] = old;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) ep.residual[at + j] += v[j];
-                        }
-                    } else if (ep.out_is_bf16) {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out) + at;
-                        if (whole && (ep.ldo & 7) == 0) {
-                            uint4 packed[2];
-                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(packed);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                            reinterpret_cast<uint4*>(o)[0] = packed[0];
-                            reinterpret_cast<uint4*>(o)[1] = packed[1];
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) o[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    } else {
-                        float* o = reinterpret_cast<float*>(ep.out) + at;
-                        if (whole && (ep.ldo & 3) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                reinterpret_cast<float4*>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) if (n0 + j < ep.outs) o[j] = v[j];
-                        }
-                    }
-                }
+                store_columns<BN>(ep, swap, a_row, w.tile_b, c, v);
             }
-            if (splits > 1 && threadIdx.x == 64) counters[tile_id] = 0u;
+            if (threadIdx.x == 64) counters[tile_id] = 0u;
         }
     }
 
@@ -407,22 +475,31 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     int stages = (200 * 1024) / (A_BYTES + B_BYTES);
     if (stages > 8) stages = 8;
+    int blocks_per_sm = 1;
     if (swap) {                                         // two blocks per SM for the decode stream
         stages = (110 * 1024) / (A_BYTES + B_BYTES);
         if (stages > 6) stages = 6;
+        blocks_per_sm = 2;
     }
-    size_t smem = 1024 + (size_t)stages * (A_BYTES + B_BYTES) + (2 * stages + 1) * 8 + 16;
+    size_t smem = 1024 + (size_t)stages * (A_BYTES + B_BYTES) + (2 * stages + 4) * 8 + 16;
     static size_t configured = 0;
     if (smem > configured) {
         LLMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int device = 0;
+        LLMB_CUDA(cudaGetDevice(&device));
+        LLMB_CUDA(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device));
+    }
     int* status = status_word();
     int* status_dev = nullptr;
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
-    dim3 grid(tiles_a, tiles_b, splits);
+    int n_units = tiles_a * tiles_b * splits;
+    int grid = n_units < n_sms * blocks_per_sm ? n_units : n_sms * blocks_per_sm;
     gemm_tc_kernel<BN><<<grid, THREADS, smem, stream>>>(map_a, map_b, ep, swap, n_kblocks, per_split, splits,
-                                                        partials, counters, status_dev, stages);
+                                                        tiles_a, n_units, partials, counters, status_dev, stages);
     return check_launch("gemm_tc");
 }
 
@@ -495,7 +572,7 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
                  "gemm_tc: unknown output dtype %d", out_dtype);
     LLMB_REQUIRE(ldo >= N, "gemm_tc: bad output stride");
     Plan p = make_plan(M, N, K);
-    LLMB_REQUIRE(p.tiles_a <= 2147483647 && p.tiles_b <= 65535 && p.splits <= 65535, "gemm_tc: grid too large");
+    LLMB_REQUIRE((long long)p.tiles_a * p.tiles_b * p.splits < (1ll << 30), "gemm_tc: too many tiles");
     if (p.splits > 1) {
         LLMB_REQUIRE(partials && counters && partial_floats >= llmb_gemm_tc_scratch_floats(M, N, K) &&
                      n_counters >= p.tiles_a * p.tiles_b, "gemm_tc: scratch is missing or too small");
