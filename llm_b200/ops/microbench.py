@@ -1,0 +1,158 @@
+"""Time one kernel of the library alone, at a given shape.
+
+    python -m llm_b200.ops.microbench linear --m 8 --n 6144 --k 4096 [--variant gemm_skinny]
+    python -m llm_b200.ops.microbench attention_decode --batch 8 --context 8192
+    python -m llm_b200.ops.microbench attention_prefill --tokens 2048
+    python -m llm_b200.ops.microbench rmsnorm --m 8 --k 4096
+
+Each call is timed inside a CUDA graph of `--reps` back-to-back launches (so that
+the host's launch cost is not in the number), with CUDA events, after warm-up.
+Weights rotate over enough copies to exceed L2, so every launch streams from
+HBM. `--once` runs a single plain launch after warm-up instead (for a profiler).
+Default sizes are those of a Llama-3.1-8B layer. The per-kernel table that
+MythEclipse/llm prints with LLM_PROFILE=1 (apps/engine/src/cuda/mod.rs:1917-1972)
+is the precedent; this tool isolates one kernel instead of wrapping every launch.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+from . import attention, linear, rmsnorm, rope_cache_write, swiglu, tactics
+
+DEV = "cuda:0"
+
+
+def time_in_graph(fn, reps: int, rounds: int = 10) -> float:
+    """Microseconds per call of fn, from `rounds` replays of a graph of `reps` calls."""
+    fn()
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(rounds):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / (rounds * reps) * 1e3
+
+
+def run(fn, args, work_bytes=0.0, work_flops=0.0, label=""):
+    if args.once:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        fn()
+        torch.cuda.synchronize()
+        print(f"{label}: one launch done")
+        return
+    us = time_in_graph(fn, args.reps)
+    line = f"{label}: {us:.1f} us"
+    if work_bytes:
+        line += f", {work_bytes / us / 1e6:.2f} TB/s"
+    if work_flops:
+        line += f", {work_flops / us / 1e6:.1f} TFLOP/s"
+    print(line)
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    p.add_argument("op", choices=["linear", "attention_decode", "attention_prefill", "rmsnorm",
+                                  "swiglu", "rope"])
+    p.add_argument("--m", type=int, default=8, help="rows (tokens)")
+    p.add_argument("--n", type=int, default=6144)
+    p.add_argument("--k", type=int, default=4096)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=8192)
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--heads", type=int, default=32)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--variant", default=None, help="force a kernel variant by disabling higher ranks")
+    p.add_argument("--residual", action="store_true", help="linear: add into a 32-bit residual")
+    p.add_argument("--reps", type=int, default=20)
+    p.add_argument("--once", action="store_true")
+    args = p.parse_args(argv)
+    torch.manual_seed(0)
+    bf16 = torch.bfloat16
+
+    if args.op == "linear":
+        if args.variant:
+            for row in tactics.LINEAR:
+                if row.name != args.variant and row.rank > [r for r in tactics.LINEAR if r.name == args.variant][0].rank:
+                    tactics.disable(row.name)
+        m, n, k = args.m, args.n, args.k
+        copies = 1 if args.once else max(2, int(300e6 / (n * k * 2)) + 1)
+        ws = [torch.randn(n, k, device=DEV, dtype=bf16) * 0.02 for _ in range(copies)]
+        x = torch.randn(m, k, device=DEV, dtype=bf16)
+        res = torch.zeros(m, n, device=DEV, dtype=torch.float32) if args.residual else None
+        out = None if args.residual else torch.empty(m, n, device=DEV, dtype=bf16)
+        turn = [0]
+
+        def fn():
+            linear(x, ws[turn[0] % copies], residual=res, out=out)
+            turn[0] += 1
+        args.reps = max(args.reps, copies * 2) if not args.once else args.reps
+        name = tactics.choose_linear(m, n, k, bf16, bf16, k)
+        run(fn, args, n * k * 2, 2.0 * m * n * k, f"linear {name} M={m} N={n} K={k}")
+    elif args.op in ("attention_decode", "attention_prefill"):
+        hq, hkv, d = args.heads, args.kv_heads, args.head_dim
+        decode = args.op == "attention_decode"
+        batch = args.batch if decode else 1
+        ctx = args.context if decode else args.tokens
+        pages_per = (ctx + 63) // 64
+        n_pages = batch * pages_per
+        kc = torch.randn(n_pages, hkv, 64, d, device=DEV, dtype=bf16)
+        vc = torch.randn(n_pages, hkv, 64, d, device=DEV, dtype=bf16)
+        table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(batch, pages_per)
+        lens = torch.full((batch,), ctx, dtype=torch.int32, device=DEV)
+        if decode:
+            qkv = torch.randn(batch, (hq + 2 * hkv) * d, device=DEV, dtype=bf16)
+            pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=DEV)
+            seq = torch.arange(batch, dtype=torch.int32, device=DEV)
+            fn = lambda: attention(qkv, kc, vc, table, pages_per, pos, seq, hq, hkv, d, d ** -0.5, 0,
+                                   decode=True, seq_lens=lens, max_len=ctx)
+            run(fn, args, batch * ctx * hkv * d * 2 * 2, 0.0,
+                f"attention_decode batch={batch} context={ctx} heads={hq}/{hkv} D={d}")
+        else:
+            qkv = torch.randn(ctx, (hq + 2 * hkv) * d, device=DEV, dtype=bf16)
+            pos = torch.arange(ctx, dtype=torch.int32, device=DEV)
+            seq = torch.zeros(ctx, dtype=torch.int32, device=DEV)
+            cu = torch.tensor([0, ctx], dtype=torch.int32, device=DEV)
+            fn = lambda: attention(qkv, kc, vc, table, pages_per, pos, seq, hq, hkv, d, d ** -0.5, 0,
+                                   seq_lens=lens, max_len=ctx, cu_seqlens=cu, max_new=ctx)
+            args.reps = min(args.reps, 5)
+            run(fn, args, 0.0, 2.0 * 2.0 * ctx * ctx / 2 * d * hq,
+                f"attention_prefill tokens={ctx} heads={hq}/{hkv} D={d} (causal flops)")
+    elif args.op == "rmsnorm":
+        x = torch.randn(args.m, args.k, device=DEV)
+        g = torch.ones(args.k, device=DEV)
+        run(lambda: rmsnorm(x, g, 1e-5, bf16), args, args.m * args.k * 6, 0.0, f"rmsnorm {args.m}x{args.k}")
+    elif args.op == "swiglu":
+        gu = torch.randn(args.m, 2 * args.n, device=DEV, dtype=bf16)
+        run(lambda: swiglu(gu), args, args.m * args.n * 6, 0.0, f"swiglu {args.m}x{args.n}")
+    elif args.op == "rope":
+        hq, hkv, d, b = args.heads, args.kv_heads, args.head_dim, args.batch
+        pages_per = (args.context + 63) // 64
+        kc = torch.zeros(b * pages_per, hkv, 64, d, device=DEV, dtype=bf16)
+        vc = torch.zeros_like(kc)
+        table = torch.arange(b * pages_per, dtype=torch.int32, device=DEV).view(b, pages_per)
+        qkv = torch.randn(b, (hq + 2 * hkv) * d, device=DEV, dtype=bf16)
+        pos = torch.full((b,), args.context - 1, dtype=torch.int32, device=DEV)
+        seq = torch.arange(b, dtype=torch.int32, device=DEV)
+        angles = torch.randn(args.context, d, device=DEV)
+        run(lambda: rope_cache_write(qkv, angles, pos, seq, table, pages_per, kc, vc, hq, hkv, d), args,
+            0.0, 0.0, f"rope_cache_write batch={b}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
