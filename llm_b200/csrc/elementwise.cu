@@ -14,12 +14,27 @@ LLMB_DEFINE_LAST_ERROR(llmb_elementwise)
 // (token, column)); here one block per token, columns strided over the threads.
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ x, int hidden, int vocab) {
+                             float* __restrict__ x, int hidden, int vocab, int vector) {
     int t = blockIdx.x;
     int token = tokens[t];
     if (token < 0 || token >= vocab) token = 0;   // host checks ids; device-sampled ids are in range
     const T* row = table + (size_t)token * hidden;
     float* out = x + (size_t)t * hidden;
+    if (vector) {
+        // 16 bytes of the table per load (hidden is a multiple of 16 / sizeof(T), rows are aligned)
+        constexpr int PER = 16 / sizeof(T);
+        const uint4* src = reinterpret_cast<const uint4*>(row);
+        for (int v = threadIdx.x; v < hidden / PER; v += blockDim.x) {
+            uint4 raw = src[v];
+            const T* e = reinterpret_cast<const T*>(&raw);
+            float4* dst = reinterpret_cast<float4*>(out + (size_t)v * PER);
+#pragma unroll
+            for (int q = 0; q < PER / 4; ++q)
+                dst[q] = make_float4(to_float(e[4 * q]), to_float(e[4 * q + 1]), to_float(e[4 * q + 2]),
+                                     to_float(e[4 * q + 3]));
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < hidden; e += blockDim.x) out[e] = to_float(row[e]);
 }
 
@@ -27,10 +42,13 @@ LLMB_EXPORT int llmb_embed(const int* tokens, const void* table, int table_dtype
                            int n_tokens, int hidden, int vocab, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
+    int aligned = (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     if (table_dtype == LLMB_DTYPE_F32)
-        embed_kernel<float><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, x, hidden, vocab);
+        embed_kernel<float><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, x, hidden, vocab,
+                                                         aligned && hidden % 4 == 0);
     else if (table_dtype == LLMB_DTYPE_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, hidden, vocab);
+        embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, hidden,
+                                                                 vocab, aligned && hidden % 8 == 0);
     else
         return fail(LLMB_ERR_ARGUMENT, "embed: unknown dtype %d", table_dtype);
     return check_launch("embed");

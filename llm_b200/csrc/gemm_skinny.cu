@@ -159,6 +159,28 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
             }
         if (lane == 0) counters[row_tile] = 0u;
     }
+    if (residual) {
+        // loads first, then stores: a load after a store would wait for it
+        float old[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int row = i < 2 ? row_lo : row_hi;
+                int token = n * 8 + 2 * t + (i & 1);
+                old[n][i] = (row < N && token < M) ? residual[(size_t)token * ldo + row] : 0.f;
+            }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int row = i < 2 ? row_lo : row_hi;
+                int token = n * 8 + 2 * t + (i & 1);
+                if (row < N && token < M)
+                    residual[(size_t)token * ldo + row] = old[n][i] + (acc[n][i] + (bias ? bias[row] : 0.f));
+            }
+        return;
+    }
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
@@ -168,8 +190,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
             if (row >= N || token >= M) continue;
             float v = acc[n][i] + (bias ? bias[row] : 0.f);
             size_t at = (size_t)token * ldo + row;
-            if (residual) residual[at] += v;
-            else if (out_is_bf16) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(v);
+            if (out_is_bf16) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(v);
             else reinterpret_cast<float*>(out)[at] = v;
         }
 }

@@ -163,14 +163,27 @@ __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int 
         // D[out column a_row, token]: one token at a time, lanes along the output row
         if (a_row >= ep.outs) return;
         float b = ep.bias ? ep.bias[a_row] : 0.f;
+        int first_token = tile_b * BN + c;
+        if (ep.residual) {
+            // all loads first, then all stores: a load placed after a store would have to
+            // wait for it (the compiler cannot know that the addresses differ)
+            float old[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                old[j] = first_token + j < ep.tokens ? ep.residual[(size_t)(first_token + j) * ep.ldo + a_row] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (first_token + j < ep.tokens)
+                    ep.residual[(size_t)(first_token + j) * ep.ldo + a_row] = old[j] + (v[j] + b);
+            return;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            int token = tile_b * BN + c + j;
+            int token = first_token + j;
             if (token >= ep.tokens) break;
             size_t at = (size_t)token * ep.ldo + a_row;
             float value = v[j] + b;
-            if (ep.residual) ep.residual[at] += value;
-            else if (ep.out_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(value);
+            if (ep.out_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(value);
             else reinterpret_cast<float*>(ep.out)[at] = value;
         }
         return;
@@ -188,11 +201,13 @@ __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int 
     if (ep.residual) {
         if (whole && (ep.ldo & 3) == 0) {
             float4* p = reinterpret_cast<float4*>(ep.residual + at);
+            float4 old[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) old[j] = p[j];              // loads first, then stores
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float4 old = p[j];
-                old.x += v[4 * j]; old.y += v[4 * j + 1]; old.z += v[4 * j + 2]; old.w += v[4 * j + 3];
-                p[j] = old;
+                old[j].x += v[4 * j]; old[j].y += v[4 * j + 1]; old[j].z += v[4 * j + 2]; old[j].w += v[4 * j + 3];
+                p[j] = old[j];
             }
         } else {
 #pragma unroll
