@@ -202,6 +202,81 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__
     }
 }
 
+// The same work for bfloat16 with 16-byte accesses: one block per token, every thread takes
+// items of 8 rotation pairs (two 16-byte pieces of a head) or 8 values of a v head.
+__global__ void __launch_bounds__(256)
+rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ table,
+                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                      const int* __restrict__ block_table, int table_stride, int ring_pages,
+                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                      int n_heads, int n_kv_heads, int head_dim, int interleaved, int write_cache) {
+    int t = blockIdx.x;
+    int pos = tok_pos[t];
+    int half = head_dim >> 1;
+    int items_rot = head_dim >> 4;                       // items of 8 pairs per rotated head
+    int items_copy = head_dim >> 3;                      // items of 8 values per v head
+    int n_rot_heads = n_heads + n_kv_heads;
+    int total = n_rot_heads * items_rot + (write_cache ? n_kv_heads * items_copy : 0);
+    __nv_bfloat16* row = qkv + (size_t)t * (n_heads + 2 * n_kv_heads) * head_dim;
+    size_t page_base = 0;
+    if (write_cache) {
+        int page = block_table[(size_t)tok_seq[t] * table_stride + ((pos / LLMB_PAGE) % ring_pages)];
+        page_base = (size_t)page * n_kv_heads * LLMB_PAGE * head_dim + (size_t)(pos % LLMB_PAGE) * head_dim;
+    }
+    const float* angles = table ? table + (size_t)pos * head_dim : nullptr;
+    for (int item = threadIdx.x; item < total; item += blockDim.x) {
+        if (item < n_rot_heads * items_rot) {
+            int head = item / items_rot, piece = item - head * items_rot;
+            bool is_q = head < n_heads;
+            if (!is_q && !write_cache) continue;
+            __nv_bfloat16* src = row + (size_t)head * head_dim;
+            __nv_bfloat16* dst = is_q ? src
+                                      : k_cache + page_base + (size_t)(head - n_heads) * LLMB_PAGE * head_dim;
+            int p0 = piece * 8;                           // first of this item's 8 pairs
+            int at_lo = interleaved ? 2 * p0 : p0, at_hi = interleaved ? 2 * p0 + 8 : p0 + half;
+            uint4 raw_lo = *reinterpret_cast<const uint4*>(src + at_lo);
+            uint4 raw_hi = *reinterpret_cast<const uint4*>(src + at_hi);
+            __nv_bfloat16* lo = reinterpret_cast<__nv_bfloat16*>(&raw_lo);
+            __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(&raw_hi);
+            float c[8], s[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                c[i] = angles ? angles[p0 + i] : 1.f;
+                s[i] = angles ? angles[half + p0 + i] : 0.f;
+            }
+            if (interleaved) {
+                // pair i of this item is elements (2i, 2i+1) of the 16 loaded values
+                __nv_bfloat16 all[16];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { all[i] = lo[i]; all[8 + i] = hi[i]; }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float a = __bfloat162float(all[2 * i]), b = __bfloat162float(all[2 * i + 1]);
+                    all[2 * i] = __float2bfloat16_rn(a * c[i] - b * s[i]);
+                    all[2 * i + 1] = __float2bfloat16_rn(a * s[i] + b * c[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { lo[i] = all[i]; hi[i] = all[8 + i]; }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float a = __bfloat162float(lo[i]), b = __bfloat162float(hi[i]);
+                    lo[i] = __float2bfloat16_rn(a * c[i] - b * s[i]);
+                    hi[i] = __float2bfloat16_rn(a * s[i] + b * c[i]);
+                }
+            }
+            *reinterpret_cast<uint4*>(dst + at_lo) = raw_lo;
+            *reinterpret_cast<uint4*>(dst + at_hi) = raw_hi;
+        } else {
+            int rest = item - n_rot_heads * items_rot;
+            int kv_head = rest / items_copy, piece = rest - kv_head * items_copy;
+            const __nv_bfloat16* src = row + (size_t)(n_rot_heads + kv_head) * head_dim + piece * 8;
+            __nv_bfloat16* dst = v_cache + page_base + (size_t)kv_head * LLMB_PAGE * head_dim + piece * 8;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        }
+    }
+}
+
 LLMB_EXPORT int llmb_rope_cache_write(void* qkv, int dtype, const float* table,
                                       const int* tok_pos, const int* tok_seq,
                                       const int* block_table, int table_stride, int ring_pages,
@@ -212,6 +287,15 @@ LLMB_EXPORT int llmb_rope_cache_write(void* qkv, int dtype, const float* table,
     LLMB_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "rope: head_dim %d must be even", head_dim);
     LLMB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && ring_pages > 0, "rope: bad sizes");
     LLMB_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope: too many heads");
+    if (dtype == LLMB_DTYPE_BF16 && head_dim % 16 == 0 &&
+        ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) |
+          reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0) {
+        rope_cache_vec_kernel<<<n_tokens, 256, 0, stream>>>(
+            (__nv_bfloat16*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim, interleaved,
+            write_cache);
+        return check_launch("rope_cache_write");
+    }
     dim3 grid(n_tokens, n_heads + 2 * n_kv_heads);
     int threads = head_dim / 2 >= 64 ? 64 : 32;
     if (dtype == LLMB_DTYPE_F32)
@@ -246,11 +330,42 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, lon
     }
 }
 
+// bfloat16 rows whose width is a multiple of 8: 16 bytes of gate and of up per thread and step
+__global__ void swiglu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
+                                  long long total_vectors, int vectors_per_row) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total_vectors; i += stride) {
+        long long t = i / vectors_per_row;
+        int f = (int)(i - t * vectors_per_row);
+        const uint4* row = reinterpret_cast<const uint4*>(gu + t * 2 * vectors_per_row * 8);
+        uint4 raw_g = row[f], raw_u = row[vectors_per_row + f];
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&raw_g);
+        const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&raw_u);
+        uint4 packed;
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float gate = __bfloat162float(g[j]);
+            o[j] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * __bfloat162float(u[j]));
+        }
+        reinterpret_cast<uint4*>(act)[i] = packed;
+    }
+}
+
 LLMB_EXPORT int llmb_swiglu(const void* gu, void* act, int dtype, int n_tokens, int width,
                             cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(n_tokens > 0 && width > 0, "swiglu: bad sizes");
     long long total = (long long)n_tokens * width;
+    if (dtype == LLMB_DTYPE_BF16 && width % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(act)) & 15) == 0) {
+        long long vectors = total / 8;
+        int blocks = (int)((vectors + 255) / 256 < 148 * 16 ? (vectors + 255) / 256 : 148 * 16);
+        swiglu_vec_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)act,
+                                                      vectors, width / 8);
+        return check_launch("swiglu");
+    }
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == LLMB_DTYPE_F32)
         swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)act, total, width);

@@ -139,8 +139,12 @@ struct Epilogue {
     float* residual;         // [tokens, ldo] 32-bit, added into
     int out_is_bf16;
     int ldo;
-    int tokens, outs;        // valid tokens and output columns
+    int tokens, outs;        // valid tokens and output columns (rows of the weight matrix)
+    int glu;                 // gated activation: the weight rows alternate 16 gate rows, 16 up rows;
+                             // out is bfloat16 [tokens, ldo] with outs / 2 columns silu(gate) * up
 };
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
 
 // One work unit: output tile (tile_a, tile_b) and one slice of its k-blocks.
 struct Unit {
@@ -159,6 +163,20 @@ __device__ __forceinline__ Unit unit_of(int u, int tiles_a, int splits) {
 template <int BN>
 __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int a_row, int tile_b,
                                               int c, float (&v)[16]) {
+    if (swap && ep.glu) {
+        // lanes 0-15 of a warp hold 16 gate rows, lanes 16-31 the up rows of the same features
+        int lane = threadIdx.x & 31;
+        int feature = (a_row >> 5) * 16 + (a_row & 15);
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float up = __shfl_xor_sync(0xffffffffu, v[j], 16);
+            int token = tile_b * BN + c + j;
+            if (lane < 16 && a_row < ep.outs && token < ep.tokens)
+                o[(size_t)token * ep.ldo + feature] = __float2bfloat16_rn(silu_mul(v[j], up));
+        }
+        return;
+    }
     if (swap) {
         // D[out column a_row, token]: one token at a time, lanes along the output row
         if (a_row >= ep.outs) return;
@@ -361,6 +379,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * BN;
             int a_row = w.tile_a * BM + row;             // swap: output column; else: token
             size_t tile_id = (size_t)w.tile_b * tiles_a + w.tile_a;
+            if (splits == 1 && ep.glu && !swap) {
+                // columns alternate 16 gate, 16 up: this thread's row gets 16 activations per pair
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out);
+#pragma unroll 1
+                for (int c = 0; c + 32 <= BN; c += 32) {
+                    uint32_t g[16], u[16];
+                    tmem_ld16(taddr + c, g);
+                    tmem_ld16(taddr + c + 16, u);
+                    int n0 = w.tile_b * BN + c;                      // first weight row of the pair
+                    if (a_row < ep.tokens && n0 + 32 <= ep.outs) {
+                        uint4 packed[2];
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            h[j] = __floats2bfloat162_rn(
+                                silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(u[2 * j])),
+                                silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1])));
+                        __nv_bfloat16* dst = o + (size_t)a_row * ep.ldo + n0 / 2;
+                        if ((ep.ldo & 7) == 0) {
+                            reinterpret_cast<uint4*>(dst)[0] = packed[0];
+                            reinterpret_cast<uint4*>(dst)[1] = packed[1];
+                        } else {
+                            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(packed);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) dst[j] = e[j];
+                        }
+                    }
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buffer]));
+                continue;
+            }
             if (splits == 1) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
@@ -572,9 +623,11 @@ LLMB_EXPORT int llmb_gemm_tc_counters(int M, int N, int K) {
 }
 
 // out[M, N] = x[M, K] . w[N, K]^T (+ bias[N]); or residual[M, N] += the same.
+// glu != 0: w holds gate and up rows alternating in blocks of 16 (N = 2 F rows, N % 32 == 0) and
+// out is bfloat16 [M, ldo] with F columns silu(gate) * up; no bias, no residual.
 LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
                              int out_dtype, float* residual, float* partials, long long partial_floats,
-                             unsigned* counters, int n_counters, int M, int N, int K, int ldo,
+                             unsigned* counters, int n_counters, int M, int N, int K, int ldo, int glu,
                              cudaStream_t stream) {
     if (M == 0 || N == 0) return LLMB_OK;
     LLMB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes");
@@ -585,7 +638,12 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
     LLMB_REQUIRE((out != nullptr) != (residual != nullptr), "gemm_tc: give out or residual");
     LLMB_REQUIRE(residual || out_dtype == LLMB_DTYPE_BF16 || out_dtype == LLMB_DTYPE_F32,
                  "gemm_tc: unknown output dtype %d", out_dtype);
-    LLMB_REQUIRE(ldo >= N, "gemm_tc: bad output stride");
+    if (glu) {
+        LLMB_REQUIRE(N % 32 == 0 && !bias && !residual && out_dtype == LLMB_DTYPE_BF16 && ldo >= N / 2,
+                     "gemm_tc: the gated epilogue needs N %% 32 == 0, a bfloat16 output and no bias");
+    } else {
+        LLMB_REQUIRE(ldo >= N, "gemm_tc: bad output stride");
+    }
     Plan p = make_plan(M, N, K);
     LLMB_REQUIRE((long long)p.tiles_a * p.tiles_b * p.splits < (1ll << 30), "gemm_tc: too many tiles");
     if (p.splits > 1) {
@@ -601,7 +659,7 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
         if ((code = make_map(&map_a, x, M, K, ldx, BM))) return code;
         if ((code = make_map(&map_b, w, N, K, K, p.bn))) return code;
     }
-    Epilogue ep{bias, out, residual, out_dtype == LLMB_DTYPE_BF16, ldo, M, N};
+    Epilogue ep{bias, out, residual, out_dtype == LLMB_DTYPE_BF16, ldo, M, N, glu != 0};
 #define GO(BN) return launch<BN>(map_a, map_b, ep, p.swap, p.tiles_a, p.tiles_b, p.n_kblocks, \
                                  p.per_split, p.splits, partials, counters, stream)
     switch (p.bn) {

@@ -178,12 +178,33 @@ def check_device_status() -> None:
                               "last steps are not valid")
 
 
-def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
+GLU_BLOCK = 16      # gate and up rows alternate in blocks of this many rows for the fused epilogue
+
+
+def glu_fusable(n_rows: int, k: int, dtype) -> bool:
+    """Whether `linear(..., glu=True)` serves a gate/up matrix of n_rows = 2 F rows."""
+    return dtype == torch.bfloat16 and n_rows % (2 * GLU_BLOCK) == 0 and k % 8 == 0
+
+
+def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
     """a [M, K] . w [N, K]^T (+ bias [N], float32). With `residual` (float32
     [M, N]) the product is added to it in place and it is returned; otherwise a
-    new [M, N] tensor of `out_dtype` (default: a's dtype)."""
+    new [M, N] tensor of `out_dtype` (default: a's dtype). With `glu`, w holds
+    gate and up rows alternating in blocks of 16 and the result is
+    silu(gate) * up as [M, N / 2] in a's dtype, computed in the product's epilogue."""
     _require_cuda(a, w, bias, residual)
     (m, k), (n, k2) = a.shape, w.shape
+    if glu:
+        if not glu_fusable(n, k, a.dtype) or bias is not None or residual is not None or a.stride(0) % 8:
+            raise KernelError("linear: the gated epilogue needs bfloat16, 2 F rows with F % 16 == 0, "
+                              "K % 8 == 0, no bias and no residual")
+        result = out if out is not None else torch.empty((m, n // 2), dtype=a.dtype, device=a.device)
+        partials, counters = _tc_scratch(a.device, m, n, k)
+        _call("gemm_tc", "llmb_gemm_tc", _ptr(a), _c_int(a.stride(0)), _ptr(w), None, _ptr(result),
+              _c_int(_code(a.dtype)), None, _ptr(partials), ctypes.c_longlong(partials.numel()),
+              _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k),
+              _c_int(n // 2), _c_int(1), _stream())
+        return result
     if k != k2 or a.dtype != w.dtype:
         raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype} does not fit w {tuple(w.shape)} {w.dtype}")
     if a.stride(1) != 1 or not w.is_contiguous():
@@ -203,7 +224,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
               _ptr(result if residual is None else None), _c_int(_code(target_dtype)),
               _ptr(residual), _ptr(partials), ctypes.c_longlong(partials.numel()),
               _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k), _c_int(n),
-              _stream())
+              _c_int(0), _stream())
     elif variant == "gemm_skinny":
         partials, counters = _skinny_scratch(a.device, m, n, k)
         _call("gemm_skinny", "llmb_gemm_skinny", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),
@@ -321,6 +342,6 @@ def required_libraries() -> list:
             "attention_decode", "attention_prefill", "sampling"]
 
 
-__all__ = ["PAGE", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
+__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

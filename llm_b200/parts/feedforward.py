@@ -20,6 +20,7 @@ class GatedMlp(FeedForward):
             raise Unsupported(f"activation '{spec.activation}' in a gated feed-forward")
         self.spec = spec
         self.w_gate_up = self.w_down = None
+        self.fused = False
 
     def parameters(self):
         s, t = self.spec, self.spec.tensor
@@ -28,14 +29,25 @@ class GatedMlp(FeedForward):
                 t["down"]: ParamSpec((s.hidden, s.intermediate))}
 
     def bind(self, tensors, dtype, device):
-        t = self.spec.tensor
-        self.w_gate_up = torch.cat([to_run_dtype(tensors[t["gate"]], dtype, device),
-                                    to_run_dtype(tensors[t["up"]], dtype, device)])
+        t, s = self.spec.tensor, self.spec
+        gate = to_run_dtype(tensors[t["gate"]], dtype, device)
+        up = to_run_dtype(tensors[t["up"]], dtype, device)
+        # where the tensor-core product can apply the activation in its epilogue, gate and up
+        # rows alternate in blocks of 16; otherwise they are stacked [gate; up]
+        self.fused = ops.glu_fusable(2 * s.intermediate, s.hidden, dtype)
+        if self.fused:
+            b = ops.GLU_BLOCK
+            self.w_gate_up = torch.stack([gate.view(-1, b, s.hidden), up.view(-1, b, s.hidden)],
+                                         dim=1).reshape(2 * s.intermediate, s.hidden).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up])
         self.w_down = to_run_dtype(tensors[t["down"]], dtype, device)
 
     def forward(self, h, ctx, residual):
-        gate_up = ops.linear(h, self.w_gate_up)
-        act = ops.swiglu(gate_up)
+        if self.fused:
+            act = ops.linear(h, self.w_gate_up, glu=True)
+        else:
+            act = ops.swiglu(ops.linear(h, self.w_gate_up))
         ops.linear(act, self.w_down, residual=residual)
 
 

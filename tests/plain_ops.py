@@ -33,8 +33,14 @@ def swiglu(gate_up, out=None):
     return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
 
 
-def linear(a, w, bias=None, out_dtype=None, residual=None, out=None):
+def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
     product = a.to(torch.float32) @ w.to(torch.float32).T
+    if glu:
+        # rows of w alternate 16 gate rows, 16 up rows
+        m = product.shape[0]
+        blocks = product.view(m, -1, 2, 16)
+        g, u = blocks[:, :, 0, :].reshape(m, -1), blocks[:, :, 1, :].reshape(m, -1)
+        return (g / (1.0 + torch.exp(-g)) * u).to(a.dtype)
     if bias is not None:
         product = product + bias.to(torch.float32)
     if residual is not None:
@@ -210,3 +216,4 @@ def install(monkeypatch):
         monkeypatch.setattr(ops, name, fn)
     monkeypatch.setattr(ops, "ensure_built", lambda names: None)
     monkeypatch.setattr(ops, "check_device_status", lambda: None)
+    monkeypatch.setattr(ops, "glu_fusable", lambda n, k, dtype: dtype == torch.bfloat16 and n % 32 == 0)

@@ -144,6 +144,25 @@ def test_linear_tensor_core_kernel(m, n, k):
     assert float((got - plain_ops.linear(view, w, out_dtype=torch.float32)).abs().max()) <= 2e-3 * scale
 
 
+@pytest.mark.parametrize("m,f,k", [(1, 64, 64), (8, 14336, 4096), (5, 208, 72), (64, 320, 128),
+                                   (70, 320, 128), (300, 1024, 520), (2048, 1024, 256)])
+def test_linear_with_gated_epilogue(m, f, k):
+    """silu(gate) * up in the epilogue of the tensor-core product, both orientations,
+    against the product followed by the plain activation."""
+    a = randn(m, k, dtype=torch.bfloat16, seed=96)
+    gate = randn(f, k, dtype=torch.bfloat16, seed=97, scale=0.1)
+    up = randn(f, k, dtype=torch.bfloat16, seed=98, scale=0.1)
+    mixed = torch.stack([gate.view(-1, 16, k), up.view(-1, 16, k)], dim=1).reshape(2 * f, k).contiguous()
+    assert ops().glu_fusable(2 * f, k, torch.bfloat16)
+    got = ops().linear(a, mixed, glu=True)
+    g, u = a.float() @ gate.float().T, a.float() @ up.float().T
+    want = g / (1 + torch.exp(-g)) * u
+    assert got.shape == (m, f)
+    assert torch.allclose(got.float(), want, atol=2e-2 * float(want.abs().max()), rtol=2e-2)
+    assert torch.allclose(plain_ops.linear(a, mixed, glu=True).float(), want, atol=1e-2 * float(want.abs().max()), rtol=2e-2)
+    assert ops().tensor_core_status() == 0
+
+
 def test_linear_rows_do_not_depend_on_the_batch():
     """32-bit: a row's product is bit-equal whether it is computed alone or among 200 rows."""
     a = randn(200, 172, seed=8)
