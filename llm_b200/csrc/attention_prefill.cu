@@ -36,8 +36,15 @@ constexpr int BQ = WARPS * 16;               // queries per block
 constexpr int STAGES = 2;
 constexpr int PAD = 8;
 
+// 2^x by the hardware approximation (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int D>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 3)          // three blocks per SM: at most 170 registers
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                          const __nv_bfloat16* __restrict__ k_cache,
                          const __nv_bfloat16* __restrict__ v_cache,
@@ -131,23 +138,22 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 mma_bf16(s[nb + 1], qa[kstep][0], qa[kstep][1], qa[kstep][2], qa[kstep][3], b[2], b[3]);
             }
         }
-        // s[nb][0..1]: row0, keys key0 + nb * 8 + 2t, +1; s[nb][2..3]: row1, the same keys
+        // s[nb][0..1]: row0, keys key0 + nb * 8 + 2t, +1; s[nb][2..3]: row1, the same keys.
+        // Maxima are kept on the raw scores (the scale is positive); the scale and log2(e) are
+        // applied inside the exponent with one fused multiply-add per score.
         bool diagonal = key0 + LLMB_PAGE - 1 > start + tile * BQ + warp * 16;   // some key may be hidden
         float local0 = -INFINITY, local1 = -INFINITY;
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                int key = key0 + nb * 8 + 2 * t + i;
-                float v0 = s[nb][i] * scale_log2, v1 = s[nb][2 + i] * scale_log2;
                 if (diagonal) {
-                    if (key > pos0) v0 = -INFINITY;
-                    if (key > pos1) v1 = -INFINITY;
+                    int key = key0 + nb * 8 + 2 * t + i;
+                    if (key > pos0) s[nb][i] = -INFINITY;
+                    if (key > pos1) s[nb][2 + i] = -INFINITY;
                 }
-                s[nb][i] = v0;
-                s[nb][2 + i] = v1;
-                local0 = fmaxf(local0, v0);
-                local1 = fmaxf(local1, v1);
+                local0 = fmaxf(local0, s[nb][i]);
+                local1 = fmaxf(local1, s[nb][2 + i]);
             }
         }
         local0 = fmaxf(local0, __shfl_xor_sync(0xffffffffu, local0, 1));
@@ -156,16 +162,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         local1 = fmaxf(local1, __shfl_xor_sync(0xffffffffu, local1, 2));
         // key 0 is visible to every row, so after page 0 both maxima are finite
         float new0 = fmaxf(max0, local0), new1 = fmaxf(max1, local1);
-        float rescale0 = exp2f(max0 - new0), rescale1 = exp2f(max1 - new1);
+        float rescale0 = fast_exp2((max0 - new0) * scale_log2), rescale1 = fast_exp2((max1 - new1) * scale_log2);
         max0 = new0;
         max1 = new1;
+        float shift0 = new0 * scale_log2, shift1 = new1 * scale_log2;
         float add0 = 0.f, add1 = 0.f;
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                s[nb][i] = exp2f(s[nb][i] - new0);
-                s[nb][2 + i] = exp2f(s[nb][2 + i] - new1);
+                s[nb][i] = fast_exp2(fmaf(s[nb][i], scale_log2, -shift0));
+                s[nb][2 + i] = fast_exp2(fmaf(s[nb][2 + i], scale_log2, -shift1));
                 add0 += s[nb][i];
                 add1 += s[nb][2 + i];
             }

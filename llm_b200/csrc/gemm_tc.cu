@@ -491,6 +491,225 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------- two SMs on one tile
+// For large token counts the 128 x 256 tile above is held back by shared-memory fill: per
+// k-block it loads 48 KB for 524 tensor-core cycles. Two blocks of a cluster (a CTA pair on
+// neighbouring SMs) computing one 256 x 256 tile with tcgen05.mma.cta_group::2 halve the
+// weight traffic per SM: each block loads its own 128 token rows and only half (128 rows) of
+// the weight tile, and the instruction reads both halves. Block 0 of the pair issues the
+// instructions for both; each block keeps its 128 x 256 half of the accumulator in its own
+// tensor memory and runs its own epilogue.
+//
+// Barriers: both producers' TMA loads report their bytes to block 0's `full` barrier (the
+// .cta_group::2 form of the load allows a barrier in the partner block); tcgen05.commit with
+// a multicast mask frees the stage in both blocks and announces the accumulator to both
+// epilogues; all eight epilogue warps of the pair arrive on block 0's `acc_empty`.
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar,
+                                                 int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate),
+          "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+}
+
+constexpr int PAIR_BN = 256;        // columns of the pair's tile; each block loads half of them
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    Epilogue ep, int n_kblocks, int tiles_a, int n_units, int* status, int stages) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = (PAIR_BN / 2) * BK * 2;
+    constexpr int TMEM_COLS = 2 * PAIR_BN;
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_tiles = base;
+    unsigned char* b_tiles = base + (size_t)stages * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_tiles + (size_t)stages * B_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + stages;
+    uint64_t* acc_full_bar = bars + 2 * stages;
+    uint64_t* acc_empty_bar = bars + 2 * stages + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank = cluster_rank();
+    int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full_bar[b]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[b]), 8);          // four epilogue warps in each block
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();                                   // the partner's barriers exist from here on
+    tcgen05_fence_after();
+    uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int u = pair; u < n_units && ok; u += n_pairs) {
+                Unit w = unit_of(u, tiles_a, 1);
+                for (int kb = 0; kb < n_kblocks; ++kb, ++it) {
+                    int s = it % stages;
+                    uint32_t round = it / stages;
+                    ok = mbar_wait(smem_u32(&empty_bar[s]), (round & 1) ^ 1, abort_flag, status, 1);
+                    if (!ok) break;
+                    // both blocks' bytes are counted on block 0's barrier
+                    if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * (A_BYTES + B_BYTES));
+                    uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
+                    tma_load_2d_pair(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a, bar, kb * BK,
+                                     w.tile_a * 2 * BM + (int)rank * BM);
+                    tma_load_2d_pair(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, kb * BK,
+                                     w.tile_b * PAIR_BN + (int)rank * (PAIR_BN / 2));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // D 32-bit, A and B bfloat16, both K-major, N = 256, M = 256 over the pair
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       ((uint32_t)(PAIR_BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            uint32_t it = 0, n_done = 0;
+            bool ok = true;
+            for (int u = pair; u < n_units && ok; u += n_pairs, ++n_done) {
+                uint32_t buffer = n_done & 1, use = n_done >> 1;
+                ok = mbar_wait(smem_u32(&acc_empty_bar[buffer]), (use & 1) ^ 1, abort_flag, status, 4);
+                if (!ok) break;
+                tcgen05_fence_after();
+                uint32_t d_tmem = tmem_base + buffer * PAIR_BN;
+                for (int kb = 0; kb < n_kblocks; ++kb, ++it) {
+                    int s = it % stages;
+                    uint32_t round = it / stages;
+                    ok = mbar_wait(smem_u32(&full_bar[s]), round & 1, abort_flag, status, 2);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    uint64_t a_desc = smem_desc(smem_u32(a_tiles + (size_t)s * A_BYTES));
+                    uint64_t b_desc = smem_desc(smem_u32(b_tiles + (size_t)s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tcgen05_mma_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tcgen05_commit_pair(smem_u32(&empty_bar[s]));      // frees the stage in both blocks
+                }
+                if (ok) tcgen05_commit_pair(smem_u32(&acc_full_bar[buffer]));
+            }
+        }
+    } else {
+        int quarter = warp & 3;
+        int row = quarter * 32 + lane;
+        uint32_t n_done = 0;
+        bool ok = true;
+        for (int u = pair; u < n_units && ok; u += n_pairs, ++n_done) {
+            Unit w = unit_of(u, tiles_a, 1);
+            uint32_t buffer = n_done & 1, use = n_done >> 1;
+            ok = mbar_wait(smem_u32(&acc_full_bar[buffer]), use & 1, abort_flag, status, 3);
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * PAIR_BN;
+            int a_row = w.tile_a * 2 * BM + (int)rank * BM + row;
+            if (ep.glu) {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out);
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN; c += 32) {
+                    uint32_t g[16], uu[16];
+                    tmem_ld16(taddr + c, g);
+                    tmem_ld16(taddr + c + 16, uu);
+                    int n0 = w.tile_b * PAIR_BN + c;
+                    if (a_row < ep.tokens && n0 + 32 <= ep.outs) {
+                        uint4 packed[2];
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            h[j] = __floats2bfloat162_rn(
+                                silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(uu[2 * j])),
+                                silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(uu[2 * j + 1])));
+                        __nv_bfloat16* dst = o + (size_t)a_row * ep.ldo + n0 / 2;
+                        if ((ep.ldo & 7) == 0) {
+                            reinterpret_cast<uint4*>(dst)[0] = packed[0];
+                            reinterpret_cast<uint4*>(dst)[1] = packed[1];
+                        } else {
+                            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(packed);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) dst[j] = e[j];
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN; c += 16) {
+                    uint32_t r[16];
+                    float v[16];
+                    tmem_ld16(taddr + c, r);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+                    store_columns<PAIR_BN>(ep, 0, a_row, w.tile_b, c, v);
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&acc_empty_bar[buffer]), 0));
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 100; ++i) __nanosleep(10000);
+        __syncthreads();
+    }
+    cluster_sync();                                   // nobody leaves while the partner may still signal it
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -569,6 +788,33 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
     return check_launch("gemm_tc");
 }
 
+int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& ep, int tiles_a,
+                int tiles_b, int n_kblocks, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = BM * BK * 2 + (PAIR_BN / 2) * BK * 2;
+    int stages = (200 * 1024) / STAGE_BYTES;
+    if (stages > 8) stages = 8;
+    size_t smem = 1024 + (size_t)stages * STAGE_BYTES + (2 * stages + 4) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        LLMB_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int device = 0;
+        LLMB_CUDA(cudaGetDevice(&device));
+        LLMB_CUDA(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device));
+    }
+    int* status = status_word();
+    int* status_dev = nullptr;
+    if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
+    int n_units = tiles_a * tiles_b;
+    int pairs = n_units < n_sms / 2 ? n_units : n_sms / 2;
+    gemm_tc_pair_kernel<<<2 * pairs, THREADS, smem, stream>>>(map_a, map_b, ep, n_kblocks, tiles_a, n_units,
+                                                             status_dev, stages);
+    return check_launch("gemm_tc_pair");
+}
+
 struct Plan {
     int swap, bn, tiles_a, tiles_b, n_kblocks, per_split, splits;
 };
@@ -623,12 +869,13 @@ LLMB_EXPORT int llmb_gemm_tc_counters(int M, int N, int K) {
 }
 
 // out[M, N] = x[M, K] . w[N, K]^T (+ bias[N]); or residual[M, N] += the same.
+// allow_pair != 0: products with more than 128 rows run 256 x 256 tiles on pairs of SMs.
 // glu != 0: w holds gate and up rows alternating in blocks of 16 (N = 2 F rows, N % 32 == 0) and
 // out is bfloat16 [M, ldo] with F columns silu(gate) * up; no bias, no residual.
 LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
                              int out_dtype, float* residual, float* partials, long long partial_floats,
                              unsigned* counters, int n_counters, int M, int N, int K, int ldo, int glu,
-                             cudaStream_t stream) {
+                             int allow_pair, cudaStream_t stream) {
     if (M == 0 || N == 0) return LLMB_OK;
     LLMB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes");
     LLMB_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
@@ -652,6 +899,14 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
     }
     CUtensorMap map_a, map_b;
     int code;
+    if (allow_pair && !p.swap && M > 128 && N >= 256) {
+        // 256 x 256 tiles over pairs of SMs; each block's boxes are 128 rows
+        if ((code = make_map(&map_a, x, M, K, ldx, BM))) return code;
+        if ((code = make_map(&map_b, w, N, K, K, PAIR_BN / 2))) return code;
+        Epilogue ep{bias, out, residual, out_dtype == LLMB_DTYPE_BF16, ldo, M, N, glu != 0};
+        return launch_pair(map_a, map_b, ep, (M + 2 * BM - 1) / (2 * BM), (N + PAIR_BN - 1) / PAIR_BN,
+                           p.n_kblocks, stream);
+    }
     if (p.swap) {
         if ((code = make_map(&map_a, w, N, K, K, BM))) return code;
         if ((code = make_map(&map_b, x, M, K, ldx, p.bn))) return code;
