@@ -258,7 +258,8 @@ def main() -> int:
     clocks.stop()
 
     line = {
-        "metric": "decode tokens/s, Llama-3.1-8B shape bf16, batch 8, context 8192",
+        "metric": f"decode tokens/s, Llama-3.1-8B shape {'bf16' if dtype == torch.bfloat16 else 'fp32'}, "
+                  f"batch {args.batch}, context {args.context}",
         "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(main_run["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -44,11 +44,15 @@ class DecoderModel:
         return out
 
     def libraries(self) -> list:
+        """The kernel files a run of this model in its dtype needs (what gets compiled)."""
         names = ["elementwise", "gemm_simt", "gemm_skinny", "gemm_tc"]
         for block in self.blocks:
             names += list(block.libraries)
         names += list(self.final_norm.libraries)
-        return list(dict.fromkeys(names))
+        names = list(dict.fromkeys(names))
+        if self.dtype == torch.float32:                 # the 32-bit path runs on the CUDA cores only
+            names = [n for n in names if n not in ops.BFLOAT16_ONLY]
+        return names
 
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe

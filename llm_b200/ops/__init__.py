@@ -19,6 +19,7 @@ from . import tactics
 from .build import all_sources, ensure_built, load_library
 
 PAGE = 64   # positions per cache page (LLMB_PAGE in csrc/common.cuh)
+BFLOAT16_ONLY = ("gemm_tc", "gemm_skinny", "attention_decode", "attention_prefill")
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
@@ -251,16 +252,26 @@ _retired: list = []      # outgrown scratch buffers, kept alive for CUDA graphs 
 
 def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     """Into how many slices the keys of every sequence are cut for decode
-    attention: enough blocks to fill the GPU (two per SM), a power of two (so
-    that captured steps fall into few shapes), at most one slice per page."""
+    attention. Blocks are (slice, kv head, sequence) and two fit on an SM: the
+    count is the largest power of two that keeps all blocks in one wave of
+    2 x 148 (measured on a B200 at 8,192 positions: batch 8 is fastest with 4
+    slices = 256 blocks, batch 1 with 16 to 32), four when the batch alone
+    exceeds a wave, and never less than two pages a slice. It depends on the
+    length only through the power-of-two bucket of its page count, so that all
+    steps replayed from one captured graph agree on it."""
+    import os
+    if os.environ.get("LLMB_DECODE_SPLITS"):
+        return int(os.environ["LLMB_DECODE_SPLITS"])
     pages = max(1, (max_len + PAGE - 1) // PAGE)
-    want = max(1, -(-296 // max(1, n_seqs * n_kv_heads)))
+    floor_pages = 1 << (pages.bit_length() - 1)
+    pairs = max(1, n_seqs * n_kv_heads)
+    want = 296 // pairs if pairs < 296 else 4
     splits = 1
-    while splits < want and splits < 64:
+    while splits * 2 <= want and splits * 2 <= 32:
         splits *= 2
-    while splits > pages:
+    while splits > 1 and splits > floor_pages // 2:
         splits //= 2
-    return max(splits, 1)
+    return splits
 
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,

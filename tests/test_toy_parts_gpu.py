@@ -171,3 +171,11 @@ def test_toy_model_with_state_steps_like_its_plain_form(tmp_path, dtype):
             assert float((g - want).abs().max()) <= limit * max(scale, 1.0), (round_index, b)
         engine.release(slots)
         engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_full_and_windowed_layers_in_one_model_on_the_gpu(tmp_path, dtype):
+    """One layer sees every key, one a window of 70 kept in a ring of three pages, prompts
+    cut into passes of 48: the kernels' window and ring addressing against the plain form."""
+    from test_window_cpu import run_windowed
+    run_windowed(tmp_path, DEV, dtype, 2e-4 if dtype == torch.float32 else 0.04)
