@@ -3,6 +3,7 @@
     python -m llm_b200 [--model DIR] [--context 4096] [--max-tokens 256] [--temperature 0.7] ID ...
     python -m llm_b200 bench [-m DIR | --random SHAPE] [-c 4096] [-p 512] [-n 128] [-b 1] [-r 5] [-o json]
     python -m llm_b200 inspect DIR
+    python -m llm_b200 random (--shape NAME | --config FILE) --out DIR [--seed S]
 
 The first form completes a prompt given as token ids and prints the generated
 ids and the run's statistics (apps/cli/src/main.rs:55-76: the same flags and
@@ -43,6 +44,8 @@ def main(argv=None) -> int:
     args = list(sys.argv[1:] if argv is None else argv)
     if args and args[0] == "bench":
         return bench(args[1:])
+    if args and args[0] == "random":
+        return random_folder(args[1:])
     if args and args[0] == "inspect":
         if len(args) < 2:
             raise SystemExit("inspect needs a model folder")
@@ -170,6 +173,44 @@ def bench(args) -> int:
         used = torch.cuda.max_memory_allocated() / 2 ** 30
         print(f"\ndevice memory peak {used:.2f} GiB; weights read per decode step "
               f"{model.weight_bytes() / 2 ** 30:.2f} GiB")
+    return 0
+
+
+def random_folder(args) -> int:
+    """python -m llm_b200 random (--shape NAME | --config FILE) --out DIR [--seed S] [--layers L]
+    [--dtype bfloat16|float32] [--std 0.02]: write config.json and model.safetensors with random
+    weights (the fixture writer of MythEclipse/llm, scripts/make_tiny_moe.py, as a command)."""
+    name, config_file, out, seed, layers, dtype, std = None, None, None, 0, None, "bfloat16", 0.02
+    while args:
+        a = args.pop(0)
+        if a == "--shape":
+            name = _value(args, a)
+        elif a == "--config":
+            config_file = _value(args, a)
+        elif a == "--out":
+            out = _value(args, a)
+        elif a == "--seed":
+            seed = int(_value(args, a))
+        elif a == "--layers":
+            layers = int(_value(args, a))
+        elif a == "--dtype":
+            dtype = _value(args, a)
+        elif a == "--std":
+            std = float(_value(args, a))
+        else:
+            raise SystemExit(f"unknown flag {a}")
+    if out is None or (name is None) == (config_file is None):
+        raise SystemExit("usage: python -m llm_b200 random (--shape NAME | --config FILE) --out DIR "
+                         "[--seed S] [--layers L] [--dtype bfloat16|float32] [--std 0.02]")
+    from .api import parse_dtype
+    from .config import config_from_dict
+    from .shapes import shape
+    from .weights import write_random_model
+    raw = shape(name, layers) if name else json.loads(open(config_file).read())
+    if config_file and layers is not None:
+        raw["num_hidden_layers"] = layers
+    folder = write_random_model(out, config_from_dict(raw), seed, parse_dtype(dtype), std=std)
+    print(folder)
     return 0
 
 

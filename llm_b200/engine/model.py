@@ -93,6 +93,24 @@ class DecoderModel:
                     add(value)
         return total
 
+    def scratch_requests(self, n_tokens: int) -> list:
+        """Scratch of one layer pass for n_tokens tokens. Layers run one after the other, so
+        the plan of the layer with the largest needs serves all (blocks with equal specs
+        declare equal lists)."""
+        best, best_bytes = [], -1
+        for block in self.blocks:
+            requests = block.scratch_requests(n_tokens, self.dtype)
+            size = sum(r.nbytes for r in requests)
+            if size > best_bytes:
+                best, best_bytes = requests, size
+        names = {r.name for r in best}
+        for block in self.blocks:                          # buffers other blocks add, at the end
+            for r in block.scratch_requests(n_tokens, self.dtype):
+                if r.name not in names:
+                    best = best + [r]
+                    names.add(r.name)
+        return best
+
     # ------------------------------------------------------------------ cache needs
 
     def cache_requests(self):

@@ -20,6 +20,7 @@ from .. import ops
 from ..cache import PAGE, PagedCache, round_up
 from ..errors import ContextFull, FormatError, LlmError
 from ..parts.base import StepContext
+from .workspace import Workspace
 
 
 GRAPH_AFTER_STEPS = 2      # plain steps of a shape before it is captured
@@ -68,8 +69,10 @@ class Engine:
                                 self.dtype, self.device, self.step_tokens)
         self.vocab = model.spec.vocab
         self.steps_run = 0
+        self.workspace = Workspace(self.device, model.scratch_requests)
         self.use_graphs = (use_graphs and self.device.type == "cuda"
                            and os.environ.get("LLMB_NO_GRAPHS", "0") in ("", "0")
+                           and not ops.PROFILING
                            and getattr(model, "graph_safe", lambda: False)())
         self._graphs, self._graph_seen, self._graph_pool = {}, {}, None
         self._ring, self._ring_at = [(None, None)] * 4, 0
@@ -187,7 +190,8 @@ class Engine:
                 tok_pos=view(1), tok_seq=view(2), cu_seqlens=view(3), seq_lens=view(4),
                 slot_ids=view(5), cache=self.cache,
                 block_tables=[view(7 + g).view(n_seqs, -1) for g in range(len(tables))],
-                decode=decode, new_counts=counts, starts=starts, max_len=max_len)
+                decode=decode, new_counts=counts, starts=starts, max_len=max_len,
+                workspace=self.workspace.for_tokens(len(tokens)))
             return ctx, view(0), view(6)
 
         logits = None

@@ -1,0 +1,155 @@
+"""Planning the scratch buffers of a step into one arena.
+
+The planner follows MythEclipse/llm's workspace (apps/engine/src/workspace.rs):
+every activation of a pass is a request {name, size, first_use, last_use} over
+numbered phases (workspace.rs:24-43), requests are placed in order of first use
+at the lowest aligned offset that overlaps no buffer that is live at the same
+time, where writing in the phase another buffer is last read counts as overlap
+(workspace.rs:63-106), and the layout has an identity hash (workspace.rs:135-146).
+Its value is less the memory saved than fixed addresses: a captured decode step
+points into the arena, and no allocation happens inside a step.
+
+Here the requests are not one fixed list: every part declares the buffers of
+its own forward pass with phases of its own, and the block lines them up. All
+layers share one plan, so the arena is as large as one layer needs.
+"""
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass
+
+import torch
+
+ALIGNMENT = 256          # bytes; TMA wants 16, 256 keeps every buffer on its own cache lines
+
+
+@dataclass(frozen=True)
+class BufferRequest:
+    name: str
+    shape: tuple
+    dtype: torch.dtype
+    first_use: int          # phase in which the buffer is first written
+    last_use: int           # last phase in which it is read
+
+    @property
+    def nbytes(self) -> int:
+        n = torch.empty((), dtype=self.dtype).element_size()
+        for d in self.shape:
+            n *= d
+        return n
+
+    def shifted(self, by: int, prefix: str = "") -> "BufferRequest":
+        return BufferRequest(prefix + self.name, self.shape, self.dtype, self.first_use + by,
+                             self.last_use + by)
+
+
+@dataclass(frozen=True)
+class Placement:
+    request: BufferRequest
+    offset: int
+
+
+class Plan:
+    def __init__(self, placements: list, total: int):
+        self.placements = {p.request.name: p for p in placements}
+        self.total = total
+
+    def identity(self) -> str:
+        h = hashlib.sha256()
+        for name in sorted(self.placements):
+            p = self.placements[name]
+            h.update(f"{name}:{p.offset}:{p.request.nbytes}:{p.request.first_use}:{p.request.last_use};".encode())
+        return h.hexdigest()[:16]
+
+    def check(self) -> None:
+        """No two buffers that are live in a common phase share a byte; all are aligned."""
+        items = list(self.placements.values())
+        for p in items:
+            if p.offset % ALIGNMENT:
+                raise AssertionError(f"{p.request.name} is not aligned")
+            if p.offset + p.request.nbytes > self.total:
+                raise AssertionError(f"{p.request.name} leaves the arena")
+        for i, a in enumerate(items):
+            for b in items[i + 1:]:
+                if _live_together(a.request, b.request) and _bytes_overlap(a, b):
+                    raise AssertionError(f"{a.request.name} and {b.request.name} overlap while both live")
+
+
+def _live_together(a: BufferRequest, b: BufferRequest) -> bool:
+    return a.first_use <= b.last_use and b.first_use <= a.last_use
+
+
+def _bytes_overlap(a: Placement, b: Placement) -> bool:
+    return a.offset < b.offset + b.request.nbytes and b.offset < a.offset + a.request.nbytes
+
+
+def plan(requests) -> Plan:
+    """Greedy first fit in order of (first use, name)."""
+    names = [r.name for r in requests]
+    if len(set(names)) != len(names):
+        raise ValueError("two scratch buffers share a name")
+    placed: list = []
+    total = 0
+    for request in sorted(requests, key=lambda r: (r.first_use, r.name)):
+        if request.last_use < request.first_use:
+            raise ValueError(f"{request.name} is read before it is written")
+        size = request.nbytes
+        busy = sorted((p.offset, p.offset + p.request.nbytes) for p in placed
+                      if _live_together(p.request, request))
+        offset = 0
+        for begin, end in busy:
+            if offset + size <= begin:
+                break
+            offset = max(offset, -(-end // ALIGNMENT) * ALIGNMENT)
+        placed.append(Placement(request, offset))
+        total = max(total, offset + size)
+    return Plan(placed, -(-total // ALIGNMENT) * ALIGNMENT)
+
+
+class Workspace:
+    """The arena of an engine. `for_tokens(n)` plans (once per token count) and
+    returns named views; an arena that was outgrown stays alive, because a
+    captured step may still point into it."""
+
+    def __init__(self, device, requests_for_tokens):
+        self.device = torch.device(device)
+        self.requests_for_tokens = requests_for_tokens      # n_tokens -> list of BufferRequest
+        self.plans: dict = {}
+        self.arena = None
+        self._retired: list = []
+
+    def plan_for(self, n_tokens: int) -> Plan:
+        if n_tokens not in self.plans:
+            if len(self.plans) > 64:
+                self.plans.clear()
+            self.plans[n_tokens] = plan(self.requests_for_tokens(n_tokens))
+        return self.plans[n_tokens]
+
+    def for_tokens(self, n_tokens: int) -> "Views":
+        p = self.plan_for(n_tokens)
+        if self.arena is None or self.arena.numel() < p.total:
+            if self.arena is not None:
+                self._retired.append(self.arena)
+            self.arena = torch.empty(max(p.total, 1), dtype=torch.uint8, device=self.device)
+        return Views(p, self.arena)
+
+    def bytes(self) -> int:
+        return 0 if self.arena is None else self.arena.numel()
+
+
+class Views:
+    """Named tensors inside the arena for one step."""
+
+    def __init__(self, plan_: Plan, arena: torch.Tensor):
+        self.plan = plan_
+        self.arena = arena
+        self.prefix = ""
+
+    def get(self, name: str):
+        """The planned buffer `name` (of the current layer prefix), or None if no part declared it."""
+        placement = self.plan.placements.get(self.prefix + name)
+        if placement is None:
+            return None
+        r = placement.request
+        flat = self.arena[placement.offset:placement.offset + r.nbytes]
+        return flat.view(r.dtype).view(r.shape)

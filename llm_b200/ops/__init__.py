@@ -10,7 +10,10 @@ The parts call these functions as attributes of this module
 """
 from __future__ import annotations
 
+import atexit
 import ctypes
+import os
+import sys
 
 import torch
 
@@ -62,11 +65,44 @@ def count_launches(n: int) -> None:
     _launches += n
 
 
+# LLMB_PROFILE=1: every launch between two CUDA events, a table of milliseconds and calls per
+# kernel entry at exit (the per-launch timing of MythEclipse/llm's LLM_PROFILE=1,
+# apps/engine/src/cuda/mod.rs:1857-1866,1917-1972). Profiling switches graph replay off.
+PROFILING = os.environ.get("LLMB_PROFILE", "0") not in ("", "0")
+_profile: dict = {}
+
+
+def _report_profile() -> None:
+    if not _profile:
+        return
+    torch.cuda.synchronize()
+    rows = []
+    for name, events in _profile.items():
+        ms = sum(a.elapsed_time(b) for a, b in events)
+        rows.append((ms, len(events), name))
+    total = sum(r[0] for r in rows) or 1.0
+    print(f"[llm_b200] kernel time by entry point ({total:.2f} ms in all)", file=sys.stderr)
+    for ms, calls, name in sorted(rows, reverse=True):
+        print(f"  {name:28s}{ms:10.3f} ms{calls:8d} calls{ms / calls * 1e3:10.1f} us/call"
+              f"{100 * ms / total:7.1f} %", file=sys.stderr)
+
+
+if PROFILING:
+    atexit.register(_report_profile)
+
+
 def _call(lib_name: str, fn_name: str, *args, kernels: int = 1):
     global _launches
     lib = load_library(lib_name)
     _launches += kernels
-    code = getattr(lib, fn_name)(*args)
+    if PROFILING and not torch.cuda.is_current_stream_capturing():
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        code = getattr(lib, fn_name)(*args)
+        end.record()
+        _profile.setdefault(fn_name, []).append((begin, end))
+    else:
+        code = getattr(lib, fn_name)(*args)
     if code != 0:
         reader = getattr(lib, f"llmb_{lib_name}_last_error")
         reader.restype = ctypes.c_char_p

@@ -56,6 +56,13 @@ class AttentionMixer(Mixer):
         if self.position is not None:
             self.position.prepare(max_positions, device)
 
+    def scratch_requests(self, n_tokens, dtype):
+        from ..engine.workspace import BufferRequest
+        s = self.spec
+        # phases: 0 projections, 1 rotation + cache write, 2 attention, 3 output projection
+        return [BufferRequest("qkv", (n_tokens, self.q_width + 2 * self.kv_width), dtype, 0, 2),
+                BufferRequest("mixed", (n_tokens, self.q_width), dtype, 2, 3)]
+
     def kv_request(self):
         return KvRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
 
@@ -64,14 +71,15 @@ class AttentionMixer(Mixer):
         group, keys, values = ctx.cache.layer_view(cache_entry)
         table = ctx.block_tables[group]
         ring = ctx.cache.table_width(group)
-        qkv = ops.linear(h, self.w_qkv, self.b_qkv)
+        qkv = ops.linear(h, self.w_qkv, self.b_qkv, out=ctx.scratch("qkv"))
         ops.rope_cache_write(
             qkv, self.position.table if self.position is not None else None, ctx.tok_pos,
             ctx.tok_seq, table, ring, keys, values, s.n_heads, s.n_kv_heads, s.head_dim,
             interleaved=self.position.interleaved if self.position is not None else False,
             write_cache=(entry == cache_entry))
         mixed = ops.attention(qkv, keys, values, table, ring, ctx.tok_pos, ctx.tok_seq, s.n_heads,
-                              s.n_kv_heads, s.head_dim, s.scale, s.window, decode=ctx.decode,
+                              s.n_kv_heads, s.head_dim, s.scale, s.window, out=ctx.scratch("mixed"),
+                              decode=ctx.decode,
                               seq_lens=ctx.seq_lens, max_len=ctx.max_len,
                               cu_seqlens=ctx.cu_seqlens, max_new=max(ctx.new_counts))
         ops.linear(mixed, self.w_o, self.b_o, residual=residual)

@@ -41,7 +41,12 @@ class StepContext:
     new_counts: list               # host: tokens each sequence brings
     starts: list                   # host: position of each sequence's first new token
     max_len: int                   # host: longest sequence after this step
+    workspace: object = None       # engine.workspace.Views of this step, or None
     extras: dict = field(default_factory=dict)
+
+    def scratch(self, name: str):
+        """The planned buffer `name` of the part that is running, or None."""
+        return self.workspace.get(name) if self.workspace is not None else None
 
 
 class Part:
@@ -64,6 +69,12 @@ class Part:
 
     def prepare(self, max_positions: int, device) -> None:
         """Build tables that depend on the longest sequence the engine allows."""
+
+    def scratch_requests(self, n_tokens: int, dtype) -> list:
+        """engine.workspace.BufferRequest for every activation `forward` writes for
+        n_tokens tokens, with phases counted from 0 inside this part. A part that
+        declares nothing lets its kernels allocate."""
+        return []
 
     def weights(self) -> list:
         """The tensors a step reads in full (for the byte count of a decode step)."""
@@ -96,8 +107,9 @@ class FeedForward(Part):
 
 
 class Norm(Part):
-    def forward(self, x, out_dtype, rows=None):
-        """Normalise float32 rows x [T, hidden] (or the gathered `rows`) -> out_dtype."""
+    def forward(self, x, out_dtype, rows=None, out=None):
+        """Normalise float32 rows x [T, hidden] (or the gathered `rows`) -> out_dtype
+        (into `out` if given)."""
         raise NotImplementedError
 
 

@@ -45,11 +45,36 @@ class PreNormBlock(Block):
     def weights(self):
         return [w for p in self.parts for w in p.weights()]
 
+    def scratch_requests(self, n_tokens, dtype):
+        """The normed inputs of both halves plus what the mixer and the feed-forward
+        declare, their phases lined up one after the other."""
+        from ..engine.workspace import BufferRequest
+        hidden = self.spec.mixer_norm.size
+        mixer = self.mixer.scratch_requests(n_tokens, dtype)
+        ffn = self.feed_forward.scratch_requests(n_tokens, dtype)
+        mixer_end = 1 + max([r.last_use for r in mixer] + [0])
+        ffn_start = mixer_end + 2
+        out = [BufferRequest("h_mixer", (n_tokens, hidden), dtype, 0, mixer_end)]
+        out += [r.shifted(1, "mixer.") for r in mixer]
+        ffn_end = ffn_start + max([r.last_use for r in ffn] + [0])
+        out.append(BufferRequest("h_ffn", (n_tokens, hidden), dtype, mixer_end + 1, ffn_end))
+        out += [r.shifted(ffn_start, "ffn.") for r in ffn]
+        return out
+
     def forward(self, x, ctx, entry, cache_entry):
-        h = self.mixer_norm.forward(x, ctx.dtype)
+        views = ctx.workspace
+        h = self.mixer_norm.forward(x, ctx.dtype, out=ctx.scratch("h_mixer"))
+        if views is not None:
+            views.prefix = "mixer."
         self.mixer.forward(h, ctx, entry, cache_entry, x)
-        h = self.ffn_norm.forward(x, ctx.dtype)
+        if views is not None:
+            views.prefix = ""
+        h = self.ffn_norm.forward(x, ctx.dtype, out=ctx.scratch("h_ffn"))
+        if views is not None:
+            views.prefix = "ffn."
         self.feed_forward.forward(h, ctx, x)
+        if views is not None:
+            views.prefix = ""
 
 
 register_block("pre_norm", PreNormBlock)

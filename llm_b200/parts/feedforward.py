@@ -43,11 +43,21 @@ class GatedMlp(FeedForward):
             self.w_gate_up = torch.cat([gate, up])
         self.w_down = to_run_dtype(tensors[t["down"]], dtype, device)
 
+    def scratch_requests(self, n_tokens, dtype):
+        from ..engine.workspace import BufferRequest
+        s = self.spec
+        # phases: 0 gate and up, 1 activation, 2 down projection
+        act = BufferRequest("act", (n_tokens, s.intermediate), dtype, 0 if self.fused else 1, 2)
+        if self.fused:
+            return [act]
+        return [BufferRequest("gate_up", (n_tokens, 2 * s.intermediate), dtype, 0, 1), act]
+
     def forward(self, h, ctx, residual):
         if self.fused:
-            act = ops.linear(h, self.w_gate_up, glu=True)
+            act = ops.linear(h, self.w_gate_up, glu=True, out=ctx.scratch("act"))
         else:
-            act = ops.swiglu(ops.linear(h, self.w_gate_up))
+            gate_up = ops.linear(h, self.w_gate_up, out=ctx.scratch("gate_up"))
+            act = ops.swiglu(gate_up, out=ctx.scratch("act"))
         ops.linear(act, self.w_down, residual=residual)
 
 

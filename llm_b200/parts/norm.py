@@ -22,8 +22,8 @@ class RmsNorm(Norm):
     def bind(self, tensors, dtype, device):
         self.gain = to_float32(tensors[self.spec.weight], device)
 
-    def forward(self, x, out_dtype, rows=None):
-        return ops.rmsnorm(x, self.gain, self.spec.eps, out_dtype, rows)
+    def forward(self, x, out_dtype, rows=None, out=None):
+        return ops.rmsnorm(x, self.gain, self.spec.eps, out_dtype, rows, out=out)
 
 
 register_norm("rmsnorm", RmsNorm)
