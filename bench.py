@@ -30,20 +30,26 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 
 def peaks():
+    """Measured peaks if the file beside this script has them (keys searched at any depth:
+    hbm_gbs, bf16_tflops, bf16_tflops_sustained), else the fallback figures."""
     path = ROOT / "MEASURED_PEAKS.json"
     if path.is_file():
         try:
             raw = json.loads(path.read_text())
             flat = {}
+
             def walk(node):
                 if isinstance(node, dict):
                     for k, v in node.items():
-                        if isinstance(v, (int, float)) and k in FALLBACK_PEAKS:
+                        if isinstance(v, (int, float)) and not isinstance(v, bool) and k in FALLBACK_PEAKS:
                             flat.setdefault(k, float(v))
                         else:
                             walk(v)
+                elif isinstance(node, list):
+                    for v in node:
+                        walk(v)
             walk(raw)
-            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+            if flat.get("hbm_gbs", 0) > 0 and flat.get("bf16_tflops", 0) > 0:
                 return {**FALLBACK_PEAKS, **flat}, "measured"
         except (OSError, ValueError):
             pass
@@ -100,7 +106,8 @@ def reference_arm():
     pip cannot install it and there is no Rust toolchain in this image."""
     print(json.dumps({"impl": "reference",
                       "unavailable": "MythEclipse/llm is a Rust workspace without Python packaging; "
-                                     "pip install from /root/reference fails and no cargo/rustc is installed"}))
+                                     "pip install of its source tree fails (no setup.py or pyproject.toml) "
+                                     "and no cargo/rustc is installed"}))
     return 0
 
 

@@ -45,7 +45,7 @@ def engine_for(folder, dtype, **options):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "D", "E"])
 def test_whole_request(folders, plain, dtype, which):
     from llm_b200.engine import Entry
     config, weights = plain[which]
@@ -60,7 +60,7 @@ def test_whole_request(folders, plain, dtype, which):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "D", "E"])
 def test_last_32_tokens_one_by_one(folders, plain, dtype, which):
     from llm_b200.engine import Entry
     config, weights = plain[which]

@@ -47,7 +47,17 @@ TINY_D = {
     "attention_bias": True, "max_position_embeddings": 1024, "hidden_act": "silu",
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
+# sizes no fast kernel takes: a width of 100 (rows of 200 bytes are no multiple of 16), head size
+# 80, five heads without grouping, an odd feed-forward width and an odd vocabulary
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5,
+    "num_key_value_heads": 5, "head_dim": 80, "intermediate_size": 333, "vocab_size": 1001,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "attention_bias": False, "max_position_embeddings": 512, "hidden_act": "silu",
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
 def make_folder(tmp_path, which: str, dtype=torch.bfloat16, std=None):
