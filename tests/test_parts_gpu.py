@@ -141,7 +141,8 @@ def test_gated_mlp_alone(dtype, hidden, inter):
         h = torch.randn(n, hidden, generator=torch.Generator().manual_seed(n))
         want = P.gated_mlp(h.to(dtype).float(), w["f.g"].float(), w["f.u"].float(), w["f.d"].float())
         residual = torch.ones(n, hidden, device=DEV)
-        ffn.forward(h.to(DEV).to(dtype), None, residual)
+        from types import SimpleNamespace
+        ffn.forward(h.to(DEV).to(dtype), SimpleNamespace(scratch=lambda name: None, extras={}), residual)
         assert close(residual - 1.0, want, dtype)
 
 
