@@ -15,6 +15,8 @@ from __future__ import annotations
 import time
 from dataclasses import dataclass, field
 
+import torch
+
 from ..errors import ContextFull, FormatError
 from ..sampling import BatchSampler, SamplingParams
 from .step import Entry
@@ -98,6 +100,11 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
             engine.release([slots[b]])
             released.add(b)
 
+    # ids travel device -> pinned host memory while the next step is already queued
+    on_gpu = str(getattr(engine, "device", "cpu")).startswith("cuda")
+    staging = torch.empty(len(batch), dtype=torch.int32, pin_memory=on_gpu)
+    copied = torch.cuda.Event() if on_gpu else None
+
     try:
         logits = engine.step([Entry(slots[b], reqs[b].prompt, [len(reqs[b].prompt) - 1])
                               for b in live])
@@ -118,13 +125,31 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
                 live = keep
                 if not live:
                     break
-            tokens = sampler.sample(logits, live).tolist()      # one small device-to-host copy
+            sampled = sampler.sample(logits, live)               # int32 on the device
+            staging[:len(live)].copy_(sampled, non_blocking=True)
+            if copied is not None:
+                copied.record()
+            # Who goes on is known before the ids are: everyone whose limits allow one more
+            # token. Their next step is queued now, fed with the ids on the device; a
+            # sequence that turns out to have drawn a stop token simply drops that step.
+            room = [engine.length(slots[b]) < engine.max_seq_len for b in live]
+            onward = [k for k, b in enumerate(live)
+                      if len(emitted[b]) + 1 < reqs[b].max_tokens and room[k]]
+            next_logits = None
+            if onward:
+                feed = sampled if len(onward) == len(live) else sampled[
+                    torch.tensor(onward, dtype=torch.long, device=sampled.device)]
+                next_logits = engine.step([Entry(slots[live[k]], [0], [0]) for k in onward],
+                                          device_tokens=feed)
+            if copied is not None:
+                copied.synchronize()                             # the ids, not the queued step
+            tokens = staging[:len(live)].tolist()
             engine.check()
             now = time.perf_counter()
             if prefill_done is None:
                 prefill_done = now
-            going, feed = [], []
-            for b, token in zip(live, tokens):
+            going_rows, going = [], []
+            for k, (b, token) in enumerate(zip(live, tokens)):
                 if token in reqs[b].stop_tokens:
                     finish(b, "eos")
                     continue
@@ -133,16 +158,16 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
                     first_token_at[b] = now
                 if on_token is not None:
                     on_token(batch[b], token)
-                if engine.length(slots[b]) >= engine.max_seq_len:
+                if not room[k]:
                     finish(b, "context_full")
                 elif len(emitted[b]) >= reqs[b].max_tokens:
                     finish(b, "max_tokens")
                 else:
                     going.append(b)
-                    feed.append(token)
+                    going_rows.append(onward.index(k))
             live = going
             if live:
-                logits = engine.step([Entry(slots[b], [t], [0]) for b, t in zip(live, feed)])
+                logits = next_logits if len(going_rows) == len(onward) else next_logits[going_rows]
         sampler.check_status()
     finally:
         for b in range(len(batch)):

@@ -95,14 +95,22 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
 
-    def step(self, entries) -> torch.Tensor:
+    def step(self, entries, device_tokens=None) -> torch.Tensor:
         """Run the new tokens of every entry as one batch and return float32
         logits [wanted, vocab] on the device, in the order of the entries and of
         each entry's `want`. Everything is checked before anything is launched
         or changed: empty token lists, ids outside the vocabulary, wanted places
         outside the tokens, sequences that would outgrow the context, pages that
-        are not there."""
+        are not there.
+
+        `device_tokens` (int32 on the device, one id per entry) serves a decode
+        step whose ids the host has not seen yet (they were just sampled on the
+        device): every entry then brings one placeholder token, and the ids are
+        taken from that tensor on the stream."""
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        if device_tokens is not None and (len(device_tokens) != len(entries)
+                                          or any(len(e.tokens) != 1 for e in entries)):
+            raise FormatError("device_tokens needs exactly one token per entry")
         if not entries:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
         seen = set()
@@ -129,7 +137,7 @@ class Engine:
                                  for e in entries])
         longest = max(len(e.tokens) for e in entries)
         if longest <= self.step_tokens:
-            return self._pass(entries)
+            return self._pass(entries, device_tokens)
         # cut long prompts into passes; keep the caller's order of wanted rows
         pieces, order = [], []
         for start in range(0, longest, self.step_tokens):
@@ -147,7 +155,7 @@ class Engine:
         wanted = sorted(range(len(order)), key=lambda r: order[r])
         return logits[torch.tensor(wanted, dtype=torch.long, device=self.device)]
 
-    def _pass(self, entries) -> torch.Tensor:
+    def _pass(self, entries, device_tokens=None) -> torch.Tensor:
         cache = self.cache
         tokens, tok_pos, tok_seq, cu, seq_lens, rows, starts, counts = [], [], [], [0], [], [], [], []
         for b, e in enumerate(entries):
@@ -196,11 +204,13 @@ class Engine:
 
         logits = None
         if self.use_graphs and decode and all(e.want == [0] for e in entries):
-            logits = self._replay(len(entries), max_len, host, total, context)
+            logits = self._replay(len(entries), max_len, host, total, context, device_tokens)
         if logits is None:
             dev = host[:max(total, 4)].to(self.device, non_blocking=True)
             self._host_done(host)
             ctx, tokens_dev, rows_dev = context(dev)
+            if device_tokens is not None:
+                tokens_dev.copy_(device_tokens)
             logits = self.model.forward(tokens_dev, ctx, rows_dev)
         for e, new_length in zip(entries, seq_lens):
             cache.set_length(e.slot, new_length)
@@ -230,7 +240,7 @@ class Engine:
 
     # ------------------------------------------------------------------ captured decode steps
 
-    def _replay(self, n_seqs, max_len, host, total, context):
+    def _replay(self, n_seqs, max_len, host, total, context, device_tokens=None):
         """Decode steps of one shape (sequences, power-of-two bucket of pages)
         run from a CUDA graph once that shape has been seen GRAPH_AFTER_STEPS
         times, as the decode graphs of apps/engine/src/model.rs:699-729 are
@@ -249,6 +259,8 @@ class Engine:
             meta = torch.zeros(total, dtype=torch.int32, device=self.device)
             meta.copy_(host[:total], non_blocking=True)
             ctx, tokens_dev, rows_dev = context(meta)
+            if device_tokens is not None:
+                tokens_dev.copy_(device_tokens)
             before = ops.launch_count()
             torch.cuda.synchronize(self.device)
             cuda_graph = torch.cuda.CUDAGraph()
@@ -262,6 +274,8 @@ class Engine:
         cuda_graph, meta, out, kernels = graph
         meta.copy_(host[:total], non_blocking=True)
         self._host_done(host)
+        if device_tokens is not None:
+            meta[:n_seqs].copy_(device_tokens)           # the tokens are the buffer's first section
         cuda_graph.replay()
         ops.count_launches(kernels)
         return out.clone()
