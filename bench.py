@@ -248,7 +248,7 @@ def main() -> int:
         # the same decode metric through the Python entry point: host token ids in
         # (pinned, copied every step with the step's index arrays), sampled ids out
         llm = llm_b200.LLM(model, context=args.context, batch=args.batch)
-        e2e_steps = min(args.steps, 32)
+        e2e_steps = args.steps
         prompt_len = (args.e2e_context or args.context) - e2e_steps - 1
         prompts = [torch.randint(0, config.vocab_size, (prompt_len,),
                                  generator=torch.Generator().manual_seed(100 + i)).tolist()

@@ -295,8 +295,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     exceeds a wave, and never less than two pages a slice. It depends on the
     length only through the power-of-two bucket of its page count, so that all
     steps replayed from one captured graph agree on it."""
-    import os
-    if os.environ.get("LLMB_DECODE_SPLITS"):
+    if os.environ.get("LLMB_DECODE_SPLITS"):             # for measurements: force a slice count
         return int(os.environ["LLMB_DECODE_SPLITS"])
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     floor_pages = 1 << (pages.bit_length() - 1)
