@@ -45,13 +45,15 @@ class Engine:
     step_tokens: most new tokens of one sequence in one pass over the layers;
         longer prompts are cut into passes (each attends to everything cached
         before it, as the chunks of apps/engine/src/session.rs:109-130 do).
+    pass_tokens: most tokens of all sequences together in one pass (bounds the scratch
+        arena); a larger step is run as several passes over subsets of its tokens.
     use_graphs: replay decode steps from CUDA graphs (only if every part of the
         model says it can be captured).
     """
 
     def __init__(self, model, max_tokens: int, max_seq_len: int | None = None,
                  max_slots: int | None = None, step_tokens: int | None = None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, pass_tokens: int = 65536):
         if model.embedding is None:
             raise LlmError("the model has no weights bound")
         self.model = model
@@ -62,6 +64,7 @@ class Engine:
         self.max_seq_len = min(max_seq_len or limit, limit, max_tokens)
         self.max_slots = max_slots or max(1, max_tokens // PAGE)
         self.step_tokens = step_tokens or self.max_seq_len
+        self.pass_tokens = max(int(pass_tokens), 1)
         ops.ensure_built(model.libraries())
         model.prepare(self.max_seq_len)
         kv, states = model.cache_requests()
@@ -136,19 +139,27 @@ class Engine:
         self.cache.reserve_many([(e.slot, self.cache.length(e.slot) + len(e.tokens))
                                  for e in entries])
         longest = max(len(e.tokens) for e in entries)
-        if longest <= self.step_tokens:
+        total = sum(len(e.tokens) for e in entries)
+        if longest <= self.step_tokens and total <= self.pass_tokens:
             return self._pass(entries, device_tokens)
-        # cut long prompts into passes; keep the caller's order of wanted rows
+        # Cut the step into passes: at most step_tokens new tokens of a sequence and at most
+        # pass_tokens tokens in all per pass. A sequence's pieces run in order (each attends
+        # to what the earlier ones cached); sequences do not depend on each other, so any
+        # grouping gives the same logits. The caller's order of wanted rows is restored.
+        done = [0] * len(entries)
         pieces, order = [], []
-        for start in range(0, longest, self.step_tokens):
-            part, keys = [], []
+        while any(done[i] < len(e.tokens) for i, e in enumerate(entries)):
+            part, keys, budget = [], [], self.pass_tokens
             for i, e in enumerate(entries):
-                chunk = e.tokens[start:start + self.step_tokens]
-                if not chunk:
+                start = done[i]
+                take = min(len(e.tokens) - start, self.step_tokens, budget)
+                if take <= 0:
                     continue
-                want = [(j, w - start) for j, w in enumerate(e.want) if start <= w < start + len(chunk)]
-                part.append(Entry(e.slot, chunk, [w for _, w in want]))
+                want = [(j, w - start) for j, w in enumerate(e.want) if start <= w < start + take]
+                part.append(Entry(e.slot, e.tokens[start:start + take], [w for _, w in want]))
                 keys += [(i, j) for j, _ in want]
+                done[i] += take
+                budget -= take
             pieces.append(self._pass(part))
             order += keys
         logits = torch.cat(pieces)

@@ -71,6 +71,24 @@ def test_chunked_passes_equal_one_pass(tmp_path, plain_kernels):
     assert row == logits.shape[0]
 
 
+def test_a_token_budget_per_pass_changes_nothing(tmp_path, plain_kernels):
+    """Five prompts, at most 40 tokens a pass and 16 of one sequence: the same logits, in
+    the caller's order, as one pass would give."""
+    config, weights, engine = _setup(tmp_path, "A", step_tokens=16, pass_tokens=40)
+    seqs = [random_tokens(n, config["vocab_size"], 50 + n) for n in (33, 7, 20, 1, 45)]
+    wants = [[32, 0], [6], [], [0], [44, 15, 16]]
+    slots = engine.acquire(5)
+    logits = engine.step([Entry(s, q, w) for s, q, w in zip(slots, seqs, wants)])
+    row = 0
+    for q, w in zip(seqs, wants):
+        expected = plain_llama.forward(config, weights, q)
+        for place in w:
+            assert torch.allclose(logits[row], expected[place], atol=2e-5, rtol=1e-5)
+            row += 1
+    assert row == logits.shape[0]
+    assert [engine.length(s) for s in slots] == [33, 7, 20, 1, 45]
+
+
 def test_slots_are_reused_between_batches(tmp_path, plain_kernels):
     config, weights, engine = _setup(tmp_path, "A", max_tokens=192, max_slots=2)
     for round_index in range(3):

@@ -69,6 +69,27 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert part in text
 
 
+def test_sharded_checkpoint_through_its_index(tmp_path):
+    config = config_from_dict(dict(TINY_B))
+    tensors = random_tensors(declared_parameters(config.model_spec()), 9)
+    names = sorted(tensors)
+    half = len(names) // 2
+    shards = {"model-00001-of-00002.safetensors": names[:half],
+              "model-00002-of-00002.safetensors": names[half:]}
+    weight_map = {}
+    for shard, members in shards.items():
+        write_safetensors(tmp_path / shard, {n: tensors[n] for n in members})
+        weight_map.update({n: shard for n in members})
+    (tmp_path / "config.json").write_text(config.to_json())
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    model = load_model(tmp_path, torch.float32, "cpu")
+    assert torch.equal(model.head, tensors["lm_head.weight"].float())
+    weight_map["model.norm.weight"] = "model-00001-of-00002.safetensors"       # not in that shard
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    with pytest.raises(FormatError):
+        load_model(tmp_path, torch.float32, "cpu")
+
+
 def test_tied_model_declares_no_head_and_untied_does():
     a = declared_parameters(config_from_dict(dict(TINY_A)).model_spec())
     b = declared_parameters(config_from_dict(dict(TINY_B)).model_spec())
