@@ -22,7 +22,8 @@ from . import tactics
 from .build import all_sources, ensure_built, load_library
 
 PAGE = 64   # positions per cache page (LLMB_PAGE in csrc/common.cuh)
-BFLOAT16_ONLY = ("gemm_tc", "gemm_skinny", "attention_decode", "attention_prefill")
+BFLOAT16_ONLY = ("gemm_tc", "gemm_skinny", "attention_decode", "attention_prefill",
+                 "attention_prefill_tc")
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
@@ -207,12 +208,12 @@ def check_device_status() -> None:
     """Raise if a kernel of a loaded library reported a wait that ran out. Cheap (it
     reads a word of host memory); meaningful after the stream was synchronised."""
     from .build import _loaded
-    if "gemm_tc" in _loaded:
-        code = _loaded["gemm_tc"].llmb_gemm_tc_status()
-        if code != 0:
-            role = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, str(code))
-            raise KernelError(f"gemm_tc: a bounded wait of the {role} ran out; the results of the "
-                              "last steps are not valid")
+    for name in ("gemm_tc", "attention_prefill_tc"):
+        if name in _loaded:
+            code = getattr(_loaded[name], f"llmb_{name}_status")()
+            if code != 0:
+                raise KernelError(f"{name}: a bounded wait ran out (code {code}); the results of the "
+                                  "last steps are not valid")
 
 
 GLU_BLOCK = 16      # gate and up rows alternate in blocks of this many rows for the fused epilogue
@@ -320,8 +321,16 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window,
-                                       cu_seqlens is not None and seq_lens is not None)
-    if variant == "attention_prefill":
+                                       cu_seqlens is not None and seq_lens is not None,
+                                       qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
+    if variant == "attention_prefill_tc":
+        _call("attention_prefill_tc", "llmb_attention_prefill_tc", _ptr(qkv), _c_int(qkv.stride(0)),
+              _c_int(n), _ptr(k_cache), _ptr(v_cache), _c_int(k_cache.shape[0]), _ptr(block_table),
+              _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(cu_seqlens), _ptr(seq_lens),
+              _ptr(out), _c_int(out.stride(0)), _c_int(cu_seqlens.numel() - 1), _c_int(max_new),
+              _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_float(scale), _c_int(window),
+              _stream())
+    elif variant == "attention_prefill":
         _call("attention_prefill", "llmb_attention_prefill", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
               _c_int(ring_pages), _ptr(cu_seqlens), _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)),
@@ -386,7 +395,7 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 def required_libraries() -> list:
     """Names of the kernel files the decoder parts of this package use."""
     return ["elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic",
-            "attention_decode", "attention_prefill", "sampling"]
+            "attention_decode", "attention_prefill", "attention_prefill_tc", "sampling"]
 
 
 __all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",

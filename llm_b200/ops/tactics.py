@@ -88,7 +88,22 @@ def _prefill_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed=
     return None
 
 
+def _prefill_tc_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed=False,
+                      aligned=True, **_):
+    reason = _prefill_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed)
+    if reason:
+        return reason
+    if head_dim != 128:
+        return f"head_dim {head_dim} (served: 128)"
+    if not aligned:
+        return "the projection's rows are not 16-byte aligned (TMA)"
+    return None
+
+
 ATTENTION = [
+    Tactic("attention_prefill_tc", 15, _prefill_tc_guard,
+           "flash attention with both products on tcgen05 (accumulators in tensor memory, K and V "
+           "pages by TMA), one thread per query row for the softmax; head size 128"),
     Tactic("attention_prefill", 10, _prefill_guard,
            "flash attention over the paged cache for steps with several new tokens a sequence: "
            "64-query tiles, mma.sync, online softmax, heaviest tile first"),
@@ -130,9 +145,10 @@ def choose_linear(m, n, k, in_dtype, out_dtype, lda, aligned=True) -> str:
                    aligned=aligned)[0]
 
 
-def choose_attention(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed=False) -> str:
+def choose_attention(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed=False,
+                     aligned=True) -> str:
     return _choose(ATTENTION, decode=decode, dtype=dtype, n_heads=n_heads, n_kv_heads=n_kv_heads,
-                   head_dim=head_dim, window=window, packed=packed)[0]
+                   head_dim=head_dim, window=window, packed=packed, aligned=aligned)[0]
 
 
 def explain(family: str, **shape) -> str:

@@ -16,7 +16,7 @@ class AttentionMixer(Mixer):
     of MythEclipse/llm (apps/engine/src/model.rs:930-1040), with the sizes, the
     scale, the window, the biases and the position encoding as parameters."""
     graph_safe = True
-    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic", "attention_decode", "attention_prefill")
+    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic", "attention_decode", "attention_prefill", "attention_prefill_tc")
 
     def __init__(self, spec):
         self.spec = spec

@@ -288,12 +288,25 @@ def test_attention_decode_kernel_long_contexts(heads, kv_heads, dim):
 
 @pytest.mark.parametrize("heads,kv_heads,dim", [(8, 2, 128), (4, 1, 64), (6, 2, 96), (4, 4, 32),
                                                 (3, 1, 128)])
-def test_attention_prefill_kernel(heads, kv_heads, dim):
-    """The flash prefill kernel: sequences that start at position 0 and sequences that
-    continue (chunked prompts), lengths around tile and page edges, one batch."""
+@pytest.mark.parametrize("variant", ["attention_prefill", "attention_prefill_tc"])
+def test_attention_prefill_kernel(heads, kv_heads, dim, variant):
+    """The flash prefill kernels (mma.sync and tcgen05): sequences that start at position 0
+    and sequences that continue (chunked prompts), lengths around tile and page edges."""
     from llm_b200.ops import tactics
+    if variant == "attention_prefill_tc" and dim != 128:
+        pytest.skip("the tcgen05 kernel serves head size 128")
+    if variant == "attention_prefill":
+        tactics.disable("attention_prefill_tc")
+    try:
+        assert tactics.choose_attention(False, torch.bfloat16, heads, kv_heads, dim, 0, True) == variant
+        _check_prefill_attention(heads, kv_heads, dim)
+        ops().check_device_status()
+    finally:
+        tactics.enable("attention_prefill_tc")
+
+
+def _check_prefill_attention(heads, kv_heads, dim):
     dtype = torch.bfloat16
-    assert tactics.choose_attention(False, dtype, heads, kv_heads, dim, 0, True) == "attention_prefill"
     starts, counts = [0, 0, 100, 64, 0, 300], [300, 1, 65, 64, 63, 130]
     lens = [s + c for s, c in zip(starts, counts)]
     table, width, k_cache, v_cache = make_cache(len(lens), lens, kv_heads, dim, dtype, 93)
