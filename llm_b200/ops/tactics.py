@@ -93,8 +93,8 @@ def _prefill_tc_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, pack
     reason = _prefill_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed)
     if reason:
         return reason
-    if head_dim != 128:
-        return f"head_dim {head_dim} (served: 128)"
+    if head_dim not in (64, 128):
+        return f"head_dim {head_dim} (served: 64, 128)"
     if not aligned:
         return "the projection's rows are not 16-byte aligned (TMA)"
     return None
@@ -103,7 +103,7 @@ def _prefill_tc_guard(decode, dtype, n_heads, n_kv_heads, head_dim, window, pack
 ATTENTION = [
     Tactic("attention_prefill_tc", 15, _prefill_tc_guard,
            "flash attention with both products on tcgen05 (accumulators in tensor memory, K and V "
-           "pages by TMA), one thread per query row for the softmax; head size 128"),
+           "pages by TMA), one thread per query row for the softmax; head sizes 64 and 128"),
     Tactic("attention_prefill", 10, _prefill_guard,
            "flash attention over the paged cache for steps with several new tokens a sequence: "
            "64-query tiles, mma.sync, online softmax, heaviest tile first"),

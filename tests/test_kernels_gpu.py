@@ -293,8 +293,8 @@ def test_attention_prefill_kernel(heads, kv_heads, dim, variant):
     """The flash prefill kernels (mma.sync and tcgen05): sequences that start at position 0
     and sequences that continue (chunked prompts), lengths around tile and page edges."""
     from llm_b200.ops import tactics
-    if variant == "attention_prefill_tc" and dim != 128:
-        pytest.skip("the tcgen05 kernel serves head size 128")
+    if variant == "attention_prefill_tc" and dim not in (64, 128):
+        pytest.skip("the tcgen05 kernel serves head sizes 64 and 128")
     if variant == "attention_prefill":
         tactics.disable("attention_prefill_tc")
     try:
