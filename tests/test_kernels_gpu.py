@@ -325,6 +325,39 @@ def _check_prefill_attention(heads, kv_heads, dim):
     assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("variant", ["attention_prefill", "attention_prefill_tc"])
+@pytest.mark.parametrize("dim", [64, 128])
+def test_attention_prefill_growing_scores(variant, dim):
+    """Keys grow from one block of 128 to the next, first a little and then by much, so that a
+    row's running maximum moves late in the sequence: by less than the kernel's threshold for
+    rescaling (probabilities above one) and by far more (the accumulated output is rescaled)."""
+    from llm_b200.ops import tactics
+    heads, kv_heads, dtype, n = 4, 2, torch.bfloat16, 700
+    if variant == "attention_prefill":
+        tactics.disable("attention_prefill_tc")
+    try:
+        assert tactics.choose_attention(False, dtype, heads, kv_heads, dim, 0, True) == variant
+        table, width, k_cache, v_cache = make_cache(1, [n], kv_heads, dim, dtype, 96)
+        fill_cache(table, width, k_cache, v_cache, [n], 97)
+        for block, factor in enumerate([0.3, 1.0, 1.4, 0.5, 6.0, 2.0]):
+            for page in (2 * block, 2 * block + 1):
+                if page < width:
+                    k_cache[int(table[0, page])] *= factor
+        tok_pos = torch.arange(n, dtype=torch.int32, device=DEV)
+        tok_seq = torch.zeros(n, dtype=torch.int32, device=DEV)
+        cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+        seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+        q = randn(n, (heads + 2 * kv_heads) * dim, dtype=dtype, seed=98)
+        want = plain_ops.attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads,
+                                   dim, dim ** -0.5)
+        got = ops().attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads, dim,
+                              dim ** -0.5, 0, seq_lens=seq_lens, max_len=n, cu_seqlens=cu, max_new=n)
+        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        ops().check_device_status()
+    finally:
+        tactics.enable("attention_prefill_tc")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(dtype):
     """Among 500 keys one early key matches the query; the output must be its
