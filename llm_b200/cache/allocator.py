@@ -1,59 +1,67 @@
-"""Bookkeeping of slots and pages, on the host.
+"""Free lists of slots and pages.
 
 A slot stands for one live sequence; a page holds the keys and values of 64
 consecutive positions of one sequence for every layer of a group. Both come
 from free lists and go back to them when the sequence ends; taking a slot or
 page that is held, or returning one that is free, is an error, never silent.
+The lists themselves live in the native host library (`csrc/host/free_list.hpp`);
+this class is a handle on one of them.
 """
 from __future__ import annotations
 
-from ..errors import CacheFull, LlmError
+from ctypes import byref, c_int, c_void_p
+
+from .. import native
 
 
 class FreeList:
     """Integers 0 .. count-1, handed out lowest first and taken back."""
 
-    def __init__(self, count: int, what: str):
-        self.count = count
+    def __init__(self, count: int, what: str, _borrowed=None, _owner=None):
         self.what = what
-        self._free = list(range(count - 1, -1, -1))     # pop() gives the lowest
-        self._held = [False] * count
+        self._owned = _borrowed is None
+        self._owner = _owner             # a borrowed list lives as long as the cache it belongs to
+        if self._owned:
+            handle = c_void_p()
+            native.check(native.lib().llmh_free_list_create(int(count), what.encode(), byref(handle)))
+            self._handle = handle
+        else:
+            self._handle = c_void_p(_borrowed)
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and self._handle:
+            native.lib().llmh_free_list_destroy(self._handle)
+            self._handle = None
+
+    def _counts(self):
+        count, n_free = c_int(), c_int()
+        native.lib().llmh_free_list_counts(self._handle, byref(count), byref(n_free))
+        return count.value, n_free.value
+
+    @property
+    def count(self) -> int:
+        return self._counts()[0]
 
     @property
     def n_free(self) -> int:
-        return len(self._free)
+        return self._counts()[1]
 
     @property
     def n_held(self) -> int:
-        return self.count - len(self._free)
+        count, n_free = self._counts()
+        return count - n_free
 
     def take(self) -> int:
-        if not self._free:
-            raise CacheFull(f"no free {self.what} left (all {self.count} are held)")
-        item = self._free.pop()
-        if self._held[item]:
-            raise LlmError(f"{self.what} {item} was on the free list while held")
-        self._held[item] = True
-        return item
+        item = c_int()
+        native.check(native.lib().llmh_free_list_take(self._handle, byref(item)))
+        return item.value
 
     def give_back(self, item: int) -> None:
-        if not 0 <= item < self.count:
-            raise LlmError(f"{self.what} {item} does not exist")
-        if not self._held[item]:
-            raise LlmError(f"{self.what} {item} is freed twice")
-        self._held[item] = False
-        self._free.append(item)
-        self._free.sort(reverse=True)
+        native.check(native.lib().llmh_free_list_give_back(self._handle, int(item)))
 
     def is_held(self, item: int) -> bool:
-        return self._held[item]
+        return bool(native.lib().llmh_free_list_is_held(self._handle, int(item)))
 
     def check(self) -> None:
         """Every item is either free once or held, never both or neither."""
-        seen = [0] * self.count
-        for item in self._free:
-            seen[item] += 1
-        for item in range(self.count):
-            if seen[item] + (1 if self._held[item] else 0) != 1:
-                raise LlmError(f"{self.what} {item}: on the free list {seen[item]} times, "
-                               f"held={self._held[item]}")
+        native.check(native.lib().llmh_free_list_check(self._handle))

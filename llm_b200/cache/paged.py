@@ -15,15 +15,18 @@ serves a batch:
 * `state` tensors [slots, ...] hold what a mixer keeps per sequence at a fixed
   size; a slot's rows are zeroed when the slot is taken.
 
-Slots and pages are given back by `release` and reused.
+Slots and pages are given back by `release` and reused. Which page holds what is
+decided by the native host library (`csrc/host/cache.cpp`); this class owns the
+tensors and hands out views of them.
 """
 from __future__ import annotations
 
+from ctypes import byref, c_int, c_longlong, c_void_p
 from dataclasses import dataclass, field
 
 import torch
 
-from ..errors import CacheFull, ContextFull, LlmError
+from .. import native
 from .allocator import FreeList
 
 PAGE = 64
@@ -52,6 +55,29 @@ class StateRequest:
     dtype: torch.dtype = torch.float32
 
 
+class _SlotPages:
+    """slot -> list of the slot's physical pages in one group (read from the native cache)."""
+
+    def __init__(self, cache, group_index: int):
+        self._cache, self._group = cache, group_index
+
+    def __getitem__(self, slot: int) -> list:
+        width = self._cache.groups[self._group].ring_pages
+        pages, count = (c_int * width)(), c_int()
+        native.check(native.lib().llmh_cache_slot_pages(self._cache._handle, self._group, int(slot), pages,
+                                                        width, byref(count)))
+        return list(pages[:count.value])
+
+    def _held(self):
+        return [s for s in range(self._cache.max_slots) if self._cache.slots.is_held(s)]
+
+    def items(self):
+        return [(s, self[s]) for s in self._held()]
+
+    def values(self):
+        return [self[s] for s in self._held()]
+
+
 @dataclass
 class Group:
     kind: str
@@ -62,8 +88,7 @@ class Group:
     ring_pages: int = 0                               # logical pages per sequence
     pool: FreeList | None = None
     storage: torch.Tensor | None = None               # [entries, 2, pages, Hkv, PAGE, D]
-    slot_pages: dict = field(default_factory=dict)    # slot -> list of physical pages
-    host_table: torch.Tensor | None = None            # int32 [slots, ring_pages], mirrors slot_pages
+    slot_pages: _SlotPages | None = None              # slot -> list of physical pages
 
 
 class PagedCache:
@@ -76,14 +101,11 @@ class PagedCache:
 
     def __init__(self, requests, states, max_tokens: int, max_seq_len: int, max_slots: int,
                  dtype, device, step_tokens: int | None = None):
-        self.max_tokens = round_up(max(max_tokens, PAGE))
         self.max_seq_len = max_seq_len
         self.max_slots = max_slots
         self.dtype = dtype
         self.device = torch.device(device)
         self.step_tokens = step_tokens or max_seq_len
-        self.slots = FreeList(max_slots, "slot")
-        self.lengths = [0] * max_slots
         self.groups: list[Group] = []
         self.entry_group: list = []          # schedule entry -> (group index, index in group) or None
         by_key = {}
@@ -98,21 +120,23 @@ class PagedCache:
             g = by_key[key]
             self.entry_group.append((g, len(self.groups[g].entries)))
             self.groups[g].entries.append(entry)
-        total_pages = self.max_tokens // PAGE
-        seq_pages = round_up(max_seq_len) // PAGE
-        for group in self.groups:
-            if group.kind == "window":
-                # a step writes up to step_tokens new positions before attention runs, and
-                # the oldest query of the step still needs the window before it
-                group.ring_pages = min(seq_pages, (group.window + self.step_tokens - 2) // PAGE + 2)
-                n_pages = min(total_pages, max_slots * group.ring_pages)
-            else:
-                group.ring_pages = seq_pages
-                n_pages = total_pages
-            group.pool = FreeList(n_pages, f"page of the {group.kind} group")
-            group.host_table = torch.zeros((max_slots, group.ring_pages), dtype=torch.int32)
+        lib = native.lib()
+        handle = c_void_p()
+        native.check(lib.llmh_cache_create(c_longlong(int(max_tokens)), int(max_seq_len), int(max_slots),
+                                           int(self.step_tokens), len(self.groups),
+                                           native.ints(g.window for g in self.groups), byref(handle)))
+        self._handle = handle
+        self.max_tokens = lib.llmh_cache_max_tokens(handle)
+        self.slots = FreeList(max_slots, "slot", _borrowed=lib.llmh_cache_list(handle, -1), _owner=self)
+        for g, group in enumerate(self.groups):
+            ring, n_pages = c_int(), c_int()
+            lib.llmh_cache_group_info(handle, g, byref(ring), byref(n_pages))
+            group.ring_pages = ring.value
+            group.pool = FreeList(n_pages.value, f"page of the {group.kind} group",
+                                  _borrowed=lib.llmh_cache_list(handle, g), _owner=self)
+            group.slot_pages = _SlotPages(self, g)
             group.storage = torch.zeros(
-                (len(group.entries), 2, n_pages, group.n_kv_heads, PAGE, group.head_dim),
+                (len(group.entries), 2, n_pages.value, group.n_kv_heads, PAGE, group.head_dim),
                 dtype=dtype, device=self.device)
         self.states = []
         for request in states:
@@ -122,84 +146,51 @@ class PagedCache:
                 self.states.append(torch.zeros((max_slots, *request.shape), dtype=request.dtype,
                                                device=self.device))
 
+    def __del__(self):
+        handle = getattr(self, "_handle", None)
+        if handle:
+            native.lib().llmh_cache_destroy(handle)
+            self._handle = None
+
     # ------------------------------------------------------------------ slots
 
     def acquire(self) -> int:
         """Take a free slot: length 0, no pages, state zeroed."""
-        slot = self.slots.take()
-        self.lengths[slot] = 0
-        for group in self.groups:
-            group.slot_pages[slot] = []
-            group.host_table[slot].zero_()
+        slot = c_int()
+        native.check(native.lib().llmh_cache_acquire(self._handle, byref(slot)))
         for state in self.states:
             if state is not None:
-                state[slot].zero_()
-        return slot
+                state[slot.value].zero_()
+        return slot.value
 
     def release(self, slot: int) -> None:
         """Give the slot and all of its pages back."""
-        if not (0 <= slot < self.max_slots) or not self.slots.is_held(slot):
-            raise LlmError(f"slot {slot} is not held")
-        for group in self.groups:
-            for page in group.slot_pages.pop(slot):
-                group.pool.give_back(page)
-        self.lengths[slot] = 0
-        self.slots.give_back(slot)
+        native.check(native.lib().llmh_cache_release(self._handle, int(slot)))
 
     def reserve(self, slot: int, new_length: int) -> None:
         """Make sure the slot has pages for positions < new_length. Raises
         ContextFull or CacheFull before anything is changed."""
-        if not self.slots.is_held(slot):
-            raise LlmError(f"slot {slot} is not held")
-        if new_length > self.max_seq_len:
-            raise ContextFull(new_length, self.max_seq_len)
-        needs = []
-        for group in self.groups:
-            want = min(round_up(new_length) // PAGE, group.ring_pages)
-            extra = want - len(group.slot_pages[slot])
-            if extra > group.pool.n_free:
-                raise CacheFull(f"the {group.kind} group has {group.pool.n_free} free pages, "
-                                f"slot {slot} needs {extra} more for {new_length} positions")
-            needs.append(extra)
-        for group, extra in zip(self.groups, needs):
-            for _ in range(max(extra, 0)):
-                page = group.pool.take()
-                group.host_table[slot, len(group.slot_pages[slot])] = page
-                group.slot_pages[slot].append(page)
+        native.check(native.lib().llmh_cache_reserve(self._handle, int(slot), c_longlong(int(new_length))))
 
     def reserve_many(self, wanted) -> None:
         """`reserve` for several (slot, new_length) pairs: all of them or none."""
-        needs = [0] * len(self.groups)
-        for slot, new_length in wanted:
-            if not self.slots.is_held(slot):
-                raise LlmError(f"slot {slot} is not held")
-            if new_length > self.max_seq_len:
-                raise ContextFull(new_length, self.max_seq_len)
-            for g, group in enumerate(self.groups):
-                want = min(round_up(new_length) // PAGE, group.ring_pages)
-                needs[g] += max(want - len(group.slot_pages[slot]), 0)
-        for g, group in enumerate(self.groups):
-            if needs[g] > group.pool.n_free:
-                raise CacheFull(f"the {group.kind} group has {group.pool.n_free} free pages, "
-                                f"this step needs {needs[g]}")
-        for slot, new_length in wanted:
-            self.reserve(slot, new_length)
+        wanted = list(wanted)
+        native.check(native.lib().llmh_cache_reserve_many(
+            self._handle, len(wanted), native.ints(s for s, _ in wanted),
+            native.ints((n for _, n in wanted), c_longlong)))
 
     def can_hold(self, lengths) -> bool:
         """Whether new sequences of these final lengths fit beside what is held."""
-        if len(lengths) > self.slots.n_free or any(n > self.max_seq_len for n in lengths):
-            return False
-        for group in self.groups:
-            pages = sum(min(round_up(n) // PAGE, group.ring_pages) for n in lengths)
-            if pages > group.pool.n_free:
-                return False
-        return True
+        lengths = list(lengths)
+        return bool(native.lib().llmh_cache_can_hold(self._handle, len(lengths), native.ints(lengths, c_longlong)))
 
     def set_length(self, slot: int, length: int) -> None:
-        self.lengths[slot] = length
+        native.check(native.lib().llmh_cache_set_length(self._handle, int(slot), int(length)))
 
     def length(self, slot: int) -> int:
-        return self.lengths[slot]
+        length = c_int()
+        native.check(native.lib().llmh_cache_length(self._handle, int(slot), byref(length)))
+        return length.value
 
     # ------------------------------------------------------------------ views for a step
 
@@ -209,7 +200,11 @@ class PagedCache:
     def block_table_rows(self, group_index: int, slots) -> torch.Tensor:
         """int32 [len(slots), width] on the host: one row of physical pages per
         slot, 0 where the slot has no page yet."""
-        return self.groups[group_index].host_table[torch.as_tensor(slots, dtype=torch.long)]
+        slots = [int(s) for s in slots]
+        out = torch.zeros((len(slots), self.groups[group_index].ring_pages), dtype=torch.int32)
+        native.check(native.lib().llmh_cache_table_rows(self._handle, int(group_index), len(slots),
+                                                        native.ints(slots), c_void_p(out.data_ptr())))
+        return out
 
     def layer_view(self, entry: int):
         """(group index, keys, values) of the schedule entry that owns storage:
@@ -226,7 +221,7 @@ class PagedCache:
 
     def held_tokens(self) -> int:
         """Tokens held now, each sequence rounded up to whole pages."""
-        return sum(round_up(self.lengths[s]) for s in range(self.max_slots) if self.slots.is_held(s))
+        return native.lib().llmh_cache_held_tokens(self._handle)
 
     def bytes(self) -> int:
         total = sum(g.storage.numel() * g.storage.element_size() for g in self.groups)
@@ -235,18 +230,4 @@ class PagedCache:
 
     def check(self) -> None:
         """No slot or page lost, held twice, or shared between two slots."""
-        self.slots.check()
-        for group in self.groups:
-            group.pool.check()
-            owners = {}
-            for slot, pages in group.slot_pages.items():
-                if not self.slots.is_held(slot):
-                    raise LlmError(f"freed slot {slot} still lists pages")
-                for page in pages:
-                    if page in owners:
-                        raise LlmError(f"page {page} is held by slots {owners[page]} and {slot}")
-                    if not group.pool.is_held(page):
-                        raise LlmError(f"slot {slot} lists page {page} that is on the free list")
-                    owners[page] = slot
-            if len(owners) != group.pool.n_held:
-                raise LlmError(f"{group.pool.n_held - len(owners)} pages are held by no slot")
+        native.check(native.lib().llmh_cache_check(self._handle))

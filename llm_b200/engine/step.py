@@ -12,13 +12,16 @@ top of what earlier steps left in the cache.
 from __future__ import annotations
 
 import os
+from array import array
+from ctypes import byref, c_int, c_longlong, c_void_p
 from dataclasses import dataclass
+from itertools import chain
 
 import torch
 
-from .. import ops
+from .. import native, ops
 from ..cache import PAGE, PagedCache, round_up
-from ..errors import ContextFull, FormatError, LlmError
+from ..errors import FormatError, LlmError
 from ..parts.base import StepContext
 from .workspace import Workspace
 
@@ -32,6 +35,29 @@ class Entry:
     slot: int
     tokens: list                 # its next tokens (at least one)
     want: list                   # indices into `tokens` whose logits are wanted
+
+
+class _Batch:
+    """The entries of a step as the C arrays that the native host library reads."""
+
+    def __init__(self, entries):
+        try:
+            self.tokens = array("i", chain.from_iterable(e.tokens for e in entries))
+            self.wants = array("i", chain.from_iterable(e.want for e in entries))
+        except (OverflowError, TypeError) as error:
+            raise FormatError(f"token ids and wanted places must be 32-bit integers ({error})") from None
+        self.n = len(entries)
+        self.slots = native.ints(e.slot for e in entries)
+        self.counts = native.ints(len(e.tokens) for e in entries)
+        self.want_counts = native.ints(len(e.want) for e in entries)
+
+    @staticmethod
+    def _pointer(values):
+        return (c_int * len(values)).from_buffer(values) if len(values) else None
+
+    def arguments(self):
+        return (self.n, self.slots, self.counts, self._pointer(self.tokens), self.want_counts,
+                self._pointer(self.wants))
 
 
 class Engine:
@@ -111,37 +137,22 @@ class Engine:
         device): every entry then brings one placeholder token, and the ids are
         taken from that tensor on the stream."""
         entries = [e if isinstance(e, Entry) else Entry(*e) for e in entries]
+        for e in entries:
+            e.tokens, e.want = list(e.tokens), list(e.want)
         if device_tokens is not None and (len(device_tokens) != len(entries)
                                           or any(len(e.tokens) != 1 for e in entries)):
             raise FormatError("device_tokens needs exactly one token per entry")
         if not entries:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=self.device)
-        seen = set()
-        for e in entries:
-            if e.slot in seen:
-                raise FormatError(f"slot {e.slot} appears twice in one step")
-            seen.add(e.slot)
-            if len(e.tokens) == 0:
-                raise FormatError(f"slot {e.slot} brings no token")
-            e.tokens = [int(t) for t in e.tokens]
-            e.want = [int(w) for w in e.want]
-            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
-                bad = next(t for t in e.tokens if not 0 <= t < self.vocab)
-                raise FormatError(f"token id {bad} is outside the vocabulary of {self.vocab}")
-            for w in e.want:
-                if not 0 <= w < len(e.tokens):
-                    raise FormatError(f"wanted place {w} is outside the {len(e.tokens)} tokens "
-                                      f"of slot {e.slot}")
-            new_length = self.cache.length(e.slot) + len(e.tokens)
-            if new_length > self.max_seq_len:
-                raise ContextFull(new_length, self.max_seq_len)
-        # pages for the whole step, all or nothing
-        self.cache.reserve_many([(e.slot, self.cache.length(e.slot) + len(e.tokens))
-                                 for e in entries])
+        # checked, and pages taken for the whole step (all or nothing), by the native host library
+        batch = _Batch(entries)
+        lib, cache = native.lib(), self.cache._handle
+        native.check(lib.llmh_step_check(cache, *batch.arguments(), self.vocab, self.max_seq_len))
+        native.check(lib.llmh_step_reserve(cache, batch.n, batch.slots, batch.counts))
         longest = max(len(e.tokens) for e in entries)
         total = sum(len(e.tokens) for e in entries)
         if longest <= self.step_tokens and total <= self.pass_tokens:
-            return self._pass(entries, device_tokens)
+            return self._pass(entries, device_tokens, batch)
         # Cut the step into passes: at most step_tokens new tokens of a sequence and at most
         # pass_tokens tokens in all per pass. A sequence's pieces run in order (each attends
         # to what the earlier ones cached); sequences do not depend on each other, so any
@@ -166,51 +177,35 @@ class Engine:
         wanted = sorted(range(len(order)), key=lambda r: order[r])
         return logits[torch.tensor(wanted, dtype=torch.long, device=self.device)]
 
-    def _pass(self, entries, device_tokens=None) -> torch.Tensor:
-        cache = self.cache
-        tokens, tok_pos, tok_seq, cu, seq_lens, rows, starts, counts = [], [], [], [0], [], [], [], []
-        for b, e in enumerate(entries):
-            start = cache.length(e.slot)
-            n = len(e.tokens)
-            base = len(tokens)
-            tokens += e.tokens
-            tok_pos += range(start, start + n)
-            tok_seq += [b] * n
-            cu.append(base + n)
-            seq_lens.append(start + n)
-            rows += [base + w for w in e.want]
-            starts.append(start)
-            counts.append(n)
-        slots = [e.slot for e in entries]
-        sections = [tokens, tok_pos, tok_seq, cu, seq_lens, slots, rows]
-        tables = [cache.block_table_rows(g, slots) for g in range(len(cache.groups))]
-        offsets, total = [], 0
-        for size in [len(s) for s in sections] + [t.numel() for t in tables]:
-            offsets.append(total)
-            total += (size + 3) // 4 * 4            # every section starts 16-byte aligned
-        host = self._host_buffer(max(total, 4))
-        flat = torch.tensor([v for s in sections for v in s], dtype=torch.int32)
-        at = 0
-        for s, offset in zip(sections, offsets):
-            host[offset:offset + len(s)] = flat[at:at + len(s)]
-            at += len(s)
-        for t, offset in zip(tables, offsets[len(sections):]):
-            host[offset:offset + t.numel()] = t.reshape(-1)
-        sizes = [len(s) for s in sections] + [t.numel() for t in tables]
-        decode = all(c == 1 for c in counts)
-        max_len = max(seq_lens)
+    def _pass(self, entries, device_tokens=None, batch=None) -> torch.Tensor:
+        batch = batch or _Batch(entries)
+        lib, cache = native.lib(), self.cache._handle
+        n_sections = lib.llmh_step_sections(cache)
+        offsets, sizes = (c_longlong * n_sections)(), (c_longlong * n_sections)()
+        total, summary = c_longlong(), (c_longlong * 5)()
+        native.check(lib.llmh_step_layout(cache, batch.n, batch.counts, batch.want_counts, offsets, sizes, byref(total)))
+        total = total.value
+        host = self._host_buffer(total)
+        native.check(lib.llmh_step_pack(cache, *batch.arguments(), host.data_ptr(), host.numel(),
+                                        offsets, sizes, summary))
+        offsets, sizes = list(offsets), list(sizes)
+        n_tokens, decode, max_len = summary[0], bool(summary[2]), summary[3]
+        counts = list(batch.counts)
+        seq_lens = host[offsets[4]:offsets[4] + batch.n].tolist()
+        starts = [after - c for after, c in zip(seq_lens, counts)]
+        n_groups = n_sections - 7
 
         def context(dev):
             def view(i):
                 return dev[offsets[i]:offsets[i] + sizes[i]]
-            n_seqs = len(slots)
+            n_seqs = batch.n
             ctx = StepContext(
-                n_tokens=len(tokens), n_seqs=n_seqs, dtype=self.dtype, device=self.device,
+                n_tokens=n_tokens, n_seqs=n_seqs, dtype=self.dtype, device=self.device,
                 tok_pos=view(1), tok_seq=view(2), cu_seqlens=view(3), seq_lens=view(4),
                 slot_ids=view(5), cache=self.cache,
-                block_tables=[view(7 + g).view(n_seqs, -1) for g in range(len(tables))],
+                block_tables=[view(7 + g).view(n_seqs, -1) for g in range(n_groups)],
                 decode=decode, new_counts=counts, starts=starts, max_len=max_len,
-                workspace=self.workspace.for_tokens(len(tokens)))
+                workspace=self.workspace.for_tokens(n_tokens))
             return ctx, view(0), view(6)
 
         logits = None
@@ -223,8 +218,7 @@ class Engine:
             if device_tokens is not None:
                 tokens_dev.copy_(device_tokens)
             logits = self.model.forward(tokens_dev, ctx, rows_dev)
-        for e, new_length in zip(entries, seq_lens):
-            cache.set_length(e.slot, new_length)
+        native.check(lib.llmh_step_commit(cache, batch.n, batch.slots, batch.counts))
         self.steps_run += 1
         return logits
 

@@ -16,9 +16,12 @@ layers share one plan, so the arena is as large as one layer needs.
 from __future__ import annotations
 
 import hashlib
+from ctypes import byref, c_char_p, c_longlong
 from dataclasses import dataclass
 
 import torch
+
+from .. import native
 
 ALIGNMENT = 256          # bytes; TMA wants 16, 256 keeps every buffer on its own cache lines
 
@@ -84,26 +87,18 @@ def _bytes_overlap(a: Placement, b: Placement) -> bool:
 
 
 def plan(requests) -> Plan:
-    """Greedy first fit in order of (first use, name)."""
-    names = [r.name for r in requests]
-    if len(set(names)) != len(names):
-        raise ValueError("two scratch buffers share a name")
-    placed: list = []
-    total = 0
-    for request in sorted(requests, key=lambda r: (r.first_use, r.name)):
-        if request.last_use < request.first_use:
-            raise ValueError(f"{request.name} is read before it is written")
-        size = request.nbytes
-        busy = sorted((p.offset, p.offset + p.request.nbytes) for p in placed
-                      if _live_together(p.request, request))
-        offset = 0
-        for begin, end in busy:
-            if offset + size <= begin:
-                break
-            offset = max(offset, -(-end // ALIGNMENT) * ALIGNMENT)
-        placed.append(Placement(request, offset))
-        total = max(total, offset + size)
-    return Plan(placed, -(-total // ALIGNMENT) * ALIGNMENT)
+    """Greedy first fit in order of (first use, name), done by the native host library
+    (`csrc/host/planner.cpp`); `Plan.check` verifies a layout independently."""
+    requests = list(requests)
+    n = len(requests)
+    offsets, total = (c_longlong * n)(), c_longlong()
+    code = native.lib().llmh_plan_place(
+        n, (c_char_p * n)(*[r.name.encode() for r in requests]),
+        native.ints((r.nbytes for r in requests), c_longlong), native.ints(r.first_use for r in requests),
+        native.ints(r.last_use for r in requests), ALIGNMENT, offsets, byref(total))
+    if code != native.OK:
+        raise ValueError(native.lib().llmh_last_error().decode("utf-8", "replace"))
+    return Plan([Placement(r, offsets[i]) for i, r in enumerate(requests)], total.value)
 
 
 class Workspace:

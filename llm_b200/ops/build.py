@@ -164,3 +164,78 @@ def load_library(name: str) -> ctypes.CDLL:
 
 def all_sources() -> list:
     return sorted(p.stem for p in CSRC.glob("*.cu"))
+
+
+# ----------------------------------------------------------------------------- the host library
+
+HOST = CSRC / "host"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+_host_lib = None
+
+
+def _host_compiler() -> list:
+    for candidate in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if candidate and (Path(candidate).is_file() or shutil.which(candidate)):
+            return [candidate, *HOST_FLAGS]
+    # nvcc drives a host compiler of its own choice
+    return [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+
+def _host_digest() -> str:
+    h = hashlib.sha256()
+    for path in sorted(HOST.glob("*.cpp")) + sorted(HOST.glob("*.hpp")):
+        h.update(path.name.encode())
+        h.update(path.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def host_library_path() -> Path | None:
+    file_name = f"llmb_host-{_host_digest()}.so"
+    for d in _build_dirs():
+        if (d / file_name).is_file():
+            return d / file_name
+    return None
+
+
+def compile_host_library() -> Path:
+    """csrc/host/*.cpp as one shared library (no CUDA in it): the cache's bookkeeping, the step
+    packer, the scratch planner and the safetensors reader."""
+    existing = host_library_path()
+    if existing is not None:
+        return existing
+    out_dir = _writable_dir()
+    target = out_dir / f"llmb_host-{_host_digest()}.so"
+    scratch = out_dir / f".{target.name}.{os.getpid()}.{threading.get_ident()}.tmp"
+    sources = [str(p) for p in sorted(HOST.glob("*.cpp"))]
+    started = time.time()
+    _say("compiling the host library ...")
+    process = subprocess.run([*_host_compiler(), "-o", str(scratch), *sources], stdout=subprocess.PIPE,
+                             stderr=subprocess.STDOUT, text=True, cwd=str(out_dir))
+    if process.returncode != 0:
+        try:
+            scratch.unlink()
+        except OSError:
+            pass
+        raise KernelError(f"the host library failed to compile:\n{process.stdout}")
+    os.replace(scratch, target)
+    for stale in out_dir.glob("llmb_host-*.so"):
+        if stale != target:
+            try:
+                stale.unlink()
+            except OSError:
+                pass
+    _say(f"built {target.name} in {time.time() - started:.1f} s")
+    return target
+
+
+def load_host_library() -> ctypes.CDLL:
+    global _host_lib
+    with _lock:
+        if _host_lib is None:
+            path = compile_host_library()
+            try:
+                _host_lib = ctypes.CDLL(str(path))
+            except OSError as error:
+                raise KernelError(f"cannot load {path}: {error}") from None
+        return _host_lib

@@ -2,18 +2,23 @@
 
 Layout: 8 bytes little-endian header length, a JSON header
 {name: {dtype, shape, data_offsets: [begin, end]}}, then the raw tensor
-bytes. Every tensor is checked to lie inside the file, as the GGUF reader of
-MythEclipse/llm checks its tensors (apps/engine/src/gguf.rs:158-165).
+bytes. The reader is the native host library's (`csrc/host/safetensors.cpp`):
+it maps the file, reads the header with its own JSON reader and checks every
+tensor to lie inside the file, as the GGUF reader of MythEclipse/llm checks its
+tensors (apps/engine/src/gguf.rs:158-165). Tensors are views of that map.
 """
 from __future__ import annotations
 
+import ctypes
 import json
-import mmap
 import struct
+import warnings
+from ctypes import POINTER, byref, c_char_p, c_int, c_longlong, c_void_p
 from pathlib import Path
 
 import torch
 
+from .. import native
 from ..errors import FormatError
 
 DTYPES = {
@@ -22,52 +27,37 @@ DTYPES = {
     "U8": torch.uint8, "BOOL": torch.bool,
 }
 NAMES = {v: k for k, v in DTYPES.items()}
-_MAX_HEADER = 100 << 20
 
 
 class SafetensorsFile:
-    """A memory-mapped safetensors file; `tensor(name)` is a view of the map."""
+    """A memory-mapped safetensors file; `tensor(name)` is a view of the map
+    (the map stays until the last such tensor is gone)."""
 
     def __init__(self, path):
         self.path = Path(path)
-        if not self.path.is_file():
-            raise FormatError(f"{self.path}: no such file")
-        size = self.path.stat().st_size
-        if size < 8:
-            raise FormatError(f"{self.path}: too short to be a safetensors file")
-        self._handle = open(self.path, "rb")
-        self._map = mmap.mmap(self._handle.fileno(), 0, access=mmap.ACCESS_READ)
-        (header_len,) = struct.unpack("<Q", self._map[:8])
-        if header_len > min(size - 8, _MAX_HEADER):
-            raise FormatError(f"{self.path}: header length {header_len} exceeds the file")
-        try:
-            header = json.loads(self._map[8:8 + header_len].decode("utf-8"))
-        except (UnicodeDecodeError, json.JSONDecodeError) as error:
-            raise FormatError(f"{self.path}: header is not JSON ({error})") from None
-        if not isinstance(header, dict):
-            raise FormatError(f"{self.path}: header is not an object")
-        self.metadata = header.pop("__metadata__", None) or {}
-        self._data_start = 8 + header_len
-        self.entries = {}
-        for name, entry in header.items():
-            try:
-                dtype = entry["dtype"]
-                shape = tuple(int(d) for d in entry["shape"])
-                begin, end = (int(v) for v in entry["data_offsets"])
-            except (KeyError, TypeError, ValueError):
-                raise FormatError(f"{self.path}: malformed entry for '{name}'") from None
-            if dtype not in DTYPES:
-                raise FormatError(f"{self.path}: '{name}' has unknown dtype {dtype}")
-            count = 1
-            for d in shape:
-                count *= d
-            width = torch.empty((), dtype=DTYPES[dtype]).element_size()
-            if begin < 0 or end < begin or self._data_start + end > size:
-                raise FormatError(f"{self.path}: '{name}' lies outside the file")
-            if end - begin != count * width:
-                raise FormatError(f"{self.path}: '{name}' holds {end - begin} bytes, "
-                                  f"its shape {list(shape)} needs {count * width}")
-            self.entries[name] = (dtype, shape, begin, end)
+        lib = native.lib()
+        handle = c_void_p()
+        native.check(lib.llmh_safetensors_open(str(self.path).encode(), byref(handle)))
+        self._handle = handle
+        self.entries = {}                      # name -> (dtype name, shape, address, bytes)
+        name, dtype, rank = c_char_p(), c_char_p(), c_int()
+        shape, address, nbytes = POINTER(c_longlong)(), c_void_p(), c_longlong()
+        for i in range(lib.llmh_safetensors_count(handle)):
+            native.check(lib.llmh_safetensors_entry(handle, i, byref(name), byref(dtype), byref(rank),
+                                                    byref(shape), byref(address), byref(nbytes)))
+            self.entries[name.value.decode("utf-8")] = (
+                dtype.value.decode(), tuple(shape[d] for d in range(rank.value)), address.value, nbytes.value)
+        self.metadata = {}
+        key, value = c_char_p(), c_char_p()
+        for i in range(lib.llmh_safetensors_metadata_count(handle)):
+            native.check(lib.llmh_safetensors_metadata_item(handle, i, byref(key), byref(value)))
+            self.metadata[key.value.decode("utf-8")] = value.value.decode("utf-8")
+
+    def __del__(self):
+        handle = getattr(self, "_handle", None)
+        if handle:
+            native.lib().llmh_safetensors_close(handle)
+            self._handle = None
 
     def names(self):
         return list(self.entries)
@@ -79,11 +69,11 @@ class SafetensorsFile:
         return DTYPES[self.entries[name][0]]
 
     def tensor(self, name) -> torch.Tensor:
-        dtype, shape, begin, end = self.entries[name]
-        if end == begin:
+        dtype, shape, address, nbytes = self.entries[name]
+        if nbytes == 0:
             return torch.empty(shape, dtype=DTYPES[dtype])
-        view = memoryview(self._map)[self._data_start + begin:self._data_start + end]
-        import warnings
+        view = (ctypes.c_ubyte * nbytes).from_address(address)
+        view._file = self                          # the tensor's storage keeps `view`, and so the map, alive
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")       # the map is read-only; tensors are only read
             flat = torch.frombuffer(view, dtype=DTYPES[dtype])
