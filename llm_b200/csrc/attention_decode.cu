@@ -50,6 +50,11 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [STAGES][2][64][LDS]
 
+    // The kernel before this one in a step writes the queries and the newest position of the
+    // cache; lengths, page tables and every older page are already final. So the first pages of
+    // this block's slice are fetched before griddep_wait(), except the page that holds the
+    // newest position.
+    griddep_launch();
     int split = blockIdx.x, n_splits = gridDim.x, kv_head = blockIdx.y, seq = blockIdx.z;
     int group = n_heads / n_kv_heads;
     int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -59,18 +64,6 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     int page_begin = min(split * per_split, n_pages);
     int page_end = min(page_begin + per_split, n_pages);
     const int* pages = block_table + (size_t)seq * table_stride;
-
-    // Q fragments of this warp's lane: row g = head kv_head * group + g (zero beyond the group)
-    uint32_t qa0[D / 16], qa2[D / 16];
-    {
-        const __nv_bfloat16* q_row = q + (size_t)seq * q_stride + (size_t)(kv_head * group + g) * D;
-        bool valid = g < group;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            qa0[ks] = valid ? *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + 2 * t) : 0u;
-            qa2[ks] = valid ? *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + 8 + 2 * t) : 0u;
-        }
-    }
 
     auto load_page = [&](int logical_page, int stage) {
         int page = pages[logical_page % ring_pages];
@@ -84,6 +77,33 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             cp_async16(vs + row * LDS + col, v_cache + base + (size_t)row * D + col);
         }
     };
+    int n_my = page_end - page_begin;
+    int late_stage = -1;                            // stage of the newest page, if it is among the first
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_my) {
+            if (page_begin + s == n_pages - 1) late_stage = s;
+            else load_page(page_begin + s, s);
+        }
+        cp_async_commit();
+    }
+    griddep_wait();
+    if (late_stage >= 0) {
+        load_page(page_begin + late_stage, late_stage);
+        cp_async_commit();
+    }
+
+    // Q fragments of this warp's lane: row g = head kv_head * group + g (zero beyond the group)
+    uint32_t qa0[D / 16], qa2[D / 16];
+    {
+        const __nv_bfloat16* q_row = q + (size_t)seq * q_stride + (size_t)(kv_head * group + g) * D;
+        bool valid = g < group;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qa0[ks] = valid ? *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + 2 * t) : 0u;
+            qa2[ks] = valid ? *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
 
     float acc[D / 8][4];
 #pragma unroll
@@ -92,14 +112,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
     float run_max = -INFINITY, run_sum = 0.f;      // for head row g (this lane's keys only for the sum)
 
-    int n_my = page_end - page_begin;
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_my) load_page(page_begin + s, s);
-        cp_async_commit();
-    }
     for (int i = 0; i < n_my; ++i) {
-        cp_async_wait<STAGES - 2>();
+        // the newest page, fetched late, is the last of its slice and the youngest group
+        if (late_stage >= 0 && i == n_my - 1) cp_async_wait<0>();
+        else cp_async_wait<STAGES - 2>();
         __syncthreads();                            // page i landed; everyone is done with page i - 1
         if (i + STAGES - 1 < n_my) load_page(page_begin + i + STAGES - 1, (i + STAGES - 1) % STAGES);
         cp_async_commit();
@@ -191,6 +207,8 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_a
                                                 const float* __restrict__ part_stats,
                                                 __nv_bfloat16* __restrict__ out, int out_stride,
                                                 int n_heads, int n_splits) {
+    griddep_launch();
+    griddep_wait();
     int seq = blockIdx.y, head = blockIdx.x;
     size_t base = ((size_t)seq * n_heads + head) * n_splits;
     float m = -INFINITY;
@@ -225,14 +243,14 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     float* part_acc = scratch;
     float* part_stats = scratch + (size_t)n_seqs * n_heads * n_splits * D;
     dim3 grid(n_splits, n_kv_heads, n_seqs);
-    attention_decode_split_kernel<D><<<grid, WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
-        (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, part_acc,
-        part_stats, n_heads, n_kv_heads, scale * 1.4426950408889634f);
+    llmb::launch(attention_decode_split_kernel<D>, grid, WARPS * 32, smem, stream, true,
+                 (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
+                 (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, part_acc,
+                 part_stats, n_heads, n_kv_heads, scale * 1.4426950408889634f);
     int code = check_launch("attention_decode_split");
     if (code) return code;
-    attention_decode_combine_kernel<D><<<dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream>>>(
-        part_acc, part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_splits);
+    llmb::launch(attention_decode_combine_kernel<D>, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, true,
+                 (const float*)part_acc, (const float*)part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_splits);
     return check_launch("attention_decode_combine");
 }
 

@@ -99,6 +99,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+    griddep_launch();            // the next kernel may set itself up; this one needs the one before it whole
+    griddep_wait();
     int seq = blockIdx.z, head = blockIdx.y;
     int first_token = cu_seqlens[seq];
     int n_new = cu_seqlens[seq + 1] - first_token;
@@ -353,9 +355,9 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap
     int* status_dev = nullptr;
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
     dim3 grid((max_new + BQ - 1) / BQ, n_heads, n_seqs);
-    attention_prefill_tc_kernel<HD><<<grid, THREADS, smem, stream>>>(
-        map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens,
-        (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f, status_dev);
+    llmb::launch(attention_prefill_tc_kernel<HD>, grid, THREADS, smem, stream, true,
+                 map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens,
+                 (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f, status_dev);
     return check_launch("attention_prefill_tc");
 }
 }  // namespace

@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 
 #define LLMB_OK 0
 #define LLMB_ERR_ARGUMENT 1    // a size or option this kernel refuses
@@ -68,6 +69,9 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
@@ -80,6 +84,38 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// Programmatic dependent launch: a kernel launched with `dependent` may begin while the kernel
+// before it in the stream is still running, once every block of that kernel has called
+// griddep_launch() (or has exited). Everything it does before its own griddep_wait() overlaps the
+// predecessor, so that part may only touch what no kernel of a step writes: weights and its own
+// shared memory. griddep_wait() returns when the predecessor has completed and its writes are
+// visible. Both calls do nothing in a kernel launched the plain way. LLMB_NO_PDL=1 turns every
+// launch into a plain one.
+inline bool pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* off = std::getenv("LLMB_NO_PDL");
+        enabled = (off && off[0] && off[0] != '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          bool dependent, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = (dependent && pdl_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
 
 }  // namespace llmb
 

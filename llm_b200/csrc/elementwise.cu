@@ -17,6 +17,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
                              float* __restrict__ x, int hidden, int vocab, int vector) {
     int t = blockIdx.x;
     int token = tokens[t];
+    griddep_launch();
     if (token < 0 || token >= vocab) token = 0;   // host checks ids; device-sampled ids are in range
     const T* row = table + (size_t)token * hidden;
     float* out = x + (size_t)t * hidden;
@@ -66,6 +67,8 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
     // PER_THREAD > 0: hidden is a multiple of 4 and at most 1024 * PER_THREAD; every thread
     // keeps its PER_THREAD float4 of the row in registers (all loads in flight at once).
     // PER_THREAD == 0: any width, the row is read twice.
+    griddep_launch();
+    griddep_wait();
     int r = blockIdx.x;
     int src = rows ? rows[r] : r;
     const float* in = x + (size_t)src * hidden;
@@ -131,11 +134,11 @@ static void launch_rmsnorm(const float* x, const float* gain, const int* rows, T
                            int hidden, float eps, cudaStream_t stream) {
     bool vector = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(gain) & 15) == 0;
-    if (vector && hidden <= 1024) rmsnorm_kernel<TOut, 1><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
-    else if (vector && hidden <= 2048) rmsnorm_kernel<TOut, 2><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
-    else if (vector && hidden <= 4096) rmsnorm_kernel<TOut, 4><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
-    else if (vector && hidden <= 8192) rmsnorm_kernel<TOut, 8><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
-    else rmsnorm_kernel<TOut, 0><<<n_rows, 256, 0, stream>>>(x, gain, rows, out, hidden, eps);
+    if (vector && hidden <= 1024) llmb::launch(rmsnorm_kernel<TOut, 1>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
+    else if (vector && hidden <= 2048) llmb::launch(rmsnorm_kernel<TOut, 2>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
+    else if (vector && hidden <= 4096) llmb::launch(rmsnorm_kernel<TOut, 4>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
+    else if (vector && hidden <= 8192) llmb::launch(rmsnorm_kernel<TOut, 8>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
+    else llmb::launch(rmsnorm_kernel<TOut, 0>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
 }
 
 LLMB_EXPORT int llmb_rmsnorm(const float* x, const float* gain, const int* rows, void* out,
@@ -210,6 +213,8 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__
                       const int* __restrict__ block_table, int table_stride, int ring_pages,
                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                       int n_heads, int n_kv_heads, int head_dim, int interleaved, int write_cache) {
+    griddep_launch();
+    griddep_wait();
     int t = blockIdx.x;
     int pos = tok_pos[t];
     int half = head_dim >> 1;
@@ -290,10 +295,10 @@ LLMB_EXPORT int llmb_rope_cache_write(void* qkv, int dtype, const float* table,
     if (dtype == LLMB_DTYPE_BF16 && head_dim % 16 == 0 &&
         ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) |
           reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0) {
-        rope_cache_vec_kernel<<<n_tokens, 256, 0, stream>>>(
-            (__nv_bfloat16*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim, interleaved,
-            write_cache);
+        llmb::launch(rope_cache_vec_kernel, n_tokens, 256, 0, stream, true,
+                     (__nv_bfloat16*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
+                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim, interleaved,
+                     write_cache);
         return check_launch("rope_cache_write");
     }
     dim3 grid(n_tokens, n_heads + 2 * n_kv_heads);

@@ -309,6 +309,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tcgen05_fence_after();
     uint32_t tmem_base = *tmem_slot;
 
+    // Let the next kernel of the stream set itself up, and fetch this block's first weight tiles
+    // (no kernel writes weights), while the kernel before this one is still running; the
+    // activations, the residual and the split-K scratch are touched only after griddep_wait().
+    griddep_launch();
+    uint32_t early = 0;                                         // k-blocks whose weight tile is on its way
+    if (warp == 0 && lane == 0 && (int)blockIdx.x < n_units) {
+        Unit w = unit_of(blockIdx.x, tiles_a, splits);
+        int kb_begin = w.split * kblocks_per_split;
+        int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
+        early = (uint32_t)min(stages, kb_end - kb_begin);
+        for (uint32_t i = 0; i < early; ++i) {
+            uint32_t bar = smem_u32(&full_bar[i]);
+            mbar_expect_tx(bar, A_BYTES + B_BYTES);
+            if (swap) tma_load_2d(smem_u32(a_tiles + (size_t)i * A_BYTES), &map_a, bar, (kb_begin + i) * BK, w.tile_a * BM);
+            else tma_load_2d(smem_u32(b_tiles + (size_t)i * B_BYTES), &map_b, bar, (kb_begin + i) * BK, w.tile_b * BN);
+        }
+    }
+    griddep_wait();
+
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;                                    // k-blocks issued so far, over all units
@@ -320,9 +339,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     int s = it % stages;
                     uint32_t round = it / stages;
+                    uint32_t bar = smem_u32(&full_bar[s]);
+                    if (it < early) {                           // armed above, the weight tile is in flight
+                        if (swap) tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, kb * BK, w.tile_b * BN);
+                        else tma_load_2d(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a, bar, kb * BK, w.tile_a * BM);
+                        continue;
+                    }
                     ok = mbar_wait(smem_u32(&empty_bar[s]), (round & 1) ^ 1, abort_flag, status, 1);
                     if (!ok) break;
-                    uint32_t bar = smem_u32(&full_bar[s]);
                     mbar_expect_tx(bar, A_BYTES + B_BYTES);
                     tma_load_2d(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a, bar, kb * BK, w.tile_a * BM);
                     tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, kb * BK, w.tile_b * BN);
@@ -590,6 +614,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tcgen05_fence_after();
     uint32_t tmem_base = *tmem_slot;
 
+    // As in gemm_tc_kernel: the first weight tiles (operand B here) are fetched while the kernel
+    // before this one may still be running; the tokens only after griddep_wait().
+    griddep_launch();
+    uint32_t early = 0;
+    if (warp == 0 && lane == 0 && pair < n_units) {
+        Unit w = unit_of(pair, tiles_a, 1);
+        early = (uint32_t)min(stages, n_kblocks);
+        for (uint32_t i = 0; i < early; ++i) {
+            if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[i]), 2 * (A_BYTES + B_BYTES));
+            uint32_t bar = map_to_rank(smem_u32(&full_bar[i]), 0);
+            tma_load_2d_pair(smem_u32(b_tiles + (size_t)i * B_BYTES), &map_b, bar, (int)i * BK,
+                             w.tile_b * PAIR_BN + (int)rank * (PAIR_BN / 2));
+        }
+    }
+    griddep_wait();
+
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;
@@ -599,6 +639,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int kb = 0; kb < n_kblocks; ++kb, ++it) {
                     int s = it % stages;
                     uint32_t round = it / stages;
+                    if (it < early) {                           // armed above, the weight tile is in flight
+                        tma_load_2d_pair(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a,
+                                         map_to_rank(smem_u32(&full_bar[s]), 0), kb * BK,
+                                         w.tile_a * 2 * BM + (int)rank * BM);
+                        continue;
+                    }
                     ok = mbar_wait(smem_u32(&empty_bar[s]), (round & 1) ^ 1, abort_flag, status, 1);
                     if (!ok) break;
                     // both blocks' bytes are counted on block 0's barrier
@@ -783,8 +829,8 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
     int n_units = tiles_a * tiles_b * splits;
     int grid = n_units < n_sms * blocks_per_sm ? n_units : n_sms * blocks_per_sm;
-    gemm_tc_kernel<BN><<<grid, THREADS, smem, stream>>>(map_a, map_b, ep, swap, n_kblocks, per_split, splits,
-                                                        tiles_a, n_units, partials, counters, status_dev, stages);
+    llmb::launch(gemm_tc_kernel<BN>, grid, THREADS, smem, stream, true, map_a, map_b, ep, swap, n_kblocks, per_split,
+                 splits, tiles_a, n_units, partials, counters, status_dev, stages);
     return check_launch("gemm_tc");
 }
 
@@ -810,8 +856,8 @@ int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilog
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
     int n_units = tiles_a * tiles_b;
     int pairs = n_units < n_sms / 2 ? n_units : n_sms / 2;
-    gemm_tc_pair_kernel<<<2 * pairs, THREADS, smem, stream>>>(map_a, map_b, ep, n_kblocks, tiles_a, n_units,
-                                                             status_dev, stages);
+    llmb::launch(gemm_tc_pair_kernel, 2 * pairs, THREADS, smem, stream, true, map_a, map_b, ep, n_kblocks, tiles_a,
+                 n_units, status_dev, stages);
     return check_launch("gemm_tc_pair");
 }
 
