@@ -31,8 +31,15 @@ using namespace llmb;
 LLMB_DEFINE_LAST_ERROR(llmb_attention_decode)
 
 constexpr int WARPS = 4;
-constexpr int STAGES = 3;
 constexpr int PAD = 8;                       // bf16 elements of row padding (bank spread)
+// Pages in the ring of a block: as many as fit in about 110 KB (two blocks an SM), between 3 and 8.
+// A small head size has small pages; it needs more of them in flight to keep HBM busy.
+template <int D>
+__host__ __device__ constexpr int stages_for() {
+    constexpr int bytes = 2 * LLMB_PAGE * (D + PAD) * 2;
+    constexpr int fit = (110 * 1024) / bytes;
+    return fit < 3 ? 3 : fit > 8 ? 8 : fit;
+}
 
 // partial layout: acc [seq, head, split, D] floats; stats [seq, head, split, 2] = (max, sum),
 // max in base-2 units (score * scale * log2 e).
@@ -43,10 +50,11 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               const __nv_bfloat16* __restrict__ v_cache,
                               const int* __restrict__ block_table, int table_stride, int ring_pages,
                               const int* __restrict__ seq_lens, float* __restrict__ part_acc,
-                              float* __restrict__ part_stats, int n_heads, int n_kv_heads,
-                              float scale_log2) {
+                              float* __restrict__ part_stats, __nv_bfloat16* __restrict__ out, int out_stride,
+                              int n_heads, int n_kv_heads, float scale_log2) {
     constexpr int LDS = D + PAD;
     constexpr int PAGE_ELEMS = LLMB_PAGE * LDS;
+    constexpr int STAGES = stages_for<D>();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [STAGES][2][64][LDS]
 
@@ -196,6 +204,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             value += merge_acc[(w * 8 + head) * D + d] * weight;
             sum += merge_sum[w * 8 + head] * weight;
         }
+        if (n_splits == 1) {                          // nothing to combine: this is the result
+            out[(size_t)seq * out_stride + (size_t)(kv_head * group + head) * D + d] = __float2bfloat16_rn(value / sum);
+            continue;
+        }
         size_t slot = ((size_t)seq * n_heads + kv_head * group + head) * n_splits + split;
         part_acc[slot * D + d] = value;
         if (d == 0) { part_stats[slot * 2] = m; part_stats[slot * 2 + 1] = sum; }
@@ -231,6 +243,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                   void* out, int out_stride, float* scratch, int n_seqs, int n_heads, int n_kv_heads,
                   float scale, int n_splits, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
+    constexpr int STAGES = stages_for<D>();
     size_t stage_bytes = (size_t)STAGES * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
     size_t merge_bytes = (size_t)(WARPS * 8 * D + 2 * WARPS * 8) * sizeof(float);
     size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
@@ -246,9 +259,9 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     llmb::launch(attention_decode_split_kernel<D>, grid, WARPS * 32, smem, stream, true,
                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
                  (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, part_acc,
-                 part_stats, n_heads, n_kv_heads, scale * 1.4426950408889634f);
+                 part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f);
     int code = check_launch("attention_decode_split");
-    if (code) return code;
+    if (code || n_splits == 1) return code;
     llmb::launch(attention_decode_combine_kernel<D>, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, true,
                  (const float*)part_acc, (const float*)part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_splits);
     return check_launch("attention_decode_combine");

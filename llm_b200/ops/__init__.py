@@ -292,8 +292,11 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     attention. Blocks are (slice, kv head, sequence) and two fit on an SM: the
     count is the largest power of two that keeps all blocks in one wave of
     2 x 148 (measured on a B200 at 8,192 positions: batch 8 is fastest with 4
-    slices = 256 blocks, batch 1 with 16 to 32), four when the batch alone
-    exceeds a wave, and never less than two pages a slice. It depends on the
+    slices = 256 blocks, batch 1 with 16 to 32), and never less than two pages
+    a slice. When the batch alone exceeds a wave, slices only help long
+    sequences (batch 64: 334 against 352 us at 8,192 positions with four, but
+    39 against 28 us at 512): four from 128 pages, else one, which also skips
+    the combining kernel. It depends on the
     length only through the power-of-two bucket of its page count, so that all
     steps replayed from one captured graph agree on it."""
     if os.environ.get("LLMB_DECODE_SPLITS"):             # for measurements: force a slice count
@@ -301,7 +304,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     floor_pages = 1 << (pages.bit_length() - 1)
     pairs = max(1, n_seqs * n_kv_heads)
-    want = 296 // pairs if pairs < 296 else 4
+    want = 296 // pairs if pairs < 296 else (4 if floor_pages >= 128 else 1)
     splits = 1
     while splits * 2 <= want and splits * 2 <= 32:
         splits *= 2
@@ -353,7 +356,7 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
               _c_int(ring_pages), _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)), _ptr(scratch),
               ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
               _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream(),
-              kernels=2)
+              kernels=2 if splits > 1 else 1)
     elif variant == "attention_generic":
         _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),

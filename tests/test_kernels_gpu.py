@@ -265,9 +265,14 @@ def test_attention_prefill_and_decode(dtype, heads, kv_heads, dim, window):
 
 @pytest.mark.parametrize("heads,kv_heads,dim", [(32, 8, 128), (8, 1, 64), (6, 2, 96), (4, 4, 32),
                                                 (3, 1, 128)])
-def test_attention_decode_kernel_long_contexts(heads, kv_heads, dim):
+@pytest.mark.parametrize("forced_slices", [0, 1, 2, 16])
+def test_attention_decode_kernel_long_contexts(heads, kv_heads, dim, forced_slices, monkeypatch):
     """The split-KV decode kernel at lengths from 1 to 3000 in one batch (page edges,
-    empty slices, many slices), twice in a row on the same scratch."""
+    empty slices, many slices), twice in a row on the same scratch; with the library's own
+    choice of slices and with forced counts (one slice writes the result without the
+    combining kernel)."""
+    if forced_slices:
+        monkeypatch.setenv("LLMB_DECODE_SPLITS", str(forced_slices))
     from llm_b200.ops import tactics
     dtype = torch.bfloat16
     assert tactics.choose_attention(True, dtype, heads, kv_heads, dim, 0) == "attention_decode"
