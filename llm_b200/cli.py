@@ -11,7 +11,8 @@ defaults; text and tokenizers are outside this library). `bench` keeps the
 flags of apps/cli/src/bench.rs:45-71 (-m, -c, -p, -n, -r, -o with comma lists)
 and its two tests: `pp<N>` times the prefill of N tokens and nothing else,
 `tg<N>` prefills a 16-token prompt and times only the decoding of N tokens
-(bench.rs:10-12,27); `-b` adds the batch size. `inspect` prints the model's
+(bench.rs:10-12,27); `-b` adds the batch size; every test runs once uncounted before its `-r`
+repetitions. `inspect` prints the model's
 geometry, checks the checkpoint's tensors and names the kernel variant each
 product and attention shape gets (apps/cli/src/inspect.rs:16-131).
 """
@@ -137,23 +138,25 @@ def bench(args) -> int:
         engine = Engine(model, max_tokens=batch * per_seq, max_seq_len=context, max_slots=batch)
         for n in prompts:
             samples = []
-            for _ in range(reps):
+            for rep in range(reps + 1):            # the first run is not counted: it plans the scratch
                 slots = engine.acquire(batch)
                 torch.cuda.synchronize()
                 started = time.perf_counter()
                 engine.step([Entry(s, filler[:n], [n - 1]) for s in slots])
                 torch.cuda.synchronize()
-                samples.append(batch * n / (time.perf_counter() - started))
+                if rep:
+                    samples.append(batch * n / (time.perf_counter() - started))
                 engine.release(slots)
             rows.append((f"pp{n}", batch, samples))
         for n in (g for g in gens if g > 0):
             samples = []
-            for _ in range(reps):
+            for rep in range(reps + 1):            # the first run is not counted: it captures the graphs
                 requests = [GenerationRequest(filler[:TG_PROMPT], n + 1, SamplingParams(temperature=0.0))
                             for _ in range(batch)]
                 results = generate(engine, requests)
                 decode_s = max(r.decode_ms for r in results) * 1e-3
-                samples.append(batch * n / decode_s if decode_s > 0 else 0.0)
+                if rep:
+                    samples.append(batch * n / decode_s if decode_s > 0 else 0.0)
             rows.append((f"tg{n}", batch, samples))
         del engine
         torch.cuda.empty_cache()
