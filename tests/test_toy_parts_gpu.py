@@ -179,3 +179,183 @@ def test_full_and_windowed_layers_in_one_model_on_the_gpu(tmp_path, dtype):
     cut into passes of 48: the kernels' window and ring addressing against the plain form."""
     from test_window_cpu import run_windowed
     run_windowed(tmp_path, DEV, dtype, 2e-4 if dtype == torch.float32 else 0.04)
+
+
+# ----------------------------------------------------------------------------- routing, other positions
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden: int
+    intermediate: int
+    n_experts: int
+    prefix: str
+    kind: str = "toy_routed"
+
+
+@dataclass(frozen=True)
+class InterpolatedSpec:
+    """Rotary angles of position / stretch (positions squeezed into a shorter range)."""
+    head_dim: int
+    theta: float
+    max_positions: int
+    stretch: float
+    kind: str = "toy_interpolated"
+
+
+def define_routed_toy():
+    from llm_b200 import ops
+    from llm_b200.config import ConfigReader, register_architecture
+    from llm_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position
+    from llm_b200.parts.spec import (AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec,
+                                     ScheduleEntry, names)
+    from llm_b200.weights import ParamSpec
+
+    class RoutedMlp(FeedForward):
+        """Every token goes to the one expert with the largest router logit (logits in 32-bit,
+        first maximum wins); each expert is a gated MLP run with the library's products on the
+        rows that chose it."""
+
+        def __init__(self, spec):
+            self.spec = spec
+
+        def parameters(self):
+            s, out = self.spec, {}
+            out[s.prefix + "router"] = ParamSpec((s.n_experts, s.hidden))
+            for e in range(s.n_experts):
+                out[f"{s.prefix}{e}.gate"] = ParamSpec((s.intermediate, s.hidden))
+                out[f"{s.prefix}{e}.up"] = ParamSpec((s.intermediate, s.hidden))
+                out[f"{s.prefix}{e}.down"] = ParamSpec((s.hidden, s.intermediate))
+            return out
+
+        def bind(self, tensors, dtype, device):
+            s = self.spec
+            self.router = tensors[s.prefix + "router"].to(device=device, dtype=torch.float32)
+            self.experts = [tuple(tensors[f"{s.prefix}{e}.{r}"].to(device=device, dtype=dtype).contiguous()
+                                  for r in ("gate", "up", "down")) for e in range(s.n_experts)]
+
+        def forward(self, h, ctx, residual):
+            logits = h.float() @ self.router.T                      # 32-bit, whatever the run dtype
+            choice = logits.argmax(dim=1)
+            for e, (gate, up, down) in enumerate(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                x = h[rows].contiguous()
+                act = ops.swiglu(torch.cat([ops.linear(x, gate), ops.linear(x, up)], dim=1))
+                update = torch.zeros((rows.numel(), self.spec.hidden), dtype=torch.float32, device=h.device)
+                ops.linear(act, down, residual=update)
+                residual[rows] += update
+
+    register_feed_forward("toy_routed", RoutedMlp)
+
+    class InterpolatedRope(PositionEncoding):
+        interleaved = True
+
+        def __init__(self, spec):
+            self.spec = spec
+            self.table = None
+
+        def prepare(self, max_positions, device):
+            s = self.spec
+            n = min(max_positions, s.max_positions)
+            inv = torch.pow(torch.tensor(s.theta, dtype=torch.float64),
+                            -2.0 * torch.arange(s.head_dim // 2, dtype=torch.float64) / s.head_dim)
+            angle = (torch.arange(n, dtype=torch.float64) / s.stretch)[:, None] * inv[None, :]
+            self.table = torch.cat([angle.cos(), angle.sin()], 1).float().to(device).contiguous()
+
+    register_position("toy_interpolated", InterpolatedRope)
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        hidden: int
+        vocab: int
+        experts: int
+        stretch: float
+
+        @classmethod
+        def from_dict(cls, raw, where="config.json"):
+            r = ConfigReader(raw, where)
+            return cls(r.integer("hidden"), r.integer("vocab"), r.integer("experts"), r.number("stretch"))
+
+        def to_dict(self):
+            return {"architectures": ["ToyRouted"], "hidden": self.hidden, "vocab": self.vocab,
+                    "experts": self.experts, "stretch": self.stretch}
+
+        def model_spec(self):
+            h = self.hidden
+            positions = (InterpolatedSpec(16, 10000.0, 512, self.stretch), None)   # layer 1: no encoding
+            def block(i):
+                p = f"layers.{i}."
+                attention = AttentionSpec(hidden=h, n_heads=3, n_kv_heads=1, head_dim=16, scale=0.25,
+                                          bias=False, window=0, position=positions[i],
+                                          names=names(q=p + "q", k=p + "k", v=p + "v", o=p + "o"))
+                return BlockSpec(NormSpec(h, 1e-6, p + "n1"), attention, NormSpec(h, 1e-6, p + "n2"),
+                                 RoutedSpec(h, 24, self.experts, p + "experts."))
+            blocks = (block(0), block(1))
+            return ModelSpec("ToyRouted", self.vocab, h, 512, "embed", blocks,
+                             (ScheduleEntry(0), ScheduleEntry(1)), NormSpec(h, 1e-6, "final_norm"), "head")
+
+    register_architecture("ToyRouted", RoutedConfig)
+    return RoutedConfig
+
+
+def plain_routed(config, w, tokens):
+    import plain_llama as P
+    n = len(tokens)
+    x = P.embedding(w["embed"], tokens)
+    inv_freq = P.rope_inverse_frequencies(16, 10000.0)
+    squeezed = [p / config.stretch for p in range(n)]
+    choices = []
+    for i in range(2):
+        p = f"layers.{i}."
+        hn = P.rms_norm(x, w[p + "n1"], 1e-6)
+        q, k = (hn @ w[p + "q"].T).view(n, 3, 16), (hn @ w[p + "k"].T).view(n, 1, 16)
+        if i == 0:
+            q = P.rope_rotate(q, squeezed, inv_freq, "interleaved")
+            k = P.rope_rotate(k, squeezed, inv_freq, "interleaved")
+        v = (hn @ w[p + "v"].T).view(n, 1, 16)
+        x = x + P.causal_attention(q, k, v, 0.25).reshape(n, 48) @ w[p + "o"].T
+        hn = P.rms_norm(x, w[p + "n2"], 1e-6)
+        choice = (hn @ w[p + "experts.router"].T).argmax(dim=1)
+        update = torch.zeros_like(x)
+        for t in range(n):
+            e = int(choice[t])
+            update[t] = P.gated_mlp(hn[t:t + 1], w[f"{p}experts.{e}.gate"], w[f"{p}experts.{e}.up"],
+                                    w[f"{p}experts.{e}.down"])[0]
+        x = x + update
+        choices.append(choice)
+    return P.rms_norm(x, w["final_norm"], 1e-6) @ w["head"].T, choices
+
+
+def test_routed_feed_forward_and_other_position_encodings(tmp_path):
+    """A feed-forward that routes every token to one of three experts, a rotary encoding with
+    squeezed positions, and a layer without any position encoding: registered from here, built by
+    the library's loader and stepped (prompts, then token by token) in 32-bit against their plain
+    form. Every expert must have been chosen, or the test would not test routing."""
+    import plain_llama
+    from llm_b200.engine import Engine, Entry, load_model
+    from llm_b200.weights import write_random_model
+    RoutedConfig = define_routed_toy()
+    config = RoutedConfig(hidden=48, vocab=150, experts=3, stretch=4.0)
+    folder = write_random_model(tmp_path / "routed", config, seed=5, dtype=torch.float32, std=0.3)
+    _, weights = plain_llama.read_model_folder(folder)
+    model = load_model(folder, torch.float32, DEV)
+    engine = Engine(model, max_tokens=512)
+    seqs = [random_tokens(n, 150, 40 + n) for n in (33, 6)]
+    slots = engine.acquire(2)
+    heads = [len(s) - 3 for s in seqs]
+    logits = engine.step([Entry(sl, s[:n], list(range(n))) for sl, s, n in zip(slots, seqs, heads)])
+    got = [[logits[:heads[0]]], [logits[heads[0]:]]]
+    for k in range(3):
+        step = engine.step([Entry(sl, [s[n + k]], [0]) for sl, s, n in zip(slots, seqs, heads)])
+        for b in range(2):
+            got[b].append(step[b:b + 1])
+    seen = set()
+    for b in range(2):
+        want, choices = plain_routed(config, weights, seqs[b])
+        for choice in choices:
+            seen |= set(choice.tolist())
+        g = torch.cat(got[b]).cpu()
+        assert float((g - want).abs().max()) <= 2e-4 * max(float(want.abs().max()), 1.0), b
+    assert seen == {0, 1, 2}
+    engine.release(slots)
