@@ -60,7 +60,7 @@ def test_whole_request(folders, plain, dtype, which):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B", "D", "E"])
+@pytest.mark.parametrize("which", ["A", "B", "D", "E", "F"])
 def test_last_32_tokens_one_by_one(folders, plain, dtype, which):
     from llm_b200.engine import Entry
     config, weights = plain[which]
@@ -76,7 +76,7 @@ def test_last_32_tokens_one_by_one(folders, plain, dtype, which):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["A", "B", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "D", "F"])
 def test_unequal_batches_with_slot_reuse(folders, plain, dtype, which):
     """Two batches one after the other on a cache that holds only one of them:
     the second batch gets the first one's slots and pages back."""
@@ -109,7 +109,7 @@ def test_unequal_batches_with_slot_reuse(folders, plain, dtype, which):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("which", ["C", "D"])
+@pytest.mark.parametrize("which", ["C", "D", "F"])
 def test_long_decoding(folders, plain, dtype, which):
     """300 decode steps after a 40-token prompt, across several pages, beside a
     second sequence that grows from 1 token."""
@@ -129,6 +129,39 @@ def test_long_decoding(folders, plain, dtype, which):
         got_b.append(logits[1])
     assert close(torch.stack(got_a), expect_a[40:], dtype)
     assert close(torch.stack(got_b), expect_b[1:], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_family_shaped_model_prefill_and_decode(folders, plain, dtype):
+    """Head size 128 with four query heads per kv head, prompts long enough for the paired
+    tcgen05 product (more than 128 tokens), for several key blocks of the tcgen05 attention
+    and for the llama3 frequency bands; then the split decode attention one token at a time."""
+    from llm_b200.engine import Entry
+    from llm_b200.ops import tactics
+    config, weights = plain["F"]
+    if dtype == torch.bfloat16:
+        assert tactics.choose_attention(False, dtype, 4, 1, 128, 0, True) == "attention_prefill_tc"
+        assert tactics.choose_attention(True, dtype, 4, 1, 128, 0) == "attention_decode"
+        assert tactics.choose_linear(330, 768, 512, dtype, dtype, 512) == "gemm_tc"
+    engine = engine_for(folders["F"], dtype)
+    seqs = [random_tokens(n, config["vocab_size"], 300 + n) for n in (330, 140, 1)]
+    expected = [plain_llama.forward(config, weights, s) for s in seqs]
+    slots = engine.acquire(3)
+    heads = [322, 132, 1]
+    wanted = [[0, 127, 128, 255, 321], [0, 131], [0]]
+    logits = engine.step([Entry(sl, s[:n], w) for sl, s, n, w in zip(slots, seqs, heads, wanted)])
+    row = 0
+    for b in range(3):
+        for w in wanted[b]:
+            assert close(logits[row], expected[b][w], dtype), (b, w)
+            row += 1
+    for k in range(8):                       # the third request has ended
+        step = engine.step([Entry(slots[b], [seqs[b][heads[b] + k]], [0]) for b in range(2)])
+        for b in range(2):
+            assert close(step[b], expected[b][heads[b] + k], dtype), (b, k)
+    engine.release(slots)
+    engine.cache.check()
+    engine.check()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

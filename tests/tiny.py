@@ -57,7 +57,22 @@ TINY_E = {
     "attention_bias": False, "max_position_embeddings": 512, "hidden_act": "silu",
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
+# the head size, grouping and kind of sizes of the Llama-3 family in small: head size 128, four
+# query heads per kv head, a feed-forward width and a vocabulary that are no powers of two, llama3
+# frequency scaling whose bands lie inside the tested lengths
+TINY_F = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 4,
+    "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 1408, "vocab_size": 5000,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "attention_bias": False,
+    "max_position_embeddings": 2048, "hidden_act": "silu",
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4),
+           "F": (TINY_F, 5)}
 
 
 def make_folder(tmp_path, which: str, dtype=torch.bfloat16, std=None):
