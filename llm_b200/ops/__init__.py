@@ -293,10 +293,14 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     count is the largest power of two that keeps all blocks in one wave of
     2 x 148 (measured on a B200 at 8,192 positions: batch 8 is fastest with 4
     slices = 256 blocks, batch 1 with 16 to 32), and never less than two pages
-    a slice. When the batch alone exceeds a wave, slices only help long
-    sequences (batch 64: 334 against 352 us at 8,192 positions with four, but
-    39 against 28 us at 512): four from 128 pages, else one, which also skips
-    the combining kernel. It depends on the
+    a slice. When the batch alone exceeds a wave, slices still shorten the
+    longest block of work (sequences of a batch differ in length, and the step
+    ends with its longest slice): one slice per 16 pages of the longest
+    sequence, at most four (batch 64 at equal lengths: 28 us with one slice
+    against 39 us with four at 512 positions, 334 against 352 us with four at
+    8,192; 16 sequences of 64 to 2,176 positions with 32 kv heads decode
+    fastest with two). One slice writes the result itself and skips the
+    combining kernel. The count depends on the
     length only through the power-of-two bucket of its page count, so that all
     steps replayed from one captured graph agree on it."""
     if os.environ.get("LLMB_DECODE_SPLITS"):             # for measurements: force a slice count
@@ -304,7 +308,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     floor_pages = 1 << (pages.bit_length() - 1)
     pairs = max(1, n_seqs * n_kv_heads)
-    want = 296 // pairs if pairs < 296 else (4 if floor_pages >= 128 else 1)
+    want = 296 // pairs if pairs < 296 else min(4, max(1, floor_pages // 16))
     splits = 1
     while splits * 2 <= want and splits * 2 <= 32:
         splits *= 2
