@@ -49,8 +49,9 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               const __nv_bfloat16* __restrict__ k_cache,
                               const __nv_bfloat16* __restrict__ v_cache,
                               const int* __restrict__ block_table, int table_stride, int ring_pages,
-                              const int* __restrict__ seq_lens, float* __restrict__ part_acc,
-                              float* __restrict__ part_stats, __nv_bfloat16* __restrict__ out, int out_stride,
+                              const int* __restrict__ seq_lens, const int* __restrict__ seq_order,
+                              float* __restrict__ part_acc, float* __restrict__ part_stats,
+                              __nv_bfloat16* __restrict__ out, int out_stride,
                               int n_heads, int n_kv_heads, float scale_log2) {
     constexpr int LDS = D + PAD;
     constexpr int PAGE_ELEMS = LLMB_PAGE * LDS;
@@ -63,7 +64,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // this block's slice are fetched before griddep_wait(), except the page that holds the
     // newest position.
     griddep_launch();
-    int split = blockIdx.x, n_splits = gridDim.x, kv_head = blockIdx.y, seq = blockIdx.z;
+    // blocks start in the order of blockIdx; seq_order (optional) lists the sequences by falling
+    // length, so that the longest ones start first and the short ones fill the end of the step
+    int split = blockIdx.x, n_splits = gridDim.x, kv_head = blockIdx.y;
+    int seq = seq_order ? seq_order[blockIdx.z] : (int)blockIdx.z;
     int group = n_heads / n_kv_heads;
     int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     int len = seq_lens[seq];
@@ -240,8 +244,8 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_a
 template <int D>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                   const int* block_table, int table_stride, int ring_pages, const int* seq_lens,
-                  void* out, int out_stride, float* scratch, int n_seqs, int n_heads, int n_kv_heads,
-                  float scale, int n_splits, cudaStream_t stream) {
+                  const int* seq_order, void* out, int out_stride, float* scratch, int n_seqs, int n_heads,
+                  int n_kv_heads, float scale, int n_splits, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
     constexpr int STAGES = stages_for<D>();
     size_t stage_bytes = (size_t)STAGES * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
@@ -258,8 +262,8 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     dim3 grid(n_splits, n_kv_heads, n_seqs);
     llmb::launch(attention_decode_split_kernel<D>, grid, WARPS * 32, smem, stream, true,
                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
-                 (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, part_acc,
-                 part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f);
+                 (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order,
+                 part_acc, part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f);
     int code = check_launch("attention_decode_split");
     if (code || n_splits == 1) return code;
     llmb::launch(attention_decode_combine_kernel<D>, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, true,
@@ -285,8 +289,8 @@ LLMB_EXPORT int llmb_attention_decode_supports(int n_heads, int n_kv_heads, int 
 
 LLMB_EXPORT int llmb_attention_decode(const void* q, int q_stride, const void* k_cache,
                                       const void* v_cache, const int* block_table, int table_stride,
-                                      int ring_pages, const int* seq_lens, void* out, int out_stride,
-                                      float* scratch, long long scratch_floats, int n_seqs,
+                                      int ring_pages, const int* seq_lens, const int* seq_order, void* out,
+                                      int out_stride, float* scratch, long long scratch_floats, int n_seqs,
                                       int n_heads, int n_kv_heads, int head_dim, float scale,
                                       int window, int n_splits, cudaStream_t stream) {
     if (n_seqs == 0) return LLMB_OK;
@@ -299,7 +303,7 @@ LLMB_EXPORT int llmb_attention_decode(const void* q, int q_stride, const void* k
     LLMB_REQUIRE(scratch != nullptr && scratch_floats >= llmb_attention_decode_scratch_floats(
                                                              n_seqs, n_heads, head_dim, n_splits),
                  "attention_decode: scratch too small");
-#define ARGS q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, seq_lens, out, \
+#define ARGS q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order, out, \
              out_stride, scratch, n_seqs, n_heads, n_kv_heads, scale, n_splits, stream
     switch (head_dim) {
         case 32: return launch<32>(ARGS);

@@ -77,7 +77,8 @@ __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int table_stride, int ring_pages, const int* __restrict__ cu_seqlens,
-                            const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out, int out_stride,
+                            const int* __restrict__ seq_lens, const int* __restrict__ seq_order,
+                            __nv_bfloat16* __restrict__ out, int out_stride,
                             int n_heads, int n_kv_heads, float scale_log2, int* status) {
     constexpr int PIECES = HD / 64;
     constexpr int TILE_BYTES = PIECES * HALF_BYTES;   // Q, or the K or V of one key block
@@ -101,7 +102,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     griddep_launch();            // the next kernel may set itself up; this one needs the one before it whole
     griddep_wait();
-    int seq = blockIdx.z, head = blockIdx.y;
+    // seq_order (optional): sequences by falling length, so that the longest start first
+    int seq = seq_order ? seq_order[blockIdx.z] : (int)blockIdx.z, head = blockIdx.y;
     int first_token = cu_seqlens[seq];
     int n_new = cu_seqlens[seq + 1] - first_token;
     int n_tiles = (n_new + BQ - 1) / BQ;
@@ -340,7 +342,7 @@ namespace {
 template <int HD>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
            const int* block_table, int table_stride, int ring_pages, const int* cu_seqlens,
-           const int* seq_lens, void* out, int out_stride, int n_seqs, int max_new, int n_heads,
+           const int* seq_lens, const int* seq_order, void* out, int out_stride, int n_seqs, int max_new, int n_heads,
            int n_kv_heads, float scale, cudaStream_t stream) {
     constexpr int TILE_BYTES = (HD / 64) * HALF_BYTES;
     // never less than 80 KB, so that no third block lands on an SM and waits for tensor memory
@@ -356,7 +358,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
     dim3 grid((max_new + BQ - 1) / BQ, n_heads, n_seqs);
     llmb::launch(attention_prefill_tc_kernel<HD>, grid, THREADS, smem, stream, true,
-                 map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens,
+                 map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, seq_order,
                  (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f, status_dev);
     return check_launch("attention_prefill_tc");
 }
@@ -368,7 +370,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap
 LLMB_EXPORT int llmb_attention_prefill_tc(const void* q, int q_stride, int n_tokens, const void* k_cache,
                                           const void* v_cache, int n_pages, const int* block_table,
                                           int table_stride, int ring_pages, const int* cu_seqlens,
-                                          const int* seq_lens, void* out, int out_stride, int n_seqs,
+                                          const int* seq_lens, const int* seq_order, void* out, int out_stride, int n_seqs,
                                           int max_new, int n_heads, int n_kv_heads, int head_dim,
                                           float scale, int window, cudaStream_t stream) {
     if (n_seqs == 0 || max_new == 0) return LLMB_OK;
@@ -385,8 +387,8 @@ LLMB_EXPORT int llmb_attention_prefill_tc(const void* q, int q_stride, int n_tok
     if ((code = make_map_2d(&map_k, k_cache, cache_rows, head_dim, head_dim, 64, LLMB_PAGE))) return code;
     if ((code = make_map_2d(&map_v, v_cache, cache_rows, head_dim, head_dim, 64, LLMB_PAGE))) return code;
     if (head_dim == 64)
-        return launch<64>(map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, out,
+        return launch<64>(map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, seq_order, out,
                           out_stride, n_seqs, max_new, n_heads, n_kv_heads, scale, stream);
-    return launch<128>(map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, out,
+    return launch<128>(map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, seq_order, out,
                        out_stride, n_seqs, max_new, n_heads, n_kv_heads, scale, stream);
 }

@@ -11,7 +11,8 @@
 // R wanted rows, G cache groups:
 //   0 tokens[T]   1 positions[T]   2 entry of each token[T]   3 first token of each entry[B+1]
 //   4 length of each sequence after the step[B]   5 slots[B]   6 wanted rows[R] (indices into T)
-//   7+g page-table rows of group g [B, ring_g]
+//   7 entries in order of falling length[B] (attention takes the longest sequences first)
+//   8+g page-table rows of group g [B, ring_g]
 #include <algorithm>
 #include <vector>
 
@@ -21,7 +22,7 @@ using namespace llmh;
 
 namespace {
 
-constexpr int FIXED_SECTIONS = 7;
+constexpr int FIXED_SECTIONS = 8;
 
 long long padded(long long n) { return (n + 3) / 4 * 4; }
 
@@ -32,7 +33,7 @@ void layout(const Cache& cache, int n, const int* counts, const int* want_counts
         tokens += counts[i];
         rows += want_counts[i];
     }
-    long long fixed[FIXED_SECTIONS] = {tokens, tokens, tokens, n + 1, n, n, rows};
+    long long fixed[FIXED_SECTIONS] = {tokens, tokens, tokens, n + 1, n, n, rows, n};
     long long at = 0;
     int section = 0;
     for (; section < FIXED_SECTIONS; ++section) {
@@ -120,6 +121,7 @@ LLMH_EXPORT int llmh_step_pack(void* cache_, int n, const int* slots, const int*
         int32_t* lens = out + offsets[4];
         int32_t* slot_ids = out + offsets[5];
         int32_t* rows = out + offsets[6];
+        int32_t* order = out + offsets[7];
         long long at = 0, row_at = 0, want_at = 0;
         int decode = 1, max_len = 0;
         cu[0] = 0;
@@ -140,6 +142,8 @@ LLMH_EXPORT int llmh_step_pack(void* cache_, int n, const int* slots, const int*
             if (count != 1) decode = 0;
             max_len = std::max(max_len, start + count);
         }
+        for (int i = 0; i < n; ++i) order[i] = i;
+        std::stable_sort(order, order + n, [&](int32_t a, int32_t b) { return lens[a] > lens[b]; });
         for (size_t g = 0; g < cache.groups.size(); ++g) {
             const Group& group = cache.groups[g];
             int32_t* table = out + offsets[FIXED_SECTIONS + g];

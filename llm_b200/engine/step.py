@@ -193,7 +193,7 @@ class Engine:
         counts = list(batch.counts)
         seq_lens = host[offsets[4]:offsets[4] + batch.n].tolist()
         starts = [after - c for after, c in zip(seq_lens, counts)]
-        n_groups = n_sections - 7
+        n_groups = n_sections - 8
 
         def context(dev):
             def view(i):
@@ -202,8 +202,8 @@ class Engine:
             ctx = StepContext(
                 n_tokens=n_tokens, n_seqs=n_seqs, dtype=self.dtype, device=self.device,
                 tok_pos=view(1), tok_seq=view(2), cu_seqlens=view(3), seq_lens=view(4),
-                slot_ids=view(5), cache=self.cache,
-                block_tables=[view(7 + g).view(n_seqs, -1) for g in range(n_groups)],
+                slot_ids=view(5), seq_order=view(7), cache=self.cache,
+                block_tables=[view(8 + g).view(n_seqs, -1) for g in range(n_groups)],
                 decode=decode, new_counts=counts, starts=starts, max_len=max_len,
                 workspace=self.workspace.for_tokens(n_tokens))
             return ctx, view(0), view(6)

@@ -319,10 +319,12 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
-              max_len=0, cu_seqlens=None, max_new=0):
+              max_len=0, cu_seqlens=None, max_new=0, seq_order=None):
     """Causal grouped-query attention of the new tokens' queries (the first
     Hq * D columns of `qkv`) over the paged cache, which already holds the new
-    tokens' keys and values. Returns [T, Hq * D] in qkv's dtype."""
+    tokens' keys and values. Returns [T, Hq * D] in qkv's dtype. `seq_order`
+    (optional, int32 [B]): the sequences by falling length; the kernels that
+    take one block of work per sequence then start the longest first."""
     _require_cuda(qkv, k_cache, v_cache, block_table, tok_pos, tok_seq)
     n = qkv.shape[0]
     if out is None:
@@ -334,9 +336,9 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
         _call("attention_prefill_tc", "llmb_attention_prefill_tc", _ptr(qkv), _c_int(qkv.stride(0)),
               _c_int(n), _ptr(k_cache), _ptr(v_cache), _c_int(k_cache.shape[0]), _ptr(block_table),
               _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(cu_seqlens), _ptr(seq_lens),
-              _ptr(out), _c_int(out.stride(0)), _c_int(cu_seqlens.numel() - 1), _c_int(max_new),
-              _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_float(scale), _c_int(window),
-              _stream())
+              _ptr(seq_order), _ptr(out), _c_int(out.stride(0)), _c_int(cu_seqlens.numel() - 1),
+              _c_int(max_new), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_float(scale),
+              _c_int(window), _stream())
     elif variant == "attention_prefill":
         _call("attention_prefill", "llmb_attention_prefill", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
@@ -357,7 +359,8 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
             _attention_scratch[qkv.device] = scratch
         _call("attention_decode", "llmb_attention_decode", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
-              _c_int(ring_pages), _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)), _ptr(scratch),
+              _c_int(ring_pages), _ptr(seq_lens), _ptr(seq_order), _ptr(out), _c_int(out.stride(0)),
+              _ptr(scratch),
               ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
               _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream(),
               kernels=2 if splits > 1 else 1)

@@ -81,7 +81,8 @@ class AttentionMixer(Mixer):
                               s.n_kv_heads, s.head_dim, s.scale, s.window, out=ctx.scratch("mixed"),
                               decode=ctx.decode,
                               seq_lens=ctx.seq_lens, max_len=ctx.max_len,
-                              cu_seqlens=ctx.cu_seqlens, max_new=max(ctx.new_counts))
+                              cu_seqlens=ctx.cu_seqlens, max_new=max(ctx.new_counts),
+                              seq_order=ctx.seq_order)
         ops.linear(mixed, self.w_o, self.b_o, residual=residual)
 
 

@@ -42,6 +42,7 @@ class StepContext:
     starts: list                   # host: position of each sequence's first new token
     max_len: int                   # host: longest sequence after this step
     workspace: object = None       # engine.workspace.Views of this step, or None
+    seq_order: torch.Tensor = None # [B] the sequences by falling length (work lists start the longest first)
     extras: dict = field(default_factory=dict)
 
     def scratch(self, name: str):

@@ -91,7 +91,7 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
-              max_len=0, cu_seqlens=None, max_new=0):
+              max_len=0, cu_seqlens=None, max_new=0, seq_order=None):
     n = qkv.shape[0]
     result = torch.zeros((n, n_heads * head_dim), dtype=torch.float32, device=qkv.device)
     group = n_heads // n_kv_heads

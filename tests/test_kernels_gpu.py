@@ -285,9 +285,11 @@ def test_attention_decode_kernel_long_contexts(heads, kv_heads, dim, forced_slic
     q = randn(len(lens), (heads + 2 * kv_heads) * dim, dtype=dtype, seed=92)
     want = plain_ops.attention(q, k_cache, v_cache, table, width, last, seqs, heads, kv_heads, dim,
                                dim ** -0.5)
-    for _ in range(2):
+    longest_first = torch.tensor(sorted(range(len(lens)), key=lambda b: -lens[b]), dtype=torch.int32, device=DEV)
+    for order in (None, longest_first):          # the second call also takes the sequences longest first
         got = ops().attention(q, k_cache, v_cache, table, width, last, seqs, heads, kv_heads, dim,
-                              dim ** -0.5, 0, decode=True, seq_lens=seq_lens, max_len=max(lens))
+                              dim ** -0.5, 0, decode=True, seq_lens=seq_lens, max_len=max(lens),
+                              seq_order=order)
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
@@ -324,10 +326,12 @@ def _check_prefill_attention(heads, kv_heads, dim):
     q = randn(tok_pos.numel(), (heads + 2 * kv_heads) * dim, dtype=dtype, seed=95)
     want = plain_ops.attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads,
                                dim, dim ** -0.5)
-    got = ops().attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads, dim,
-                          dim ** -0.5, 0, seq_lens=seq_lens, max_len=max(lens), cu_seqlens=cu,
-                          max_new=max(counts))
-    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    longest_first = torch.tensor(sorted(range(len(lens)), key=lambda b: -lens[b]), dtype=torch.int32, device=DEV)
+    for order in (None, longest_first):
+        got = ops().attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads, dim,
+                              dim ** -0.5, 0, seq_lens=seq_lens, max_len=max(lens), cu_seqlens=cu,
+                              max_new=max(counts), seq_order=order)
+        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("variant", ["attention_prefill", "attention_prefill_tc"])

@@ -66,7 +66,7 @@ def test_packing_of_an_unequal_batch():
     batch = _Batch(entries)
     native.check(lib.llmh_step_reserve(cache._handle, batch.n, batch.slots, batch.counts))
     n_sections = lib.llmh_step_sections(cache._handle)
-    assert n_sections == 7 + 2                                 # two cache groups: full, window
+    assert n_sections == 8 + 2                                 # two cache groups: full, window
     offsets, sizes = (c_longlong * n_sections)(), (c_longlong * n_sections)()
     total, summary = c_longlong(), (c_longlong * 5)()
     native.check(lib.llmh_step_layout(cache._handle, batch.n, batch.counts, batch.want_counts, offsets, sizes,
@@ -83,10 +83,11 @@ def test_packing_of_an_unequal_batch():
     assert section(4) == [5, 72]
     assert section(5) == [c, a]
     assert section(6) == [4, 0, 6]                             # rows among the packed tokens
+    assert section(7) == [1, 0]                                # the longer sequence (72 positions) first
     for g in range(2):
         width = cache.table_width(g)
-        assert section(7 + g) == cache.block_table_rows(g, [c, a]).reshape(-1).tolist()
-        assert sizes[7 + g] == 2 * width
+        assert section(8 + g) == cache.block_table_rows(g, [c, a]).reshape(-1).tolist()
+        assert sizes[8 + g] == 2 * width
     assert list(summary) == [7, 3, 0, 72, total.value]
     assert host[total.value:].tolist() == [-7] * 8             # nothing written past the end
     with pytest.raises(LlmError, match="the step needs"):
