@@ -158,6 +158,8 @@ def bench(args) -> int:
                 if rep:
                     samples.append(batch * n / decode_s if decode_s > 0 else 0.0)
             rows.append((f"tg{n}", batch, samples))
+        scratch_identity = engine.workspace.plan_for(batch).identity()
+        scratch_bytes, graphs = engine.workspace.bytes(), engine.use_graphs
         del engine
         torch.cuda.empty_cache()
     out = []
@@ -176,6 +178,10 @@ def bench(args) -> int:
         used = torch.cuda.max_memory_allocated() / 2 ** 30
         print(f"\ndevice memory peak {used:.2f} GiB; weights read per decode step "
               f"{model.weight_bytes() / 2 ** 30:.2f} GiB")
+        from .ops.build import build_identity, nvcc_version
+        print(f"build {build_identity()} (nvcc {nvcc_version()}, sm_100a); kernel plan "
+              f"{model.plan_identity()}; scratch plan {scratch_identity} ({scratch_bytes / 2 ** 20:.1f} MiB); "
+              f"decode steps {'replayed from CUDA graphs' if graphs else 'launched one by one'}")
     return 0
 
 
@@ -247,17 +253,10 @@ def inspect(folder) -> int:
     except LlmError as error:
         print(f"checkpoint problem:\n{error}")
         verdict = "not runnable"
-    first = spec.blocks[0]
-    if getattr(first.mixer, "kind", None) == "attention":
-        m = first.mixer
-        width = (m.n_heads + 2 * m.n_kv_heads) * m.head_dim
-        for tokens in (1, 8, 2048):
-            print(tactics.explain("linear", m=tokens, n=width, k=m.hidden, in_dtype=torch.bfloat16,
-                                  out_dtype=torch.bfloat16, lda=m.hidden, aligned=True)
-                  + f"   [qkv product, {tokens} tokens]")
-        for decode in (True, False):
-            print(tactics.explain("attention", decode=decode, dtype=torch.bfloat16, n_heads=m.n_heads,
-                                  n_kv_heads=m.n_kv_heads, head_dim=m.head_dim, window=m.window,
-                                  packed=True) + f"   [{'decode' if decode else 'prefill'}]")
+    for label, family, shape in model.kernel_shapes(torch.bfloat16):
+        print(tactics.explain(family, **shape) + f"   [{label}]")
+    from .ops.build import build_identity, nvcc_version
+    print(f"{'kernel plan':28s}{model.plan_identity(torch.bfloat16)}")
+    print(f"{'build':28s}{build_identity()} (nvcc {nvcc_version()}, sm_100a)")
     print(verdict)
     return 0 if verdict == "runnable" else 1

@@ -54,6 +54,27 @@ class DecoderModel:
             names = [n for n in names if n not in ops.BFLOAT16_ONLY]
         return names
 
+    def kernel_shapes(self, dtype=None, token_counts=(1, 8, 2048)) -> list:
+        """Every distinct kernel choice of a forward pass: (label, family, chooser arguments)."""
+        dtype = dtype or self.dtype or torch.bfloat16
+        seen, out = set(), []
+        shapes = [s for block in self.blocks for s in block.kernel_shapes(dtype, token_counts)]
+        for n in token_counts:
+            shapes.append((f"head product, {min(n, 64)} rows", "linear",
+                           dict(m=min(n, 64), n=self.spec.vocab, k=self.spec.hidden, in_dtype=dtype,
+                                out_dtype=torch.float32, lda=self.spec.hidden, aligned=True)))
+        for label, family, shape in shapes:
+            key = (label, family, tuple(sorted((k, str(v)) for k, v in shape.items())))
+            if key not in seen:
+                seen.add(key)
+                out.append((label, family, shape))
+        return out
+
+    def plan_identity(self, dtype=None) -> str:
+        """Changes exactly when the choice of a kernel variant for this model changes."""
+        from ..ops import tactics
+        return tactics.plan_identity((family, shape) for _, family, shape in self.kernel_shapes(dtype))
+
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
 

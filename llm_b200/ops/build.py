@@ -166,6 +166,33 @@ def all_sources() -> list:
     return sorted(p.stem for p in CSRC.glob("*.cu"))
 
 
+_nvcc_version = None
+
+
+def nvcc_version() -> str:
+    """'12.9.86' from `nvcc --version` ('unknown' if nvcc cannot be run)."""
+    global _nvcc_version
+    if _nvcc_version is None:
+        try:
+            text = subprocess.run([_nvcc(), "--version"], capture_output=True, text=True, timeout=30).stdout
+            _nvcc_version = text.rsplit("V", 1)[1].split()[0] if "V" in text else "unknown"
+        except (KernelError, OSError, subprocess.SubprocessError, IndexError):
+            _nvcc_version = "unknown"
+    return _nvcc_version
+
+
+def build_identity() -> str:
+    """One hash over every kernel source, the host library's sources, the compiler flags and the
+    compiler's version: two runs with equal identities ran the same native code (the build
+    manifest of MythEclipse/llm records the same things, apps/engine/build.rs:30-62 and
+    manifest.rs)."""
+    h = hashlib.sha256()
+    for name in all_sources():
+        h.update(f"{name}:{_digest(CSRC / (name + '.cu'))};".encode())
+    h.update(f"host:{_host_digest()};nvcc:{nvcc_version()}".encode())
+    return h.hexdigest()[:16]
+
+
 # ----------------------------------------------------------------------------- the host library
 
 HOST = CSRC / "host"

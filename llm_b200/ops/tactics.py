@@ -166,3 +166,16 @@ def explain(family: str, **shape) -> str:
     lines = [f"{family}: {name}"]
     lines += [f"  not {n}: {why}" for n, why in reasons]
     return "\n".join(lines)
+
+
+def plan_identity(shapes) -> str:
+    """A hash of which variant every (family, shape) of `shapes` gets, in the manner of the kernel
+    plan's identity in MythEclipse/llm (apps/engine/src/tactics.rs:298-303): it changes exactly when
+    a selection changes. `shapes`: iterable of (family, dict of the chooser's arguments)."""
+    import hashlib
+    h = hashlib.sha256()
+    for family, shape in shapes:
+        table = LINEAR if family == "linear" else ATTENTION
+        name = _choose(table, **shape)[0]
+        h.update(f"{family}:{sorted((k, str(v)) for k, v in shape.items())}->{name};".encode())
+    return h.hexdigest()[:16]

@@ -63,6 +63,21 @@ class AttentionMixer(Mixer):
         return [BufferRequest("qkv", (n_tokens, self.q_width + 2 * self.kv_width), dtype, 0, 2),
                 BufferRequest("mixed", (n_tokens, self.q_width), dtype, 2, 3)]
 
+    def kernel_shapes(self, dtype, token_counts):
+        s, out = self.spec, []
+        width = self.q_width + 2 * self.kv_width
+        for n in token_counts:
+            out.append((f"qkv product, {n} tokens", "linear",
+                        dict(m=n, n=width, k=s.hidden, in_dtype=dtype, out_dtype=dtype, lda=s.hidden, aligned=True)))
+            out.append((f"output product, {n} tokens", "linear",
+                        dict(m=n, n=s.hidden, k=self.q_width, in_dtype=dtype, out_dtype=torch.float32,
+                             lda=self.q_width, aligned=True)))
+        for decode in (True, False):
+            out.append(("decode attention" if decode else "prefill attention", "attention",
+                        dict(decode=decode, dtype=dtype, n_heads=s.n_heads, n_kv_heads=s.n_kv_heads,
+                             head_dim=s.head_dim, window=s.window, packed=True, aligned=True)))
+        return out
+
     def kv_request(self):
         return KvRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
 

@@ -64,6 +64,11 @@ class Part:
         """tensor name -> ParamSpec of everything this part binds."""
         return {}
 
+    def kernel_shapes(self, dtype, token_counts) -> list:
+        """(label, family, chooser arguments) of the kernel choices this part's forward pass makes
+        for steps of `token_counts` tokens: what `inspect` prints and the plan identity hashes."""
+        return []
+
     def bind(self, tensors: dict, dtype: torch.dtype, device) -> None:
         """Take the declared tensors (CPU or device, storage dtype) and keep
         what `forward` needs on `device` for a run in `dtype`."""

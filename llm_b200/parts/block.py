@@ -45,6 +45,9 @@ class PreNormBlock(Block):
     def weights(self):
         return [w for p in self.parts for w in p.weights()]
 
+    def kernel_shapes(self, dtype, token_counts):
+        return [shape for p in self.parts for shape in p.kernel_shapes(dtype, token_counts)]
+
     def scratch_requests(self, n_tokens, dtype):
         """The normed inputs of both halves plus what the mixer and the feed-forward
         declare, their phases lined up one after the other."""

@@ -43,6 +43,16 @@ class GatedMlp(FeedForward):
             self.w_gate_up = torch.cat([gate, up])
         self.w_down = to_run_dtype(tensors[t["down"]], dtype, device)
 
+    def kernel_shapes(self, dtype, token_counts):
+        s, out = self.spec, []
+        for n in token_counts:
+            out.append((f"gate and up product, {n} tokens", "linear",
+                        dict(m=n, n=2 * s.intermediate, k=s.hidden, in_dtype=dtype, out_dtype=dtype, lda=s.hidden, aligned=True)))
+            out.append((f"down product, {n} tokens", "linear",
+                        dict(m=n, n=s.hidden, k=s.intermediate, in_dtype=dtype, out_dtype=torch.float32,
+                             lda=s.intermediate, aligned=True)))
+        return out
+
     def scratch_requests(self, n_tokens, dtype):
         from ..engine.workspace import BufferRequest
         s = self.spec

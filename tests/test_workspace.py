@@ -70,3 +70,28 @@ def test_a_model_declares_its_scratch_and_gets_views(tmp_path):
     assert workspace.for_tokens(10).arena is workspace.arena
     # the attention output reuses the bytes of the normed input: their lifetimes do not meet
     assert views.plan.total < sum(r.nbytes for r in requests)
+
+
+def test_kernel_plan_and_build_identities(tmp_path):
+    """The kernel plan's identity changes exactly when a selection changes; the build identity
+    is one hash over the native sources, the flags and the compiler."""
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine.model import DecoderModel
+    from llm_b200.ops import tactics
+    from llm_b200.ops.build import build_identity
+    from tiny import TINY_F
+    model = DecoderModel(config_from_dict(dict(TINY_F)).model_spec())
+    shapes = model.kernel_shapes(torch.bfloat16)
+    labels = [label for label, _, _ in shapes]
+    assert "prefill attention" in labels and "decode attention" in labels
+    assert any(label.startswith("head product") for label in labels)
+    before = model.plan_identity(torch.bfloat16)
+    assert before == model.plan_identity(torch.bfloat16) and len(before) == 16
+    tactics.disable("attention_prefill_tc")
+    try:
+        assert model.plan_identity(torch.bfloat16) != before
+    finally:
+        tactics.enable("attention_prefill_tc")
+    assert model.plan_identity(torch.bfloat16) == before
+    assert model.plan_identity(torch.float32) != before         # the 32-bit path picks other kernels
+    assert build_identity() == build_identity() and len(build_identity()) == 16
