@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import torch
 
+from .cache import round_up
 from .engine import Engine, GenerationRequest, generate as _generate, load_model
 from .errors import FormatError
 from .sampling import DEFAULT_SEED, SamplingParams
@@ -41,7 +42,7 @@ class LLM:
             model = load_model(model, parse_dtype(dtype), device)
         self.model = model
         context = min(context, model.spec.max_positions)
-        held = max_tokens_held or batch * ((context + 63) // 64 * 64)
+        held = max_tokens_held or batch * round_up(context)
         self.engine = Engine(model, max_tokens=held, max_seq_len=context, max_slots=batch)
         self.default_stop_tokens = tuple(model.spec.stop_tokens)
 

@@ -29,7 +29,7 @@ import torch
 from .. import native
 from .allocator import FreeList
 
-PAGE = 64
+PAGE = native.plan_constant("page")      # positions per cache page (csrc/plan.h)
 
 
 def round_up(n: int, unit: int = PAGE) -> int:

@@ -123,6 +123,7 @@ def bench(args) -> int:
     from .config import config_from_dict
     from .engine import (Engine, Entry, GenerationRequest, generate, load_model, random_model)
     from .sampling import SamplingParams
+    from .cache import round_up
     from .shapes import shape
     if model_dir:
         model, name = load_model(model_dir, parse_dtype(dtype)), model_dir
@@ -134,7 +135,7 @@ def bench(args) -> int:
                            generator=torch.Generator().manual_seed(0)).tolist()
     rows = []
     for batch in batches:
-        per_seq = (context + 63) // 64 * 64
+        per_seq = round_up(context)
         engine = Engine(model, max_tokens=batch * per_seq, max_seq_len=context, max_slots=batch)
         for n in prompts:
             samples = []

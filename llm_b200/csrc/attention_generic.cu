@@ -22,7 +22,7 @@ using namespace llmb;
 
 LLMB_DEFINE_LAST_ERROR(llmb_attention_generic)
 
-constexpr int MAX_PER_LANE = 8;   // head_dim <= 256
+constexpr int MAX_PER_LANE = LLMB_MAX_HEAD_DIM / 32;   // elements of a head per lane
 constexpr int WARPS = 4;
 
 template <typename T>

@@ -23,7 +23,7 @@
 #define LLMB_DTYPE_F32 0
 #define LLMB_DTYPE_BF16 1
 
-#define LLMB_PAGE 64           // positions per cache page
+#include "plan.h"              // LLMB_PAGE and the other constants shared with the host library
 
 namespace llmb {
 

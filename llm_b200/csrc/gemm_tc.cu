@@ -144,6 +144,8 @@ struct Epilogue {
                              // out is bfloat16 [tokens, ldo] with outs / 2 columns silu(gate) * up
 };
 
+static_assert(LLMB_GLU_BLOCK == 16, "the gated epilogue reads 16 gate and 16 up columns of tensor memory per pair");
+
 __device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
 
 // One work unit: output tile (tile_a, tile_b) and one slice of its k-blocks.

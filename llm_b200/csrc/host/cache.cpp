@@ -151,6 +151,16 @@ using namespace llmh;
 
 // ------------------------------------------------------------------------------------ C boundary
 
+// The constants of plan.h for callers that cannot include it: 0 page, 1 gated block, 2 largest head size.
+LLMH_EXPORT int llmh_plan_constant(int which) {
+    switch (which) {
+        case 0: return LLMB_PAGE;
+        case 1: return LLMB_GLU_BLOCK;
+        case 2: return LLMB_MAX_HEAD_DIM;
+        default: return -1;
+    }
+}
+
 LLMH_EXPORT const char* llmh_last_error() { return last_failure().text.c_str(); }
 LLMH_EXPORT void llmh_last_error_numbers(long long* first, long long* second) {
     *first = last_failure().first;

@@ -11,11 +11,12 @@
 #include <cstdint>
 #include <vector>
 
+#include "../plan.h"
 #include "free_list.hpp"
 
 namespace llmh {
 
-constexpr int PAGE = 64;
+constexpr int PAGE = LLMB_PAGE;
 
 inline int pages_for(long long positions) { return (int)((positions + PAGE - 1) / PAGE); }
 

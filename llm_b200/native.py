@@ -27,6 +27,7 @@ _BATCH = [c_int, _INTS, _INTS, _INTS, _INTS, _INTS]      # n, slots, counts, tok
 
 # name: (result type, argument types); the declarations are in the .cpp files of csrc/host
 _SIGNATURES = {
+    "llmh_plan_constant": (c_int, [c_int]),
     "llmh_last_error": (c_char_p, []),
     "llmh_last_error_numbers": (None, [_LONGS, _LONGS]),
     "llmh_free_list_create": (c_int, [c_int, c_char_p, POINTER(_P)]),
@@ -102,3 +103,8 @@ def ints(values, ctype=c_int):
     """A C array from a sequence of Python ints."""
     values = list(values)
     return (ctype * len(values))(*values)
+
+
+def plan_constant(name: str) -> int:
+    """A constant of csrc/plan.h, the one definition shared by kernels, host library and Python."""
+    return lib().llmh_plan_constant({"page": 0, "glu_block": 1, "max_head_dim": 2}[name])

@@ -17,11 +17,12 @@ import sys
 
 import torch
 
+from .. import native
 from ..errors import KernelError
 from . import tactics
 from .build import all_sources, ensure_built, load_library
 
-PAGE = 64   # positions per cache page (LLMB_PAGE in csrc/common.cuh)
+PAGE = native.plan_constant("page")              # positions per cache page (csrc/plan.h)
 BFLOAT16_ONLY = ("gemm_tc", "gemm_skinny", "attention_decode", "attention_prefill",
                  "attention_prefill_tc")
 
@@ -216,7 +217,7 @@ def check_device_status() -> None:
                                   "last steps are not valid")
 
 
-GLU_BLOCK = 16      # gate and up rows alternate in blocks of this many rows for the fused epilogue
+GLU_BLOCK = native.plan_constant("glu_block")    # gate and up rows alternate in blocks of this many rows (csrc/plan.h)
 
 
 def glu_fusable(n_rows: int, k: int, dtype) -> bool:

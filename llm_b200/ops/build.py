@@ -210,7 +210,7 @@ def _host_compiler() -> list:
 
 def _host_digest() -> str:
     h = hashlib.sha256()
-    for path in sorted(HOST.glob("*.cpp")) + sorted(HOST.glob("*.hpp")):
+    for path in sorted(HOST.glob("*.cpp")) + sorted(HOST.glob("*.hpp")) + [CSRC / "plan.h"]:
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join(HOST_FLAGS).encode())
