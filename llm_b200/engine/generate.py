@@ -8,15 +8,20 @@ batch of requests with unequal prompts starts together (one prefill step),
 every live sequence then advances by one token per step, sequences that end
 leave the batch (their slot goes back to the cache) and the rest go on; when
 the batch is empty the next batch starts. Stop reasons and the timing fields
-are those of generate.rs:20-49,129-160.
+are those of generate.rs:20-49,129-160. Who is live, who goes on and who leaves
+for which reason is decided by the native host library
+(`csrc/host/generation.cpp`); this module owns slots, steps, sampling, timing
+and callbacks.
 """
 from __future__ import annotations
 
 import time
+from ctypes import byref, c_int, c_void_p
 from dataclasses import dataclass, field
 
 import torch
 
+from .. import native
 from ..errors import ContextFull, FormatError
 from ..sampling import BatchSampler, SamplingParams
 from .step import Entry
@@ -83,15 +88,68 @@ def generate(engine, requests, max_batch: int | None = None, on_token=None, canc
     return results
 
 
+_REASONS = ("eos", "max_tokens", "cancelled", "context_full")       # codes of csrc/host/generation.cpp
+
+
+class _Schedule:
+    """The batch's decisions, kept by the native host library (`csrc/host/generation.cpp`):
+    who is live, who goes on, who leaves and why."""
+
+    def __init__(self, reqs, max_seq_len: int):
+        n = len(reqs)
+        self.n = n
+        stops = [int(t) for r in reqs for t in r.stop_tokens]
+        handle = c_void_p()
+        native.check(native.lib().llmh_generation_create(
+            n, native.ints(int(r.max_tokens) for r in reqs), native.ints(len(r.stop_tokens) for r in reqs),
+            native.ints(stops), int(max_seq_len), byref(handle)))
+        self._handle = handle
+        self._a, self._b, self._c, self._d = ((c_int * max(n, 1))() for _ in range(4))
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            native.lib().llmh_generation_destroy(self._handle)
+            self._handle = None
+
+    def live(self) -> list:
+        return list(self._a[:native.lib().llmh_generation_live(self._handle, self._a)])
+
+    def drop_exhausted(self):
+        """(rows of the live list that stay, sequences that leave with 'max_tokens')."""
+        kept, done = c_int(), c_int()
+        native.check(native.lib().llmh_generation_drop_exhausted(self._handle, self._a, byref(kept), self._b,
+                                                                 byref(done)))
+        return list(self._a[:kept.value]), list(self._b[:done.value])
+
+    def plan_onward(self, lengths) -> list:
+        count = c_int()
+        native.check(native.lib().llmh_generation_plan_onward(self._handle, native.ints(lengths), self._a,
+                                                              byref(count)))
+        return list(self._a[:count.value])
+
+    def take_tokens(self, tokens):
+        """(emitted flag per live row, [(sequence, reason)] that leave, rows of the planned step that stay)."""
+        done, going = c_int(), c_int()
+        native.check(native.lib().llmh_generation_take_tokens(
+            self._handle, native.ints(tokens), self._a, self._b, self._c, byref(done), self._d, byref(going)))
+        finished = [(self._b[i], _REASONS[self._c[i]]) for i in range(done.value)]
+        return list(self._a[:len(tokens)]), finished, list(self._d[:going.value])
+
+    def cancel(self) -> list:
+        done = c_int()
+        native.check(native.lib().llmh_generation_cancel(self._handle, self._a, byref(done)))
+        return list(self._a[:done.value])
+
+
 def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
     started = time.perf_counter()
     slots = engine.acquire(len(batch))
-    live = list(range(len(batch)))                      # indices into `batch`
     reqs = [requests[i] for i in batch]
     emitted = [[] for _ in batch]
     reason = ["max_tokens"] * len(batch)
     first_token_at = [None] * len(batch)
     sampler = BatchSampler([r.params for r in reqs], engine.vocab, engine.device)
+    schedule = _Schedule(reqs, engine.max_seq_len)
     released = set()
 
     def finish(b, why):
@@ -106,23 +164,22 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
     copied = torch.cuda.Event() if on_gpu else None
 
     try:
+        live = schedule.live()
         logits = engine.step([Entry(slots[b], reqs[b].prompt, [len(reqs[b].prompt) - 1])
                               for b in live])
         prefill_done = None
         while live:
             if cancel is not None and cancel():
-                for b in live:
+                for b in schedule.cancel():
                     finish(b, "cancelled")
                 break
             # sequences that may not emit anything leave before sampling
-            keep = [b for b in live if len(emitted[b]) < reqs[b].max_tokens]
-            if len(keep) != len(live):
-                rows = [k for k, b in enumerate(live) if b in set(keep)]
-                for b in live:
-                    if b not in keep:
-                        finish(b, "max_tokens")
-                logits = logits[rows] if keep else logits[:0]
-                live = keep
+            rows, exhausted = schedule.drop_exhausted()
+            if exhausted:
+                for b in exhausted:
+                    finish(b, "max_tokens")
+                logits = logits[rows] if rows else logits[:0]
+                live = schedule.live()
                 if not live:
                     break
             sampled = sampler.sample(logits, live)               # int32 on the device
@@ -132,9 +189,7 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
             # Who goes on is known before the ids are: everyone whose limits allow one more
             # token. Their next step is queued now, fed with the ids on the device; a
             # sequence that turns out to have drawn a stop token simply drops that step.
-            room = [engine.length(slots[b]) < engine.max_seq_len for b in live]
-            onward = [k for k, b in enumerate(live)
-                      if len(emitted[b]) + 1 < reqs[b].max_tokens and room[k]]
+            onward = schedule.plan_onward([engine.length(slots[b]) for b in live])
             next_logits = None
             if onward:
                 feed = sampled if len(onward) == len(live) else sampled[
@@ -148,24 +203,18 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
             now = time.perf_counter()
             if prefill_done is None:
                 prefill_done = now
-            going_rows, going = [], []
-            for k, (b, token) in enumerate(zip(live, tokens)):
-                if token in reqs[b].stop_tokens:
-                    finish(b, "eos")
+            counts, finished, going_rows = schedule.take_tokens(tokens)
+            for b, token, counted in zip(live, tokens, counts):
+                if not counted:
                     continue
                 emitted[b].append(token)
                 if first_token_at[b] is None:
                     first_token_at[b] = now
                 if on_token is not None:
                     on_token(batch[b], token)
-                if not room[k]:
-                    finish(b, "context_full")
-                elif len(emitted[b]) >= reqs[b].max_tokens:
-                    finish(b, "max_tokens")
-                else:
-                    going.append(b)
-                    going_rows.append(onward.index(k))
-            live = going
+            for b, why in finished:
+                finish(b, why)
+            live = schedule.live()
             if live:
                 logits = next_logits if len(going_rows) == len(onward) else next_logits[going_rows]
         sampler.check_status()

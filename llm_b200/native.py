@@ -60,6 +60,18 @@ _SIGNATURES = {
     "llmh_step_pack": (c_int, [_P, *_BATCH, _P, c_longlong, _LONGS, _LONGS, _LONGS]),
     "llmh_step_commit": (c_int, [_P, c_int, _INTS, _INTS]),
     "llmh_plan_place": (c_int, [c_int, POINTER(c_char_p), _LONGS, _INTS, _INTS, c_longlong, _LONGS, _LONGS]),
+    "llmh_generation_create": (c_int, [c_int, _INTS, _INTS, _INTS, c_int, POINTER(_P)]),
+    "llmh_generation_destroy": (None, [_P]),
+    "llmh_generation_live": (c_int, [_P, _INTS]),
+    "llmh_generation_drop_exhausted": (c_int, [_P, _INTS, _INTS, _INTS, _INTS]),
+    "llmh_generation_plan_onward": (c_int, [_P, _INTS, _INTS, _INTS]),
+    "llmh_generation_take_tokens": (c_int, [_P, _INTS, _INTS, _INTS, _INTS, _INTS, _INTS, _INTS]),
+    "llmh_generation_cancel": (c_int, [_P, _INTS, _INTS]),
+    "llmh_tactics_choose": (c_int, [c_int, _INTS, c_char_p, c_int, c_char_p, c_int]),
+    "llmh_tactics_set_disabled": (None, [c_char_p, c_int]),
+    "llmh_tactics_is_disabled": (c_int, [c_char_p]),
+    "llmh_tactics_rows": (c_int, [c_int]),
+    "llmh_tactics_row": (c_int, [c_int, c_int, POINTER(c_char_p), _INTS, POINTER(c_char_p)]),
     "llmh_safetensors_open": (c_int, [c_char_p, POINTER(_P)]),
     "llmh_safetensors_close": (None, [_P]),
     "llmh_safetensors_count": (c_int, [_P]),

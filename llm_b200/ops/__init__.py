@@ -242,7 +242,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
         _call("gemm_tc", "llmb_gemm_tc", _ptr(a), _c_int(a.stride(0)), _ptr(w), None, _ptr(result),
               _c_int(_code(a.dtype)), None, _ptr(partials), ctypes.c_longlong(partials.numel()),
               _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k),
-              _c_int(n // 2), _c_int(1), _c_int(0 if "gemm_tc_pair" in tactics._disabled else 1),
+              _c_int(n // 2), _c_int(1), _c_int(0 if tactics.is_disabled("gemm_tc_pair") else 1),
               _stream())
         return result
     if k != k2 or a.dtype != w.dtype:
@@ -264,7 +264,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
               _ptr(result if residual is None else None), _c_int(_code(target_dtype)),
               _ptr(residual), _ptr(partials), ctypes.c_longlong(partials.numel()),
               _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k), _c_int(n),
-              _c_int(0), _c_int(0 if "gemm_tc_pair" in tactics._disabled else 1), _stream())
+              _c_int(0), _c_int(0 if tactics.is_disabled("gemm_tc_pair") else 1), _stream())
     elif variant == "gemm_skinny":
         partials, counters = _skinny_scratch(a.device, m, n, k)
         _call("gemm_skinny", "llmb_gemm_skinny", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),

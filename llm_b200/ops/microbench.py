@@ -86,8 +86,10 @@ def main(argv=None) -> int:
 
     if args.op == "linear":
         if args.variant:
-            for row in tactics.LINEAR:
-                if row.name != args.variant and row.rank > [r for r in tactics.LINEAR if r.name == args.variant][0].rank:
+            table = tactics.rows("linear")
+            wanted = [r for r in table if r.name == args.variant][0]
+            for row in table:
+                if row.rank > wanted.rank:
                     tactics.disable(row.name)
         m, n, k = args.m, args.n, args.k
         copies = 1 if args.once else max(2, int(300e6 / (n * k * 2)) + 1)

@@ -161,3 +161,35 @@ def test_a_tensor_keeps_its_file_mapped(tmp_path):
     t = SafetensorsFile(path).tensor("w")
     gc.collect()
     assert t.tolist() == [4, 5, 6]
+
+
+def test_generation_schedule_decisions():
+    """Stop tokens are neither emitted nor fed, limits end a sequence after the token that reaches
+    them, a full context ends it after the token that was sampled from its last position, and
+    sequences that may emit nothing leave before sampling."""
+    from llm_b200.engine.generate import GenerationRequest, _Schedule
+    reqs = [GenerationRequest([1], max_tokens=3, stop_tokens=(9,)),       # ends by its limit
+            GenerationRequest([1], max_tokens=5, stop_tokens=(9, 7)),     # draws a stop token
+            GenerationRequest([1], max_tokens=0),                         # may emit nothing
+            GenerationRequest([1], max_tokens=8)]                         # runs into the context's end
+    s = _Schedule(reqs, max_seq_len=10)
+    assert s.live() == [0, 1, 2, 3]
+    rows, exhausted = s.drop_exhausted()
+    assert rows == [0, 1, 3] and exhausted == [2] and s.live() == [0, 1, 3]
+    onward = s.plan_onward([4, 4, 9])                     # sequence 3 holds 9 of 10 positions: room for one
+    assert onward == [0, 1, 2]
+    counts, finished, going = s.take_tokens([5, 6, 4])
+    assert counts == [1, 1, 1] and finished == [] and going == [0, 1, 2]
+    assert s.drop_exhausted() == ([0, 1, 2], [])
+    onward = s.plan_onward([5, 5, 10])                    # sequence 3 is full now: it does not go on
+    assert onward == [0, 1]
+    counts, finished, going = s.take_tokens([5, 7, 4])
+    assert counts == [1, 0, 1]                            # the stop token is not output
+    assert finished == [(1, "eos"), (3, "context_full")] and going == [0] and s.live() == [0]
+    assert s.plan_onward([6]) == []                       # its third token is its last: nothing to queue
+    counts, finished, going = s.take_tokens([9])
+    assert counts == [0] and finished == [(0, "eos")] and s.live() == []
+    t = _Schedule(reqs[:2], max_seq_len=10)
+    assert t.cancel() == [0, 1] and t.live() == []
+    with pytest.raises(LlmError):
+        _Schedule(reqs[:1], 10).take_tokens([1])          # tokens without a planned step

@@ -1,0 +1,68 @@
+"""The kernel tables: a switched-off row is never chosen, every row states its evidence, the
+family's shapes resolve to the intended kernels, and refusals keep their reasons
+(the invariants MythEclipse/llm tests in apps/engine/src/tactics.rs:454-517)."""
+import pytest
+import torch
+
+from llm_b200.ops import tactics
+from llm_b200.shapes import shape
+
+BF16, F32 = torch.bfloat16, torch.float32
+
+
+def test_every_row_states_its_evidence_and_ranks_differ():
+    for family in ("linear", "attention"):
+        rows = tactics.rows(family)
+        assert len({r.name for r in rows}) == len(rows)
+        assert len({r.rank for r in rows}) == len(rows)          # no tie to break by accident
+        for row in rows:
+            assert len(row.evidence) > 40, row.name
+        assert min(r.rank for r in rows) == 0                      # a row without conditions ends each table
+
+
+def test_switched_off_rows_are_never_chosen():
+    args = dict(m=8, n=4096, k=4096, in_dtype=BF16, out_dtype=BF16, lda=4096)
+    assert tactics.choose_linear(**args) == "gemm_tc"
+    tactics.disable("gemm_tc")
+    try:
+        assert tactics.choose_linear(**args) == "gemm_skinny"
+        assert "not gemm_tc: disabled" in tactics.explain("linear", **args)
+        tactics.disable("gemm_skinny")
+        assert tactics.choose_linear(**args) == "gemm_simt"
+    finally:
+        tactics.enable("gemm_tc")
+        tactics.enable("gemm_skinny")
+    assert tactics.choose_linear(**args) == "gemm_tc"
+    assert not tactics.is_disabled("gemm_tc")
+
+
+@pytest.mark.parametrize("name", ["llama-3.1-8b", "llama-2-7b", "llama-3.2-1b"])
+def test_family_shapes_get_the_fast_kernels(name):
+    """No shape of the measured configurations falls back silently."""
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine.model import DecoderModel
+    model = DecoderModel(config_from_dict(shape(name, 1)).model_spec())
+    for label, family, args in model.kernel_shapes(BF16):
+        chosen = tactics._choose(family, **args)[0]
+        if family == "linear":
+            assert chosen == "gemm_tc", label
+        elif label.startswith("decode"):
+            assert chosen == "attention_decode", label
+        else:
+            assert chosen == "attention_prefill_tc", label
+    for label, family, args in model.kernel_shapes(F32):           # the 32-bit path: CUDA cores only
+        assert tactics._choose(family, **args)[0] in ("gemm_simt", "attention_generic"), label
+
+
+def test_refusals_name_the_assumption_that_fails():
+    text = tactics.explain("attention", decode=True, dtype=BF16, n_heads=32, n_kv_heads=2, head_dim=128,
+                           window=0, packed=True)
+    assert text.startswith("attention: attention_prefill_tc") and "group of 16 query heads exceeds 8" in text
+    text = tactics.explain("attention", decode=False, dtype=BF16, n_heads=4, n_kv_heads=4, head_dim=80,
+                           window=0, packed=True)
+    assert text.startswith("attention: attention_generic") and "head_dim 80" in text
+    text = tactics.explain("attention", decode=True, dtype=BF16, n_heads=4, n_kv_heads=2, head_dim=64,
+                           window=100, packed=True)
+    assert text.startswith("attention: attention_generic") and "no window" in text
+    text = tactics.explain("linear", m=2048, n=4096, k=4100, in_dtype=BF16, out_dtype=BF16, lda=4100)
+    assert text.startswith("linear: gemm_simt") and "multiple of 8" in text and "exceed 64" in text
