@@ -212,11 +212,12 @@ def random_folder(args) -> int:
     if out is None or (name is None) == (config_file is None):
         raise SystemExit("usage: python -m llm_b200 random (--shape NAME | --config FILE) --out DIR "
                          "[--seed S] [--layers L] [--dtype bfloat16|float32] [--std 0.02]")
+    from . import native
     from .api import parse_dtype
     from .config import config_from_dict
     from .shapes import shape
     from .weights import write_random_model
-    raw = shape(name, layers) if name else json.loads(open(config_file).read())
+    raw = shape(name, layers) if name else native.read_json(open(config_file, "rb").read(), config_file)
     if config_file and layers is not None:
         raw["num_hidden_layers"] = layers
     folder = write_random_model(out, config_from_dict(raw), seed, parse_dtype(dtype), std=std)

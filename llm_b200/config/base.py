@@ -88,7 +88,8 @@ def read_config_json(folder) -> dict:
     path = Path(folder) / "config.json"
     if not path.is_file():
         raise FormatError(f"{path}: no such file")
-    try:
-        return json.loads(path.read_text())
-    except json.JSONDecodeError as error:
-        raise FormatError(f"{path}: not valid JSON ({error})") from None
+    from .. import native
+    raw = native.read_json(path.read_bytes(), str(path))         # the host library's own reader
+    if not isinstance(raw, dict):
+        raise FormatError(f"{path}: the configuration must be a JSON object")
+    return raw

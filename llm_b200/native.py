@@ -12,7 +12,7 @@ raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, byref, c_char_p, c_int, c_longlong, c_void_p
+from ctypes import POINTER, byref, c_char_p, c_double, c_int, c_longlong, c_void_p
 
 from .errors import CacheFull, ContextFull, FormatError, LlmError
 
@@ -60,6 +60,11 @@ _SIGNATURES = {
     "llmh_step_pack": (c_int, [_P, *_BATCH, _P, c_longlong, _LONGS, _LONGS, _LONGS]),
     "llmh_step_commit": (c_int, [_P, c_int, _INTS, _INTS]),
     "llmh_plan_place": (c_int, [c_int, POINTER(c_char_p), _LONGS, _INTS, _INTS, c_longlong, _LONGS, _LONGS]),
+    "llmh_json_parse": (c_int, [c_char_p, c_longlong, c_char_p, POINTER(_P)]),
+    "llmh_json_free": (None, [_P]),
+    "llmh_json_count": (c_int, [_P]),
+    "llmh_json_node": (c_int, [_P, c_int, _INTS, POINTER(c_char_p), POINTER(c_char_p), _LONGS, POINTER(c_double),
+                               _INTS]),
     "llmh_generation_create": (c_int, [c_int, _INTS, _INTS, _INTS, c_int, POINTER(_P)]),
     "llmh_generation_destroy": (None, [_P]),
     "llmh_generation_live": (c_int, [_P, _INTS]),
@@ -120,3 +125,44 @@ def ints(values, ctype=c_int):
 def plan_constant(name: str) -> int:
     """A constant of csrc/plan.h, the one definition shared by kernels, host library and Python."""
     return lib().llmh_plan_constant({"page": 0, "glu_block": 1, "max_head_dim": 2}[name])
+
+
+def read_json(text, where: str = "text"):
+    """The value of a JSON document (bytes or str), read by the host library's own reader;
+    FormatError with the byte position if it is not JSON."""
+    data = text.encode("utf-8") if isinstance(text, str) else bytes(text)
+    document = c_void_p()
+    check(lib().llmh_json_parse(data, len(data), where.encode("utf-8", "replace"), byref(document)))
+    try:
+        kind, key, string = c_int(), c_char_p(), c_char_p()
+        integer, real, children = c_longlong(), c_double(), c_int()
+        at = [0]
+
+        def build():
+            check(lib().llmh_json_node(document, at[0], byref(kind), byref(key), byref(string), byref(integer),
+                                       byref(real), byref(children)))
+            at[0] += 1
+            k, n = kind.value, children.value
+            if k == 0:
+                return None
+            if k == 1:
+                return bool(integer.value)
+            if k == 2:
+                return integer.value
+            if k == 3:
+                return real.value
+            if k == 4:
+                return string.value.decode("utf-8")
+            if k == 5:
+                return [build() for _ in range(n)]
+            out = {}
+            for _ in range(n):
+                check(lib().llmh_json_node(document, at[0], byref(kind), byref(key), byref(string),
+                                           byref(integer), byref(real), byref(children)))
+                name = key.value.decode("utf-8")
+                out[name] = build()
+            return out
+
+        return build()
+    finally:
+        lib().llmh_json_free(document)

@@ -119,8 +119,9 @@ def open_checkpoint(folder) -> dict:
         return out
     if index.is_file():
         try:
-            weight_map = json.loads(index.read_text())["weight_map"]
-        except (json.JSONDecodeError, KeyError, TypeError):
+            weight_map = native.read_json(index.read_bytes(), str(index))["weight_map"]
+            weight_map.items()
+        except (KeyError, TypeError, AttributeError):
             raise FormatError(f"{index}: no weight_map") from None
         files = {}
         for name, shard in weight_map.items():

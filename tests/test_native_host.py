@@ -193,3 +193,21 @@ def test_generation_schedule_decisions():
     assert t.cancel() == [0, 1] and t.live() == []
     with pytest.raises(LlmError):
         _Schedule(reqs[:1], 10).take_tokens([1])          # tokens without a planned step
+
+
+def test_json_reader_gives_the_values_python_would(tmp_path):
+    text = ('{"a": 1, "b": -2.5e3, "c": [true, false, null, "x\\u00e9\\n", [], {}], "d": {"e": {"f": [1, 2]}},'
+            ' "n": 123456789012345678, "s": ""}')
+    assert native.read_json(text) == json.loads(text)
+    assert native.read_json("12345678901234567890") == 1.2345678901234567e19      # beyond 64 bits: a real
+    assert native.read_json(b"[]") == [] and native.read_json("3") == 3 and native.read_json('"q"') == "q"
+    for bad in ['{"a": 1,}', "{'a': 1}", '{"a" 1}', "[1 2]", "", "nul", '{"a": 01x}', '"\\x"', "[" * 80]:
+        with pytest.raises(FormatError):
+            native.read_json(bad, "here")
+    from llm_b200.config import load_config
+    (tmp_path / "config.json").write_text("[1, 2]")
+    with pytest.raises(FormatError, match="must be a JSON object"):
+        load_config(tmp_path)
+    (tmp_path / "config.json").write_text('{"architectures": ["LlamaForCausalLM"],')
+    with pytest.raises(FormatError, match="not JSON"):
+        load_config(tmp_path)
