@@ -57,12 +57,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [STAGES][2][64][LDS]
 
-    int seq = blockIdx.z, head = blockIdx.y;
+    int seq = blockIdx.z, head = blockIdx.x;
     int first_token = cu_seqlens[seq];
     int n_new = cu_seqlens[seq + 1] - first_token;
     int n_tiles = (n_new + BQ - 1) / BQ;
-    if ((int)blockIdx.x >= n_tiles) return;
-    int tile = n_tiles - 1 - blockIdx.x;                 // the heaviest tile first
+    if ((int)blockIdx.y >= n_tiles) return;
+    int tile = n_tiles - 1 - blockIdx.y;                 // the heaviest tile of every head first (x runs fastest)
     int start = seq_lens[seq] - n_new;                   // position of the sequence's first new token
     int kv_head = head / (n_heads / n_kv_heads);
     int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -232,7 +232,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    dim3 grid((max_new + BQ - 1) / BQ, n_heads, n_seqs);
+    dim3 grid(n_heads, (max_new + BQ - 1) / BQ, n_seqs);
     attention_prefill_kernel<D><<<grid, WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         block_table, table_stride, ring_pages, cu_seqlens, seq_lens, (__nv_bfloat16*)out, out_stride,
@@ -261,7 +261,7 @@ LLMB_EXPORT int llmb_attention_prefill(const void* q, int q_stride, const void* 
     if (n_seqs == 0 || max_new == 0) return LLMB_OK;
     int code = llmb_attention_prefill_supports(n_heads, n_kv_heads, head_dim, window);
     if (code) return code;
-    LLMB_REQUIRE(n_seqs <= 65535 && n_heads <= 65535 && ring_pages > 0, "attention_prefill: bad sizes");
+    LLMB_REQUIRE(n_seqs <= 65535 && max_new / BQ < 65535 && ring_pages > 0, "attention_prefill: bad sizes");
     LLMB_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0 &&
                  (reinterpret_cast<uintptr_t>(out) & 3) == 0,
                  "attention_prefill: q and out must be 4-byte aligned with even row strides");

@@ -103,12 +103,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     griddep_launch();            // the next kernel may set itself up; this one needs the one before it whole
     griddep_wait();
     // seq_order (optional): sequences by falling length, so that the longest start first
-    int seq = seq_order ? seq_order[blockIdx.z] : (int)blockIdx.z, head = blockIdx.y;
+    int seq = seq_order ? seq_order[blockIdx.z] : (int)blockIdx.z, head = blockIdx.x;
     int first_token = cu_seqlens[seq];
     int n_new = cu_seqlens[seq + 1] - first_token;
     int n_tiles = (n_new + BQ - 1) / BQ;
-    if ((int)blockIdx.x >= n_tiles) return;                  // uniform for the block: nothing is allocated yet
-    int tile = n_tiles - 1 - blockIdx.x;                     // the heaviest tile first
+    if ((int)blockIdx.y >= n_tiles) return;                  // uniform for the block: nothing is allocated yet
+    // blocks start in the order x, y, z: the heaviest tile of every head first, then the next
+    // lighter one of every head, so that the light tiles fill the end of the triangle's work
+    int tile = n_tiles - 1 - blockIdx.y;
     int start = seq_lens[seq] - n_new;
     int kv_head = head / (n_heads / n_kv_heads);
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -356,7 +358,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap
     int* status = status_word();
     int* status_dev = nullptr;
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
-    dim3 grid((max_new + BQ - 1) / BQ, n_heads, n_seqs);
+    dim3 grid(n_heads, (max_new + BQ - 1) / BQ, n_seqs);
     llmb::launch(attention_prefill_tc_kernel<HD>, grid, THREADS, smem, stream, true,
                  map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, seq_order,
                  (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f, status_dev);
@@ -376,7 +378,7 @@ LLMB_EXPORT int llmb_attention_prefill_tc(const void* q, int q_stride, int n_tok
     if (n_seqs == 0 || max_new == 0) return LLMB_OK;
     int code = llmb_attention_prefill_tc_supports(n_heads, n_kv_heads, head_dim, window);
     if (code) return code;
-    LLMB_REQUIRE(n_seqs <= 65535 && n_heads <= 65535 && ring_pages > 0 && n_pages > 0, "attention_prefill_tc: bad sizes");
+    LLMB_REQUIRE(n_seqs <= 65535 && max_new / BQ < 65535 && ring_pages > 0 && n_pages > 0, "attention_prefill_tc: bad sizes");
     LLMB_REQUIRE(q_stride % 8 == 0 && out_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0,
