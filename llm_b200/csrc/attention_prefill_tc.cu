@@ -214,20 +214,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tcgen05_fence_after();
             int key0 = kb * BKV;
             bool whole = key0 + BKV - 1 <= pos;              // no key of the block is hidden from this row
-            // first reading of the row: its maximum over the visible keys
+            // first reading of the row: its maximum over the visible keys. The next 32 columns are
+            // on their way from tensor memory while the last 32 are compared.
             float block_max = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BKV; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(lane_addr + S_COL + c, r);
+            auto row_max = [&](const uint32_t (&r)[32], int c) {
                 if (whole) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) block_max = fmaxf(block_max, __uint_as_float(r[j]));
+                    for (int j = 0; j < 32; j += 2)
+                        block_max = max3(block_max, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (key0 + c + j <= pos) block_max = fmaxf(block_max, __uint_as_float(r[j]));
                 }
+            };
+            {
+                uint32_t ra[32], rb[32];
+                tmem_ld32_start(lane_addr + S_COL, ra);
+                tmem_ld32_wait(ra);
+                tmem_ld32_start(lane_addr + S_COL + 32, rb);
+                row_max(ra, 0);
+                tmem_ld32_wait(rb);
+                tmem_ld32_start(lane_addr + S_COL + 64, ra);
+                row_max(rb, 32);
+                tmem_ld32_wait(ra);
+                tmem_ld32_start(lane_addr + S_COL + 96, rb);
+                row_max(ra, 64);
+                tmem_ld32_wait(rb);
+                row_max(rb, 96);
             }
             // The exponent's reference moves only when the block's maximum exceeds it by more than
             // 2^8 (softmax does not depend on the reference; probabilities up to 256 are as exact in
@@ -255,12 +269,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             run_max = new_max;
-            // second reading: probabilities, written back over the scores as bfloat16 pairs
+            // second reading: probabilities, written back over the scores as bfloat16 pairs (a chunk's
+            // probabilities land on columns that have been read already), again one chunk ahead
             float add = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BKV; c += 32) {
-                uint32_t r[32], packed[16];
-                tmem_ld32(lane_addr + S_COL + c, r);
+            auto to_probabilities = [&](const uint32_t (&r)[32], int c) {
+                uint32_t packed[16];
                 if (whole) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
@@ -279,6 +292,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     }
                 }
                 tmem_st16(lane_addr + P_COL + (c >> 1), packed);
+            };
+            {
+                uint32_t ra[32], rb[32];
+                tmem_ld32_start(lane_addr + S_COL, ra);
+                tmem_ld32_wait(ra);
+                tmem_ld32_start(lane_addr + S_COL + 32, rb);
+                to_probabilities(ra, 0);             // writes columns 0-15: read already
+                tmem_ld32_wait(rb);
+                tmem_ld32_start(lane_addr + S_COL + 64, ra);
+                to_probabilities(rb, 32);            // writes columns 16-31
+                tmem_ld32_wait(ra);
+                tmem_ld32_start(lane_addr + S_COL + 96, rb);
+                to_probabilities(ra, 64);            // writes columns 32-47
+                tmem_ld32_wait(rb);
+                to_probabilities(rb, 96);            // writes columns 48-63
             }
             run_sum = run_sum * alpha + add;
             tmem_st_wait();
