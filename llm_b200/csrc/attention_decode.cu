@@ -34,9 +34,14 @@ constexpr int WARPS = 4;
 constexpr int PAD = 8;                       // bf16 elements of row padding (bank spread)
 // Pages in the ring of a block: as many as fit in about 110 KB (two blocks an SM), between 3 and 8.
 // A small head size has small pages; it needs more of them in flight to keep HBM busy.
+// Pages per stage of the ring: two where a page is small (head sizes up to 64), so that the fixed
+// cost of a stage (the barrier, the wait for its copies) is paid once per 128 keys.
+template <int D>
+__host__ __device__ constexpr int pages_per_stage() { return D <= 64 ? 2 : 1; }
+
 template <int D>
 __host__ __device__ constexpr int stages_for() {
-    constexpr int bytes = 2 * LLMB_PAGE * (D + PAD) * 2;
+    constexpr int bytes = pages_per_stage<D>() * 2 * LLMB_PAGE * (D + PAD) * 2;
     constexpr int fit = (110 * 1024) / bytes;
     return fit < 3 ? 3 : fit > 8 ? 8 : fit;
 }
@@ -56,8 +61,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     constexpr int LDS = D + PAD;
     constexpr int PAGE_ELEMS = LLMB_PAGE * LDS;
     constexpr int STAGES = stages_for<D>();
+    constexpr int UNIT = pages_per_stage<D>();
+    constexpr int STAGE_ELEMS = UNIT * 2 * PAGE_ELEMS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [STAGES][2][64][LDS]
+    __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [STAGES][UNIT][k, v][64][LDS]
 
     // The kernel before this one in a step writes the queries and the newest position of the
     // cache; lengths, page tables and every older page are already final. So the first pages of
@@ -77,10 +84,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     int page_end = min(page_begin + per_split, n_pages);
     const int* pages = block_table + (size_t)seq * table_stride;
 
-    auto load_page = [&](int logical_page, int stage) {
+    auto load_page = [&](int logical_page, int stage, int place) {
         int page = pages[logical_page % ring_pages];
         size_t base = ((size_t)page * n_kv_heads + kv_head) * LLMB_PAGE * D;
-        __nv_bfloat16* ks = smem + (size_t)stage * 2 * PAGE_ELEMS;
+        __nv_bfloat16* ks = smem + (size_t)stage * STAGE_ELEMS + (size_t)place * 2 * PAGE_ELEMS;
         __nv_bfloat16* vs = ks + PAGE_ELEMS;
         constexpr int CHUNKS_PER_ROW = D / 8;
         for (int c = tid; c < LLMB_PAGE * CHUNKS_PER_ROW; c += WARPS * 32) {
@@ -90,18 +97,30 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     };
     int n_my = page_end - page_begin;
-    int late_stage = -1;                            // stage of the newest page, if it is among the first
+    int n_units = (n_my + UNIT - 1) / UNIT;         // stages' worth of pages in this slice
+    // unit u = pages page_begin + u * UNIT ... ; `hold_back`: leave out the page of the newest position
+    int late_unit = -1, late_place = 0;
+    auto load_unit = [&](int u, int stage, bool hold_back) {
+#pragma unroll
+        for (int place = 0; place < UNIT; ++place) {
+            int logical = page_begin + u * UNIT + place;
+            if (logical >= page_end) break;
+            if (hold_back && logical == n_pages - 1) {
+                late_unit = u;
+                late_place = place;
+            } else {
+                load_page(logical, stage, place);
+            }
+        }
+    };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_my) {
-            if (page_begin + s == n_pages - 1) late_stage = s;
-            else load_page(page_begin + s, s);
-        }
+        if (s < n_units) load_unit(s, s, true);
         cp_async_commit();
     }
     griddep_wait();
-    if (late_stage >= 0) {
-        load_page(page_begin + late_stage, late_stage);
+    if (late_unit >= 0) {
+        load_page(page_begin + late_unit * UNIT + late_place, late_unit, late_place);
         cp_async_commit();
     }
 
@@ -124,18 +143,22 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
     float run_max = -INFINITY, run_sum = 0.f;      // for head row g (this lane's keys only for the sum)
 
-    for (int i = 0; i < n_my; ++i) {
-        // the newest page, fetched late, is the last of its slice and the youngest group
-        if (late_stage >= 0 && i == n_my - 1) cp_async_wait<0>();
+    for (int i = 0; i < n_units; ++i) {
+        // the newest page, fetched late, is in the last unit of its slice and the youngest group
+        if (late_unit >= 0 && i == n_units - 1) cp_async_wait<0>();
         else cp_async_wait<STAGES - 2>();
-        __syncthreads();                            // page i landed; everyone is done with page i - 1
-        if (i + STAGES - 1 < n_my) load_page(page_begin + i + STAGES - 1, (i + STAGES - 1) % STAGES);
+        __syncthreads();                            // unit i landed; everyone is done with unit i - 1
+        if (i + STAGES - 1 < n_units) load_unit(i + STAGES - 1, (i + STAGES - 1) % STAGES, false);
         cp_async_commit();
 
-        const __nv_bfloat16* ks = smem + (size_t)(i % STAGES) * 2 * PAGE_ELEMS;
+#pragma unroll
+      for (int place = 0; place < UNIT; ++place) {
+        int logical = page_begin + i * UNIT + place;
+        if (logical >= page_end) break;
+        const __nv_bfloat16* ks = smem + (size_t)(i % STAGES) * STAGE_ELEMS + (size_t)place * 2 * PAGE_ELEMS;
         const __nv_bfloat16* vs = ks + PAGE_ELEMS;
         int key_base = warp * 16;
-        int first_key = (page_begin + i) * LLMB_PAGE + key_base;
+        int first_key = logical * LLMB_PAGE + key_base;
         if (first_key >= len) continue;             // this warp's 16 keys are all beyond the sequence
 
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -178,6 +201,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_bf16(acc[n], pa0, 0u, pa2, 0u, b[0], b[1]);
             mma_bf16(acc[n + 1], pa0, 0u, pa2, 0u, b[2], b[3]);
         }
+      }
     }
     cp_async_wait<0>();
     __syncthreads();                                 // the stage buffers are free: reuse them
@@ -248,7 +272,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                   int n_kv_heads, float scale, int n_splits, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
     constexpr int STAGES = stages_for<D>();
-    size_t stage_bytes = (size_t)STAGES * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
+    size_t stage_bytes = (size_t)STAGES * pages_per_stage<D>() * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
     size_t merge_bytes = (size_t)(WARPS * 8 * D + 2 * WARPS * 8) * sizeof(float);
     size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     static bool configured = false;
