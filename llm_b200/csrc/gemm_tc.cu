@@ -162,9 +162,11 @@ __device__ __forceinline__ Unit unit_of(int u, int tiles_a, int splits) {
 }
 
 // Stores 16 consecutive accumulator columns (c .. c+15) of this thread's row.
+// `preloaded` (swapped products with a residual only): the residual's values at these 16 places,
+// read by the caller earlier so that their latency ran under other loads.
 template <int BN>
 __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int a_row, int tile_b,
-                                              int c, float (&v)[16]) {
+                                              int c, float (&v)[16], const float* preloaded = nullptr) {
     if (swap && ep.glu) {
         // lanes 0-15 of a warp hold 16 gate rows, lanes 16-31 the up rows of the same features
         int lane = threadIdx.x & 31;
@@ -189,8 +191,10 @@ __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int 
             // wait for it (the compiler cannot know that the addresses differ)
             float old[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                old[j] = first_token + j < ep.tokens ? ep.residual[(size_t)(first_token + j) * ep.ldo + a_row] : 0.f;
+            for (int j = 0; j < 16; ++j) {
+                if (preloaded) old[j] = preloaded[j];
+                else old[j] = first_token + j < ep.tokens ? ep.residual[(size_t)(first_token + j) * ep.ldo + a_row] : 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j)
                 if (first_token + j < ep.tokens)
@@ -264,7 +268,7 @@ __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int 
 // buffers in tensor memory run on across units, so the loads and products of the next unit
 // overlap the epilogue of this one.
 template <int BN>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                Epilogue ep, int swap, int n_kblocks, int kblocks_per_split, int splits, int tiles_a,
                int n_units, float* __restrict__ partials, unsigned* __restrict__ counters,
@@ -479,25 +483,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const float* first = partials + tile_id * splits * (size_t)(BN * BM) + row;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
-                float v[16];
+                float v[16], old[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                // partials are added in split order; four splits' loads are in flight at once
-                for (int s0 = 0; s0 < splits; s0 += 4) {
-                    float t[4][16];
+                // columns that hold tokens (swapped products: the rest of the 16 is padding)
+                int valid = swap ? min(16, ep.tokens - (w.tile_b * BN + c)) : 16;
+                // the residual's values first: their latency runs under the partials' loads
+                bool preload = swap && ep.residual && !ep.glu && a_row < ep.outs;
+                if (preload) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        bool live = s0 + i < splits;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            t[i][j] = live ? __ldcg(first + (size_t)(s0 + i) * (BN * BM) + (size_t)(c + j) * BM) : 0.f;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] += t[i][j];
+                    for (int j = 0; j < 16; ++j)
+                        old[j] = j < valid ? ep.residual[(size_t)(w.tile_b * BN + c + j) * ep.ldo + a_row] : 0.f;
                 }
-                store_columns<BN>(ep, swap, a_row, w.tile_b, c, v);
+                // Partials are added in split order. With at most 8 valid columns, 8 splits' loads
+                // are in flight at once (a decode step of up to 8 sequences sums 9 splits in two
+                // rounds of loads instead of three over all 16 columns); else 4 splits of 16 columns.
+                if (valid <= 8) {
+                    for (int s0 = 0; s0 < splits; s0 += 8) {
+                        float t[8][8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            bool live = s0 + i < splits;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                t[i][j] = (live && j < valid) ? __ldcg(first + (size_t)(s0 + i) * (BN * BM) + (size_t)(c + j) * BM) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] += t[i][j];
+                    }
+                } else {
+                    for (int s0 = 0; s0 < splits; s0 += 4) {
+                        float t[4][16];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            bool live = s0 + i < splits;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                t[i][j] = (live && j < valid) ? __ldcg(first + (size_t)(s0 + i) * (BN * BM) + (size_t)(c + j) * BM) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) v[j] += t[i][j];
+                    }
+                }
+                store_columns<BN>(ep, swap, a_row, w.tile_b, c, v, preload ? old : nullptr);
             }
             if (threadIdx.x == 64) counters[tile_id] = 0u;
         }
