@@ -119,6 +119,27 @@ inline cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size
 
 }  // namespace llmb
 
+// Built with -DLLMB_TRACE (LLMB_NVCC_FLAGS=-DLLMB_TRACE), a kernel stamps the GPU's global timer
+// (nanoseconds) at the phases it names with LLMB_STAMP(slot, thread): thread `thread` of each of the
+// first LLMB_TRACE_BLOCKS blocks writes slot `slot` of its block's row. Otherwise the macro is empty.
+#define LLMB_TRACE_BLOCKS 296
+#define LLMB_TRACE_SLOTS 12
+#ifdef LLMB_TRACE
+__device__ unsigned long long llmb_trace_buffer[LLMB_TRACE_BLOCKS * LLMB_TRACE_SLOTS];
+__device__ __forceinline__ unsigned long long llmb_global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define LLMB_STAMP(slot, thread)                                                          \
+    do {                                                                                  \
+        if (threadIdx.x == (thread) && blockIdx.x < LLMB_TRACE_BLOCKS)                    \
+            llmb_trace_buffer[blockIdx.x * LLMB_TRACE_SLOTS + (slot)] = llmb_global_timer(); \
+    } while (0)
+#else
+#define LLMB_STAMP(slot, thread) do { } while (0)
+#endif
+
 #define LLMB_EXPORT extern "C" __attribute__((visibility("default")))
 
 // Each .cu file is built into a library of its own and defines its own reader

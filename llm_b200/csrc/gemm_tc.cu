@@ -267,12 +267,18 @@ __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int 
 // takes the units b, b + gridDim.x, ... . The shared-memory ring and the two accumulator
 // buffers in tensor memory run on across units, so the loads and products of the next unit
 // overlap the epilogue of this one.
+//
+// Split K: every block leaves its partial tile in global memory. Either the block that arrives
+// last at the tile's counter sums them in split order (one round of loads for up to 8 tokens), or,
+// with sum_later (more than 16 tokens: the tile is wide and one block would sum for a long time),
+// the blocks only write and splitk_sum_kernel, launched behind this kernel, sums with the whole
+// GPU. The order of the sum is the same on both ways.
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                Epilogue ep, int swap, int n_kblocks, int kblocks_per_split, int splits, int tiles_a,
                int n_units, float* __restrict__ partials, unsigned* __restrict__ counters,
-               int* status, int stages) {
+               int* status, int stages, int sum_later) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;       // two accumulator buffers
@@ -291,6 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    LLMB_STAMP(0, 0);                                           // the block has started
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -318,6 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Let the next kernel of the stream set itself up, and fetch this block's first weight tiles
     // (no kernel writes weights), while the kernel before this one is still running; the
     // activations, the residual and the split-K scratch are touched only after griddep_wait().
+    LLMB_STAMP(1, 0);                                           // barriers and tensor memory are set up
     griddep_launch();
     uint32_t early = 0;                                         // k-blocks whose weight tile is on its way
     if (warp == 0 && lane == 0 && (int)blockIdx.x < n_units) {
@@ -333,6 +341,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     }
     griddep_wait();
+    LLMB_STAMP(2, 0);                                           // the kernel before this one has completed
 
     if (warp == 0) {
         if (lane == 0) {
@@ -381,6 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     uint32_t round = it / stages;
                     ok = mbar_wait(smem_u32(&full_bar[s]), round & 1, abort_flag, status, 2);
                     if (!ok) break;
+                    if (it == 0) LLMB_STAMP(3, 32);             // the first operand tiles have landed
                     tcgen05_fence_after();
                     uint64_t a_desc = smem_desc(smem_u32(a_tiles + (size_t)s * A_BYTES));
                     uint64_t b_desc = smem_desc(smem_u32(b_tiles + (size_t)s * B_BYTES));
@@ -393,6 +403,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tcgen05_commit(smem_u32(&empty_bar[s]));
                 }
                 if (ok) tcgen05_commit(smem_u32(&acc_full_bar[buffer]));
+                LLMB_STAMP(4, 32);                              // the unit's last product is issued
             }
         }
     } else {
@@ -470,7 +481,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[buffer]));
+            if (sum_later) {
+                LLMB_STAMP(5, 64);
+                continue;                                           // the kernel's end publishes the partials
+            }
             __threadfence();
+            LLMB_STAMP(5, 64);                                      // the partial tile is written and fenced
             asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
             if (threadIdx.x == 64) {
                 unsigned arrived = atomicAdd(&counters[tile_id], 1u);
@@ -478,6 +494,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             bool last = *last_flag != 0;     // the flag is next written after the next unit's first barrier
+            LLMB_STAMP(6, 64);                                      // the tile's counter has answered
             if (!last) continue;
             __threadfence();
             const float* first = partials + tile_id * splits * (size_t)(BN * BM) + row;
@@ -532,6 +549,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 store_columns<BN>(ep, swap, a_row, w.tile_b, c, v, preload ? old : nullptr);
             }
             if (threadIdx.x == 64) counters[tile_id] = 0u;
+            LLMB_STAMP(7, 64);                                      // the last arriver has summed and stored
         }
     }
 
@@ -547,6 +565,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
+}
+
+// Sums the partial tiles of a swapped split-K product: one thread per (token, output feature),
+// the splits added in order, then bias / residual / store as the product's epilogue would.
+// Partials: [tile_b][tile_a][split][BN columns = tokens][128 rows = features].
+__global__ void __launch_bounds__(256)
+splitk_sum_kernel(const float* __restrict__ partials, Epilogue ep, int tiles_a, int splits, int bn) {
+    griddep_launch();
+    griddep_wait();
+    int token = blockIdx.y;
+    int feature = blockIdx.x * 256 + threadIdx.x;                  // with glu: the activated column
+    int n_features = ep.glu ? ep.outs / 2 : ep.outs;
+    if (feature >= n_features) return;
+    size_t tile_floats = (size_t)bn * BM;
+    auto row_sum = [&](int weight_row) {
+        int tile_a = weight_row / BM, row = weight_row % BM, tile_b = token / bn, col = token % bn;
+        const float* p = partials + ((size_t)tile_b * tiles_a + tile_a) * splits * tile_floats + (size_t)col * BM + row;
+        float v = 0.f;
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t[i] = s0 + i < splits ? __ldcg(p + (size_t)(s0 + i) * tile_floats) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v += t[i];
+        }
+        return v;
+    };
+    if (ep.glu) {
+        // weight rows alternate 16 gate rows, 16 up rows
+        int gate_row = (feature / LLMB_GLU_BLOCK) * 2 * LLMB_GLU_BLOCK + feature % LLMB_GLU_BLOCK;
+        float gate = row_sum(gate_row), up = row_sum(gate_row + LLMB_GLU_BLOCK);
+        reinterpret_cast<__nv_bfloat16*>(ep.out)[(size_t)token * ep.ldo + feature] = __float2bfloat16_rn(silu_mul(gate, up));
+        return;
+    }
+    float v = row_sum(feature) + (ep.bias ? ep.bias[feature] : 0.f);
+    size_t at = (size_t)token * ep.ldo + feature;
+    if (ep.residual) ep.residual[at] = ep.residual[at] + v;
+    else if (ep.out_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(ep.out)[at] = v;
 }
 
 // ------------------------------------------------------------------------- two SMs on one tile
@@ -833,6 +890,11 @@ int* status_word() {
     return host;
 }
 
+// Whether a swapped split-K product leaves the sum to splitk_sum_kernel: from 17 tokens. Up to 16
+// tokens both ways measured the same on a decode step (4.87 ms at batch 8), at 64 tokens the
+// kernel of its own is far ahead (O projection 21.8 -> 12.0 us).
+inline int sums_later(int swap, int splits, int bn) { return (swap && splits > 1 && bn >= 32) ? 1 : 0; }
+
 template <int BN>
 int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& ep, int swap,
            int tiles_a, int tiles_b, int n_kblocks, int per_split, int splits, float* partials,
@@ -863,9 +925,15 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
     int n_units = tiles_a * tiles_b * splits;
     int grid = n_units < n_sms * blocks_per_sm ? n_units : n_sms * blocks_per_sm;
+    int sum_later = sums_later(swap, splits, BN);
     llmb::launch(gemm_tc_kernel<BN>, grid, THREADS, smem, stream, true, map_a, map_b, ep, swap, n_kblocks, per_split,
-                 splits, tiles_a, n_units, partials, counters, status_dev, stages);
-    return check_launch("gemm_tc");
+                 splits, tiles_a, n_units, partials, counters, status_dev, stages, sum_later);
+    int code = check_launch("gemm_tc");
+    if (code || !sum_later) return code;
+    int n_features = ep.glu ? ep.outs / 2 : ep.outs;
+    llmb::launch(splitk_sum_kernel, dim3((n_features + 255) / 256, ep.tokens), 256, 0, stream, true,
+                 (const float*)partials, ep, tiles_a, splits, BN);
+    return check_launch("gemm_tc (split-K sum)");
 }
 
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& ep, int tiles_a,
@@ -930,6 +998,25 @@ Plan make_plan(int M, int N, int K) {
 
 // 0 if nothing went wrong since the last call of this function; else the code of the
 // wait that ran out (1 producer, 2 mma, 3 epilogue). Call after a synchronisation.
+// The stamps of the last launches (a build with -DLLMB_TRACE): LLMB_TRACE_BLOCKS rows of
+// LLMB_TRACE_SLOTS global-timer values, 0 where nothing was stamped. Returns 1 in a build without.
+LLMB_EXPORT int llmb_gemm_tc_trace(unsigned long long* out, int clear) {
+#ifdef LLMB_TRACE
+    size_t bytes = sizeof(unsigned long long) * LLMB_TRACE_BLOCKS * LLMB_TRACE_SLOTS;
+    if (cudaMemcpyFromSymbol(out, llmb_trace_buffer, bytes) != cudaSuccess) return 2;
+    if (clear) {
+        void* address = nullptr;
+        if (cudaGetSymbolAddress(&address, llmb_trace_buffer) != cudaSuccess || cudaMemset(address, 0, bytes) != cudaSuccess)
+            return 2;
+    }
+    return 0;
+#else
+    (void)out;
+    (void)clear;
+    return 1;
+#endif
+}
+
 LLMB_EXPORT int llmb_gemm_tc_status() {
     int* s = status_word();
     if (!s) return -1;
@@ -946,6 +1033,12 @@ LLMB_EXPORT long long llmb_gemm_tc_scratch_floats(int M, int N, int K) {
 LLMB_EXPORT int llmb_gemm_tc_counters(int M, int N, int K) {
     Plan p = make_plan(M, N, K);
     return p.tiles_a * p.tiles_b;
+}
+
+// Kernels a call launches (1, or 2 where the split-K sum is a kernel of its own).
+LLMB_EXPORT int llmb_gemm_tc_kernels(int M, int N, int K) {
+    Plan p = make_plan(M, N, K);
+    return 1 + sums_later(p.swap, p.splits, p.bn);
 }
 
 // out[M, N] = x[M, K] . w[N, K]^T (+ bias[N]); or residual[M, N] += the same.

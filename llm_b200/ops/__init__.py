@@ -225,6 +225,11 @@ def glu_fusable(n_rows: int, k: int, dtype) -> bool:
     return dtype == torch.bfloat16 and n_rows % (2 * GLU_BLOCK) == 0 and k % 8 == 0
 
 
+def _tc_kernels(m: int, n: int, k: int) -> int:
+    """Kernels one call of the tcgen05 product launches (2 where the split-K sum is its own kernel)."""
+    return load_library("gemm_tc").llmb_gemm_tc_kernels(_c_int(m), _c_int(n), _c_int(k))
+
+
 def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
     """a [M, K] . w [N, K]^T (+ bias [N], float32). With `residual` (float32
     [M, N]) the product is added to it in place and it is returned; otherwise a
@@ -243,7 +248,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
               _c_int(_code(a.dtype)), None, _ptr(partials), ctypes.c_longlong(partials.numel()),
               _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k),
               _c_int(n // 2), _c_int(1), _c_int(0 if tactics.is_disabled("gemm_tc_pair") else 1),
-              _stream())
+              _stream(), kernels=_tc_kernels(m, n, k))
         return result
     if k != k2 or a.dtype != w.dtype:
         raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype} does not fit w {tuple(w.shape)} {w.dtype}")
@@ -264,7 +269,8 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
               _ptr(result if residual is None else None), _c_int(_code(target_dtype)),
               _ptr(residual), _ptr(partials), ctypes.c_longlong(partials.numel()),
               _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k), _c_int(n),
-              _c_int(0), _c_int(0 if tactics.is_disabled("gemm_tc_pair") else 1), _stream())
+              _c_int(0), _c_int(0 if tactics.is_disabled("gemm_tc_pair") else 1), _stream(),
+              kernels=_tc_kernels(m, n, k))
     elif variant == "gemm_skinny":
         partials, counters = _skinny_scratch(a.device, m, n, k)
         _call("gemm_skinny", "llmb_gemm_skinny", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),

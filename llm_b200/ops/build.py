@@ -46,12 +46,18 @@ def _headers() -> list:
     return sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
 
 
+def _extra_flags() -> list:
+    """More nvcc flags from $LLMB_NVCC_FLAGS (for instance -DLLMB_TRACE); they are part of a
+    library's hash, so such a build lies beside the plain one."""
+    return os.environ.get("LLMB_NVCC_FLAGS", "").split()
+
+
 def _digest(source: Path) -> str:
     h = hashlib.sha256()
     for path in [source] + _headers():
         h.update(path.name.encode())
         h.update(path.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
     return h.hexdigest()[:16]
 
 
@@ -109,7 +115,7 @@ def compile_library(name: str) -> Path:
     out_dir = _writable_dir()
     target = out_dir / f"llmb_{name}-{_digest(source)}.so"
     scratch = out_dir / f".{target.name}.{os.getpid()}.{threading.get_ident()}.tmp"
-    command = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(scratch), str(source), "-lcuda"]
+    command = [_nvcc(), *NVCC_FLAGS, *_extra_flags(), "-I", str(CSRC), "-o", str(scratch), str(source), "-lcuda"]
     started = time.time()
     _say(f"compiling {source.name} for sm_100a ...")
     process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
@@ -127,7 +133,7 @@ def compile_library(name: str) -> Path:
             pass
         raise KernelError(f"nvcc failed on {source.name}:\n{output}")
     os.replace(scratch, target)
-    for stale in out_dir.glob(f"llmb_{name}-*.so"):      # earlier builds of this source
+    for stale in ([] if _extra_flags() else out_dir.glob(f"llmb_{name}-*.so")):      # earlier builds of this source
         if stale != target:
             try:
                 stale.unlink()

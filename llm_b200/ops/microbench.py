@@ -4,6 +4,7 @@
     python -m llm_b200.ops.microbench attention_decode --batch 8 --context 8192
     python -m llm_b200.ops.microbench attention_prefill --tokens 2048
     python -m llm_b200.ops.microbench rmsnorm --m 8 --k 4096
+    LLMB_NVCC_FLAGS=-DLLMB_TRACE python -m llm_b200.ops.microbench linear --m 8 --n 6144 --k 4096 --timeline
 
 Each call is timed inside a CUDA graph of `--reps` back-to-back launches (so that
 the host's launch cost is not in the number), with CUDA events, after warm-up.
@@ -12,6 +13,8 @@ HBM. `--once` runs a single plain launch after warm-up instead (for a profiler).
 Default sizes are those of a Llama-3.1-8B layer. The per-kernel table that
 MythEclipse/llm prints with LLM_PROFILE=1 (apps/engine/src/cuda/mod.rs:1917-1972)
 is the precedent; this tool isolates one kernel instead of wrapping every launch.
+`--timeline` (tcgen05 product, a build with -DLLMB_TRACE) prints when the blocks of the
+last launch passed the phases the kernel stamps with the GPU's global timer.
 """
 from __future__ import annotations
 
@@ -63,6 +66,44 @@ def run(fn, args, work_bytes=0.0, work_flops=0.0, label=""):
     print(line)
 
 
+PHASES = ["block started", "set-up done", "predecessor complete", "first tiles landed", "last product issued",
+          "partial written and fenced", "counter answered", "summed and stored (last arriver)"]
+
+
+def timeline(fn, label: str) -> int:
+    """Back-to-back launches of fn, then the global-timer stamps of the last one, in microseconds
+    after its first block started: earliest, median and latest block for every phase."""
+    import ctypes
+    from .build import load_library
+    lib = load_library("gemm_tc")
+    rows, slots = 296, 12
+    stamps = (ctypes.c_ulonglong * (rows * slots))()
+    for _ in range(20):
+        fn()
+    torch.cuda.synchronize()
+    if lib.llmb_gemm_tc_trace(stamps, 1) != 0:
+        print("this build has no stamps: set LLMB_NVCC_FLAGS=-DLLMB_TRACE", file=sys.stderr)
+        return 1
+    for _ in range(3):                       # the chain that is measured: the last of three launches
+        fn()
+    torch.cuda.synchronize()
+    lib.llmb_gemm_tc_trace(stamps, 0)
+    table = torch.tensor(list(stamps), dtype=torch.float64).view(rows, slots)
+    table = table[table[:, 0] > 0]
+    # every block of every launch overwrites its row: what is left belongs to the last launch,
+    # except phases that only some blocks reach (they may be older): those are cut at the start
+    start = table[:, 0].min()
+    print(f"{label}: {table.shape[0]} blocks; microseconds after the first block started")
+    for slot, name in enumerate(PHASES):
+        column = table[:, slot]
+        column = column[column >= start]
+        if column.numel():
+            relative = (column - start) / 1e3
+            print(f"  {name:34s}{relative.min():8.2f}{relative.median():8.2f}{relative.max():8.2f}"
+                  f"   ({column.numel()} blocks)")
+    return 0
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     p.add_argument("op", choices=["linear", "attention_decode", "attention_prefill", "rmsnorm",
@@ -80,6 +121,7 @@ def main(argv=None) -> int:
     p.add_argument("--residual", action="store_true", help="linear: add into a 32-bit residual")
     p.add_argument("--reps", type=int, default=20)
     p.add_argument("--once", action="store_true")
+    p.add_argument("--timeline", action="store_true", help="linear: phases of the last launch's blocks")
     args = p.parse_args(argv)
     torch.manual_seed(0)
     bf16 = torch.bfloat16
@@ -104,6 +146,8 @@ def main(argv=None) -> int:
             turn[0] += 1
         args.reps = max(args.reps, copies * 2) if not args.once else args.reps
         name = tactics.choose_linear(m, n, k, bf16, bf16, k)
+        if args.timeline:
+            return timeline(fn, f"linear {name} M={m} N={n} K={k}")
         run(fn, args, n * k * 2, 2.0 * m * n * k, f"linear {name} M={m} N={n} K={k}")
     elif args.op in ("attention_decode", "attention_prefill"):
         hq, hkv, d = args.heads, args.kv_heads, args.head_dim

@@ -145,10 +145,13 @@ def test_linear_tensor_core_kernel(m, n, k):
 
 
 @pytest.mark.parametrize("m,f,k", [(1, 64, 64), (8, 14336, 4096), (5, 208, 72), (64, 320, 128),
-                                   (70, 320, 128), (300, 1024, 520), (2048, 1024, 256)])
+                                   (70, 320, 128), (300, 1024, 520), (2048, 1024, 256),
+                                   (8, 320, 1024), (40, 320, 1024)])
 def test_linear_with_gated_epilogue(m, f, k):
     """silu(gate) * up in the epilogue of the tensor-core product, both orientations,
-    against the product followed by the plain activation."""
+    against the product followed by the plain activation. The last two shapes split K: the
+    activation is then applied where the splits are summed (by the last block of a tile at 8
+    tokens, by the sum kernel at 40)."""
     a = randn(m, k, dtype=torch.bfloat16, seed=96)
     gate = randn(f, k, dtype=torch.bfloat16, seed=97, scale=0.1)
     up = randn(f, k, dtype=torch.bfloat16, seed=98, scale=0.1)
