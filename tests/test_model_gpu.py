@@ -165,6 +165,37 @@ def test_family_shaped_model_prefill_and_decode(folders, plain, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_a_batch_of_seventy_sequences(folders, plain, dtype):
+    """More sequences than the decode products' 64-token orientation takes (their steps run the
+    kernels that prefill uses, on one token per sequence), lengths from 1 to 90, sequences
+    leaving along the way."""
+    from llm_b200.engine import Entry
+    config, weights = plain["F"]
+    engine = engine_for(folders["F"], dtype, max_tokens=70 * 128)
+    lengths = [1 + (7 * i) % 90 for i in range(70)]
+    seqs = [random_tokens(n + 4, config["vocab_size"], 500 + i) for i, n in enumerate(lengths)]
+    watch = [0, 13, 37, 69]
+    expected = {b: plain_llama.forward(config, weights, seqs[b]) for b in watch}
+    slots = engine.acquire(70)
+    logits = engine.step([Entry(slots[b], seqs[b][:lengths[b]], [lengths[b] - 1]) for b in range(70)])
+    for b in watch:
+        assert close(logits[b], expected[b][lengths[b] - 1], dtype), b
+    live = list(range(70))
+    for k in range(4):
+        logits = engine.step([Entry(slots[b], [seqs[b][lengths[b] + k]], [0]) for b in live])
+        for row, b in enumerate(live):
+            if b in watch:
+                assert close(logits[row], expected[b][lengths[b] + k], dtype), (b, k)
+        gone = [b for b in live if b % 4 == k and b not in watch]      # a quarter leaves after each step
+        engine.release([slots[b] for b in gone])
+        live = [b for b in live if b not in gone]
+    engine.release([slots[b] for b in live])
+    engine.cache.check()
+    engine.check()
+    assert engine.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_of_a_sequence(folders, plain, dtype):
     """Positions 0, 1, 2 decoded one by one from an empty slot."""
     from llm_b200.engine import Entry
