@@ -967,17 +967,26 @@ struct Plan {
     int swap, bn, tiles_a, tiles_b, n_kblocks, per_split, splits;
 };
 
+// The weights take the 128-row side of the tiles (tokens in tiles of up to 128 on the other) and K
+// is split whenever the 256 x 256 tiles of the pair kernel would fill less than 0.6 of the GPU's 74
+// pairs of SMs: always up to 128 tokens, and up to 1,024 tokens for products with few output
+// columns. (With the tokens on the 128-row side a 128 x 4096 x 4096 product has 16 tiles and took
+// 38 us, a 256 x 4096 x 14336 product 103 us; this way they take 16 and 44 us. At 512 x 6144 x 4096
+// the 48 pair tiles are faster again: 28 against 34 us.)
+constexpr int SWAP_TOKENS = 128, SWAP_TOKENS_MOST = 1024, PAIRS = 74;
+
 Plan make_plan(int M, int N, int K) {
     Plan p;
     p.n_kblocks = (K + BK - 1) / BK;
-    p.swap = M <= 64;
+    long long pair_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    p.swap = M <= SWAP_TOKENS || (M <= SWAP_TOKENS_MOST && pair_tiles * 5 < PAIRS * 3);
     if (p.swap) {
-        p.bn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+        p.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
         p.tiles_a = (N + BM - 1) / BM;
-        p.tiles_b = 1;
+        p.tiles_b = (M + p.bn - 1) / p.bn;
         // all blocks resident at once (two per SM): a second, partly filled wave would
         // double the time of a product this short
-        int want = (2 * 148) / p.tiles_a;
+        int want = (2 * 148) / (p.tiles_a * p.tiles_b);
         int most = p.n_kblocks / 4 > 0 ? p.n_kblocks / 4 : 1; // at least four k-blocks a block
         if (want > most) want = most;
         if (want > 32) want = 32;

@@ -87,9 +87,9 @@ const std::vector<Row>& table(int family) {
     static const std::vector<Row> linear = {
         {"gemm_tc", 30, tc_guard,
          "tcgen05.mma with the accumulator in tensor memory, operands by TMA; weights on the 128-row side and "
-         "split K for up to 64 tokens, tokens on it above (pairs of SMs on 256 x 256 tiles above 128 tokens). "
-         "Measured on a B200 at 4096 x 14336 layer sizes: about 1,200 TFLOP/s at 2,048 tokens, 3.9 to 5.9 TB/s "
-         "of weights at 8 tokens"},
+         "split K while the output has few tiles (always up to 128 tokens), pairs of SMs on 256 x 256 tiles "
+         "above. Measured on a B200 at Llama-3.1-8B layer sizes: about 1,200 TFLOP/s at 2,048 tokens, 3.1 to "
+         "5.9 TB/s of weights at 8 tokens, 16 us for 128 x 4096 x 4096"},
         {"gemm_skinny", 20, skinny_guard,
          "decode product for up to 64 rows: W streamed once with 128-bit loads into mma.sync fragments, K split "
          "over warps with an ordered last-arriver sum; within a few percent of gemm_tc at 8 rows, behind it from 16"},

@@ -119,7 +119,9 @@ def _check_decode_product(m, n, k):
                                    (513, 6144, 4096), (2048, 4096, 1024), (70, 72, 72),
                                    (300, 4104, 2048)])
 def test_linear_tensor_core_kernel(m, n, k):
-    """tcgen05 product with tokens on the 128-row side: tile edges in M, N and K."""
+    """tcgen05 product for more than 64 tokens: tile edges in M, N and K. Shapes with few output
+    tiles run with the weights on the 128-row side, several token tiles and split K (513 x 6144,
+    300 x 4104), the others as 256 x 256 tiles on pairs of SMs (2048 x 4096)."""
     from llm_b200.ops import tactics
     assert tactics.choose_linear(m, n, k, torch.bfloat16, torch.bfloat16, k) == "gemm_tc"
     a = randn(m, k, dtype=torch.bfloat16, seed=84)
