@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import atexit
 import ctypes
+import functools
 import os
 import sys
 
@@ -192,11 +193,19 @@ def _skinny_scratch(device, m, n, k):
     return _split_scratch(device, need // 4, (n + 15) // 16)
 
 
-def _tc_scratch(device, m, n, k):
+@functools.lru_cache(maxsize=4096)
+def _tc_needs(m: int, n: int, k: int) -> tuple:
+    """(floats of partial sums, tile counters, kernels launched) of a tcgen05 product of this shape."""
     lib = load_library("gemm_tc")
     lib.llmb_gemm_tc_scratch_floats.restype = ctypes.c_longlong
-    floats = lib.llmb_gemm_tc_scratch_floats(_c_int(m), _c_int(n), _c_int(k))
-    return _split_scratch(device, floats, lib.llmb_gemm_tc_counters(_c_int(m), _c_int(n), _c_int(k)))
+    return (lib.llmb_gemm_tc_scratch_floats(_c_int(m), _c_int(n), _c_int(k)),
+            lib.llmb_gemm_tc_counters(_c_int(m), _c_int(n), _c_int(k)),
+            lib.llmb_gemm_tc_kernels(_c_int(m), _c_int(n), _c_int(k)))
+
+
+def _tc_scratch(device, m, n, k):
+    floats, counters, _ = _tc_needs(m, n, k)
+    return _split_scratch(device, floats, counters)
 
 
 def tensor_core_status() -> int:
@@ -227,7 +236,7 @@ def glu_fusable(n_rows: int, k: int, dtype) -> bool:
 
 def _tc_kernels(m: int, n: int, k: int) -> int:
     """Kernels one call of the tcgen05 product launches (2 where the split-K sum is its own kernel)."""
-    return load_library("gemm_tc").llmb_gemm_tc_kernels(_c_int(m), _c_int(n), _c_int(k))
+    return _tc_needs(m, n, k)[2]
 
 
 def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
