@@ -23,6 +23,8 @@ LLMB_DEFINE_LAST_ERROR(llmb_sampling)
 constexpr int THREADS = 512;
 constexpr int MAX_TOP_K = 1024;
 constexpr int CANDIDATES = 2048;   // room for ties at the top-k threshold
+constexpr int RADIX_BINS = 2048;   // bins of the widest digit of the radix select
+constexpr int WINDOW = 1024;       // recent tokens the penalty handles in parallel (longer windows: one thread)
 
 __device__ __forceinline__ unsigned ordered_key(float v) {
     unsigned u = __float_as_uint(v);
@@ -38,13 +40,39 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
     return a;
 }
 
-// First maximum of row[0..n). NaN never wins (comparisons with NaN are false).
-__device__ ArgMax block_argmax(const float* row, int n, ArgMax* scratch) {
-    ArgMax best{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = row[i];
-        if (v > best.value) best = ArgMax{v, i};
+// Calls visit(value, index) for every element of row[0..n) that falls to this thread, in rising
+// index order. Rows that start on a 16-byte boundary are read four values a load and eight loads
+// ahead: a thread's share of a 128,256-entry row is 8 rounds of loads instead of 250 dependent ones
+// (one block has to keep enough bytes in flight to fetch half a megabyte quickly).
+template <typename Visit>
+__device__ __forceinline__ void for_each_of_row(const float* row, int n, Visit visit) {
+    int quads = (reinterpret_cast<uintptr_t>(row) & 15) == 0 ? n >> 2 : 0;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    auto visit4 = [&](const float4& v, int q) {
+        visit(v.x, 4 * q);
+        visit(v.y, 4 * q + 1);
+        visit(v.z, 4 * q + 2);
+        visit(v.w, 4 * q + 3);
+    };
+    int q = threadIdx.x;
+    for (; q + 7 * THREADS < quads; q += 8 * THREADS) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = row4[q + u * THREADS];          // eight loads in flight
+#pragma unroll
+        for (int u = 0; u < 8; ++u) visit4(v[u], q + u * THREADS);
     }
+    for (; q < quads; q += THREADS) visit4(row4[q], q);
+    for (int i = 4 * quads + threadIdx.x; i < n; i += THREADS) visit(row[i], i);
+}
+
+// First maximum of scale * row[0..n). NaN never wins (comparisons with NaN are false).
+__device__ ArgMax block_argmax(const float* row, int n, ArgMax* scratch, float scale = 1.0f) {
+    ArgMax best{-INFINITY, 0x7fffffff};
+    for_each_of_row(row, n, [&](float v, int i) {
+        v *= scale;
+        if (v > best.value) best = ArgMax{v, i};
+    });
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {
         ArgMax other{__shfl_xor_sync(0xffffffffu, best.value, offset),
@@ -98,11 +126,28 @@ __device__ __forceinline__ float next_uniform(unsigned long long* state) {
     return (float)(value >> 40) / 16777216.0f;
 }
 
+// Sum of `value` over the threads before this one (thread 0 first), for every thread of the block.
+__device__ unsigned block_exclusive_sum(unsigned value, unsigned* warp_totals) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned inclusive = value;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        unsigned below = __shfl_up_sync(0xffffffffu, inclusive, offset);
+        if (lane >= offset) inclusive += below;
+    }
+    if (lane == 31) warp_totals[warp] = inclusive;
+    __syncthreads();
+    unsigned before = 0u;
+    for (int w = 0; w < warp; ++w) before += warp_totals[w];
+    __syncthreads();
+    return before + inclusive - value;
+}
+
 // params[row] = {temperature, top_p, min_p, repeat_penalty}; iparams[row] =
 // {top_k, repeat_last_n}. recent[row, 0..recent_cap) holds the row's generated
 // tokens as a ring: token number i (counted from 0) is at recent[row, i % cap],
-// recent_len[row] counts all of them. `logits` is modified in place (penalty
-// and temperature). status[row] = 0, or 1 if the parameters were refused.
+// recent_len[row] counts all of them. `logits` is modified in place (the penalty
+// on the recent tokens' entries). status[row] = 0, or 1 if the parameters were refused.
 __global__ void __launch_bounds__(THREADS)
 sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
                    const float4* __restrict__ params, const int2* __restrict__ iparams,
@@ -110,24 +155,49 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
                    int recent_cap, unsigned long long* __restrict__ rng, int* __restrict__ out,
                    int* __restrict__ status) {
     __shared__ ArgMax scratch[32];
-    __shared__ unsigned histogram[256];
+    __shared__ unsigned histogram[RADIX_BINS];
+    __shared__ unsigned block_sums_u[32];
     __shared__ float cand_value[CANDIDATES];
     __shared__ int cand_index[CANDIDATES];
     __shared__ unsigned shared_prefix, shared_need, shared_count;
     __shared__ float block_sums[THREADS];
+    __shared__ int window[WINDOW];
 
     int row_id = blockIdx.x;
+    LLMB_STAMP(0, 0);
     float* row = logits + (size_t)row_id * stride;
     float temperature = params[row_id].x, top_p = params[row_id].y, min_p = params[row_id].z;
     float penalty = params[row_id].w;
     int top_k = iparams[row_id].x, last_n = iparams[row_id].y;
     int tid = threadIdx.x;
 
-    if (tid == 0) {
-        status[row_id] = 0;
-        if (penalty != 1.0f && last_n > 0 && recent != nullptr) {
-            int total = recent_len[row_id];
-            int span = min(min(total, last_n), recent_cap);
+    if (tid == 0) status[row_id] = 0;
+    if (penalty != 1.0f && last_n > 0 && recent != nullptr) {
+        // A token that occurs c times in the window is penalised c times, one after the other
+        // (apps/engine/src/sampler.rs:115-127). One thread per window place; the first place of a
+        // token applies all of its c steps, so the arithmetic is that of the serial loop.
+        int total = recent_len[row_id];
+        int span = min(min(total, last_n), recent_cap);
+        if (span <= WINDOW) {
+            for (int t = tid; t < span; t += THREADS)
+                window[t] = recent[(size_t)row_id * recent_cap + ((total - span + t) % recent_cap)];
+            __syncthreads();
+            for (int t = tid; t < span; t += THREADS) {
+                int id = window[t];
+                if (id < 0 || id >= vocab) continue;
+                int count = 0;
+                bool first = true;
+                for (int u = 0; u < span; ++u) {
+                    if (window[u] != id) continue;
+                    if (u < t) { first = false; break; }
+                    ++count;
+                }
+                if (!first) continue;
+                float v = row[id];
+                for (int c = 0; c < count; ++c) v = v > 0.f ? v / penalty : v * penalty;
+                row[id] = v;
+            }
+        } else if (tid == 0) {
             for (int i = total - span; i < total; ++i) {
                 int id = recent[(size_t)row_id * recent_cap + (i % recent_cap)];
                 if (id < 0 || id >= vocab) continue;
@@ -143,9 +213,10 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
         if (tid == 0) out[row_id] = best.index;
         return;
     }
+    // every later reading of the row takes its values times 1 / temperature (the same rounding each
+    // time) instead of a pass that writes the scaled row back
     float inverse = 1.0f / temperature;
-    for (int i = tid; i < vocab; i += THREADS) row[i] *= inverse;
-    __syncthreads();
+    LLMB_STAMP(1, 0);                                 // the penalty is applied
 
     if (top_k <= 0 || top_k >= vocab) {
         if (vocab <= MAX_TOP_K) {
@@ -162,13 +233,13 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
 
     if (top_k <= 0) {
         // ---- whole row, index order: softmax, min-p, inverse CDF
-        ArgMax best = block_argmax(row, vocab, scratch);
+        ArgMax best = block_argmax(row, vocab, scratch, inverse);
         float cut = min_p > 0.f ? min_p : 0.f;
         int per_thread = (vocab + THREADS - 1) / THREADS;
         int begin = min(tid * per_thread, vocab), end = min(begin + per_thread, vocab);
         float local = 0.f;
         for (int i = begin; i < end; ++i) {
-            float p = expf(row[i] - best.value);
+            float p = expf(row[i] * inverse - best.value);
             if (p >= cut) local += p;
         }
         block_sums[tid] = local;
@@ -190,7 +261,7 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
                 float remaining = target - before;
                 int b = min(owner * per_thread, vocab), e = min(b + per_thread, vocab);
                 for (int i = b; i < e; ++i) {
-                    float p = expf(row[i] - best.value);
+                    float p = expf(row[i] * inverse - best.value);
                     if (p < cut) continue;
                     pick = i;
                     remaining -= p;
@@ -202,42 +273,56 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
         return;
     }
 
-    // ---- ranked chain: radix select of the top_k-th largest key
+    // ---- ranked chain: radix select of the top_k-th largest key, three digits of 11, 11 and 10 bits.
+    // The first digit is the sign, the exponent and two bits of the mantissa: wide enough to spread
+    // a row of logits over some hundred bins, so that the threads' additions seldom meet.
     if (tid == 0) { shared_prefix = 0u; shared_need = (unsigned)top_k; }
     __syncthreads();
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = tid; i < 256; i += THREADS) histogram[i] = 0u;
+    for (int digit = 0; digit < 3; ++digit) {
+        const int shift = digit == 0 ? 21 : digit == 1 ? 10 : 0;
+        const int n_bins = digit == 2 ? 1024 : 2048;
+        for (int i = tid; i < RADIX_BINS; i += THREADS) histogram[i] = 0u;
         __syncthreads();
         unsigned prefix = shared_prefix;
-        unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-        for (int i = tid; i < vocab; i += THREADS) {
-            unsigned key = ordered_key(row[i]);
-            if ((key & mask) == prefix) atomicAdd(&histogram[(key >> shift) & 0xffu], 1u);
-        }
+        unsigned mask = digit == 0 ? 0u : (0xffffffffu << (digit == 1 ? 21 : 10));
+        for_each_of_row(row, vocab, [&](float v, int) {
+            unsigned key = ordered_key(v * inverse);
+            if ((key & mask) == prefix) atomicAdd(&histogram[(key >> shift) & (unsigned)(n_bins - 1)], 1u);
+        });
         __syncthreads();
-        if (tid == 0) {
-            unsigned need = shared_need;
-            int bin = 255;
-            for (; bin > 0; --bin) {
-                if (histogram[bin] >= need) break;
-                need -= histogram[bin];
+        // the bin, counted from the top, in which the running count reaches what is still needed:
+        // every thread sums four neighbouring bins, the block scans the threads from the top down
+        unsigned need = shared_need;
+        int top_bin = n_bins - 1 - 4 * tid;                       // this thread's highest bin
+        unsigned mine = 0u;
+        if (top_bin >= 3)
+            mine = histogram[top_bin] + histogram[top_bin - 1] + histogram[top_bin - 2] + histogram[top_bin - 3];
+        unsigned before = block_exclusive_sum(mine, block_sums_u);  // of the threads with higher bins
+        if (top_bin >= 3 && before < need && before + mine >= need) {
+            unsigned left = need - before;
+            int bin = top_bin;
+            for (; bin > top_bin - 3; --bin) {
+                if (histogram[bin] >= left) break;
+                left -= histogram[bin];
             }
-            shared_need = need;
+            shared_need = left;
             shared_prefix = prefix | ((unsigned)bin << shift);
         }
         __syncthreads();
     }
+    LLMB_STAMP(2, 0);                                 // the radix select has its threshold
     unsigned threshold = shared_prefix;        // key of the top_k-th largest value
     if (tid == 0) shared_count = 0u;
     __syncthreads();
-    for (int i = tid; i < vocab; i += THREADS) {
-        float v = row[i];
+    for_each_of_row(row, vocab, [&](float v, int i) {
+        v *= inverse;
         if (ordered_key(v) >= threshold) {
             unsigned at = atomicAdd(&shared_count, 1u);
             if (at < CANDIDATES) { cand_value[at] = v; cand_index[at] = i; }
         }
-    }
+    });
     __syncthreads();
+    LLMB_STAMP(3, 0);                                 // the candidates are gathered
     int count = (int)min(shared_count, (unsigned)CANDIDATES);
     if (shared_count > (unsigned)CANDIDATES) {
         // more ties at the threshold than the buffer holds
@@ -267,6 +352,7 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
             __syncthreads();
         }
     }
+    LLMB_STAMP(4, 0);                                 // the candidates are sorted
     int kept = min(count, top_k);
     float top_value = cand_value[0];
     for (int i = tid; i < kept; i += THREADS) cand_value[i] = expf(cand_value[i] - top_value);
@@ -302,7 +388,18 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
             }
         }
         out[row_id] = pick;
+        LLMB_STAMP(5, 0);                             // the token is drawn
     }
+}
+
+// The stamps of the last sampling launch in a build with -DLLMB_TRACE (see common.cuh); 1 otherwise.
+LLMB_EXPORT int llmb_sampling_trace(unsigned long long* out) {
+#ifdef LLMB_TRACE
+    return cudaMemcpyFromSymbol(out, llmb_trace_buffer, sizeof(unsigned long long) * LLMB_TRACE_BLOCKS * LLMB_TRACE_SLOTS) == cudaSuccess ? 0 : 2;
+#else
+    (void)out;
+    return 1;
+#endif
 }
 
 LLMB_EXPORT int llmb_sample_rows(float* logits, int stride, int n_rows, int vocab,
