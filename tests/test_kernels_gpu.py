@@ -442,10 +442,11 @@ def _sampler_state(n, params, iparams, seeds, cap=8):
     return f, i, recent, recent_len, rng, out, status
 
 
-@pytest.mark.parametrize("vocab", [384, 5000])
+@pytest.mark.parametrize("vocab", [384, 5000, 50001])
 def test_sample_rows_matches_plain_chain(vocab):
     """Greedy, temperature with top-k / top-p / min-p, penalty, and no top-k at all:
-    the same tokens and generator states as the plain chain, over several draws."""
+    the same tokens and generator states as the plain chain, over several draws. 50,001 entries:
+    rows that are read four values a load, eight loads ahead, with a tail that is not."""
     params = [[0.0, 0.75, 0.25, 1.0], [0.8, 0.75, 0.25, 1.1], [1.5, 0.95, 0.0, 1.3],
               [1.0, 1.0, 0.0, 1.0], [0.7, 2.0, 0.05, 1.0]]
     iparams = [[40, 64], [40, 64], [7, 4], [0, 0], [0, 0]]
