@@ -151,9 +151,9 @@ __device__ unsigned block_exclusive_sum(unsigned value, unsigned* warp_totals) {
 __global__ void __launch_bounds__(THREADS)
 sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
                    const float4* __restrict__ params, const int2* __restrict__ iparams,
-                   const int* __restrict__ recent, const int* __restrict__ recent_len,
+                   int* __restrict__ recent, int* __restrict__ recent_len,
                    int recent_cap, unsigned long long* __restrict__ rng, int* __restrict__ out,
-                   int* __restrict__ status) {
+                   int* __restrict__ status, int record, const int* __restrict__ state_rows) {
     __shared__ ArgMax scratch[32];
     __shared__ unsigned histogram[RADIX_BINS];
     __shared__ unsigned block_sums_u[32];
@@ -163,13 +163,26 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
     __shared__ float block_sums[THREADS];
     __shared__ int window[WINDOW];
 
-    int row_id = blockIdx.x;
+    // row of logits and of `out`; the sequence's parameters, window, generator and status are in
+    // row state_rows[row] of their arrays (the same row if state_rows is null)
+    int logits_row = blockIdx.x;
+    int row_id = state_rows ? state_rows[logits_row] : logits_row;
     LLMB_STAMP(0, 0);
-    float* row = logits + (size_t)row_id * stride;
+    float* row = logits + (size_t)logits_row * stride;
     float temperature = params[row_id].x, top_p = params[row_id].y, min_p = params[row_id].z;
     float penalty = params[row_id].w;
     int top_k = iparams[row_id].x, last_n = iparams[row_id].y;
     int tid = threadIdx.x;
+    // thread 0 calls this once: the token is the row's result and, with `record`, the newest entry
+    // of the row's window (a ring over its generated tokens)
+    auto finish = [&](int token) {
+        out[logits_row] = token;
+        if (record && recent != nullptr) {
+            int total = recent_len[row_id];
+            recent[(size_t)row_id * recent_cap + (total % recent_cap)] = token;
+            recent_len[row_id] = total + 1;
+        }
+    };
 
     if (tid == 0) status[row_id] = 0;
     if (penalty != 1.0f && last_n > 0 && recent != nullptr) {
@@ -210,7 +223,7 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
 
     if (!(temperature > 0.f)) {
         ArgMax best = block_argmax(row, vocab, scratch);
-        if (tid == 0) out[row_id] = best.index;
+        if (tid == 0) finish(best.index);
         return;
     }
     // every later reading of the row takes its values times 1 / temperature (the same rounding each
@@ -223,11 +236,11 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
             top_k = vocab;                      // a small row: rank all of it
         } else if (top_k > 0 || (top_p >= 0.f && top_p < 1.f)) {
             // the ranked chain is limited to MAX_TOP_K candidates
-            if (tid == 0) { status[row_id] = 1; out[row_id] = 0; }
+            if (tid == 0) { status[row_id] = 1; finish(0); }
             return;
         }
     } else if (top_k > MAX_TOP_K) {
-        if (tid == 0) { status[row_id] = 1; out[row_id] = 0; }
+        if (tid == 0) { status[row_id] = 1; finish(0); }
         return;
     }
 
@@ -268,7 +281,7 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
                     if (remaining <= 0.f) break;
                 }
             }
-            out[row_id] = pick;
+            finish(pick);
         }
         return;
     }
@@ -326,7 +339,7 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
     int count = (int)min(shared_count, (unsigned)CANDIDATES);
     if (shared_count > (unsigned)CANDIDATES) {
         // more ties at the threshold than the buffer holds
-        if (tid == 0) { status[row_id] = 1; out[row_id] = 0; }
+        if (tid == 0) { status[row_id] = 1; finish(0); }
         return;
     }
     // bitonic sort, descending by value, ascending by index among equals
@@ -387,7 +400,7 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
                 if (target <= 0.f) { pick = cand_index[i]; break; }
             }
         }
-        out[row_id] = pick;
+        finish(pick);
         LLMB_STAMP(5, 0);                             // the token is drawn
     }
 }
@@ -403,15 +416,15 @@ LLMB_EXPORT int llmb_sampling_trace(unsigned long long* out) {
 }
 
 LLMB_EXPORT int llmb_sample_rows(float* logits, int stride, int n_rows, int vocab,
-                                 const float* params, const int* iparams, const int* recent,
-                                 const int* recent_len, int recent_cap,
-                                 unsigned long long* rng, int* out, int* status,
-                                 cudaStream_t stream) {
+                                 const float* params, const int* iparams, int* recent,
+                                 int* recent_len, int recent_cap,
+                                 unsigned long long* rng, int* out, int* status, int record,
+                                 const int* state_rows, cudaStream_t stream) {
     if (n_rows == 0) return LLMB_OK;
     LLMB_REQUIRE(n_rows > 0 && vocab > 0 && stride >= vocab, "sample: bad sizes");
     LLMB_REQUIRE(recent == nullptr || recent_cap > 0, "sample: recent window without capacity");
     sample_rows_kernel<<<n_rows, THREADS, 0, stream>>>(
         logits, stride, vocab, (const float4*)params, (const int2*)iparams, recent, recent_len,
-        recent_cap, rng, out, status);
+        recent_cap, rng, out, status, record, state_rows);
     return check_launch("sample_rows");
 }

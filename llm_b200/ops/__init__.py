@@ -404,17 +404,21 @@ def argmax_rows(logits, out=None):
     return out
 
 
-def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, status):
+def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, status, record=False,
+                state_rows=None):
     """The whole sampling chain for every row; see csrc/sampling.cu. `logits`
-    (float32 [B, V]) is overwritten. params float32 [B, 4], iparams int32 [B, 2],
-    recent int32 [B, cap] or None, recent_len int32 [B], rng_state int64 [B],
-    out int32 [B], status int32 [B]."""
+    (float32 [B, V]) is changed where the repeat penalty applies. params float32 [B, 4],
+    iparams int32 [B, 2], recent int32 [B, cap] or None, recent_len int32 [B], rng_state
+    int64 [B], out int32 [B], status int32 [B]. With `record` the kernel also enters every
+    drawn token into its row's window (recent, recent_len). `state_rows` (int32 [B], optional):
+    row i of the logits belongs to the sequence whose parameters, window, generator and status
+    are in row state_rows[i] of those arrays (which may then have more rows than the logits)."""
     _require_cuda(logits, params, iparams, recent, rng_state, out, status)
     n, vocab = logits.shape
     _call("sampling", "llmb_sample_rows", _ptr(logits), _c_int(logits.stride(0)), _c_int(n),
           _c_int(vocab), _ptr(params), _ptr(iparams), _ptr(recent), _ptr(recent_len),
           _c_int(recent.shape[1] if recent is not None else 0), _ptr(rng_state), _ptr(out),
-          _ptr(status), _stream())
+          _ptr(status), _c_int(1 if record else 0), _ptr(state_rows), _stream())
     return out
 
 

@@ -55,26 +55,14 @@ class BatchSampler:
             raise KernelError("sample: one logits row per live sequence is needed")
         if self.all_greedy:
             return ops.argmax_rows(logits)
-        index = None
+        state_rows = None
         if len(rows) != self.n or rows != list(range(self.n)):
-            index = torch.tensor(rows, dtype=torch.long, device=self.device)
-        take = (lambda t: t) if index is None else (lambda t: t[index].contiguous())
-        fparams, iparams, rng = take(self.fparams), take(self.iparams), take(self.rng)
-        recent, recent_len, status = take(self.recent), take(self.recent_len), take(self.status)
+            state_rows = torch.tensor(rows, dtype=torch.int32, device=self.device)
         out = torch.empty((len(rows),), dtype=torch.int32, device=self.device)
-        ops.sample_rows(logits, fparams, iparams, recent, recent_len, rng, out, status)
-        # record the drawn tokens in the windows (a ring over the generated tokens)
-        cap = self.recent.shape[1]
-        where = (recent_len % cap).long()
-        recent[torch.arange(len(rows), device=self.device), where] = out
-        recent_len = recent_len + 1
-        if index is None:
-            self.rng, self.recent, self.recent_len, self.status = rng, recent, recent_len, status
-        else:
-            self.rng[index] = rng
-            self.recent[index] = recent
-            self.recent_len[index] = recent_len
-            self.status[index] = status
+        # one launch: the kernel finds each row's sequence state through state_rows and also
+        # records the drawn tokens in the windows (a ring over the generated tokens)
+        ops.sample_rows(logits, self.fparams, self.iparams, self.recent, self.recent_len, self.rng, out,
+                        self.status, record=True, state_rows=state_rows)
         return out
 
     def check_status(self) -> None:

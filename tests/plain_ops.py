@@ -129,7 +129,7 @@ def _next_uniform(state):
     return x, float(value >> 40) / float(1 << 24)
 
 
-def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, status):
+def _sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, status):
     """Row by row, the chain of csrc/sampling.cu in 32-bit host arithmetic."""
     n, vocab = logits.shape
     f32 = torch.float32
@@ -202,6 +202,29 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
         rng_state[r] = state - (1 << 64) if state >= (1 << 63) else state
         out[r] = pick
     return out
+
+
+def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, status, record=False,
+                state_rows=None):
+    """The chain for every row; with `record`, the drawn tokens then enter the rows' windows.
+    `state_rows`: row i of the logits belongs to the sequence in row state_rows[i] of the state."""
+    if state_rows is not None:
+        index = state_rows.long()
+        taken = [t[index].clone() if t is not None else None
+                 for t in (params, iparams, recent, recent_len, rng_state, status)]
+        sample_rows(logits, taken[0], taken[1], taken[2], taken[3], taken[4], out, taken[5], record)
+        for whole, part in zip((recent, recent_len, rng_state, status), (taken[2], taken[3], taken[4], taken[5])):
+            if whole is not None:
+                whole[index] = part
+        return out
+    _sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, status)
+    if record and recent is not None:
+        cap = recent.shape[1]
+        for r in range(logits.shape[0]):
+            recent[r, int(recent_len[r]) % cap] = int(out[r])
+            recent_len[r] += 1
+    return out
+
 
 
 OPS = {"embed": embed, "rmsnorm": rmsnorm, "swiglu": swiglu, "linear": linear,

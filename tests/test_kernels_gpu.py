@@ -469,6 +469,32 @@ def test_sample_rows_matches_plain_chain(vocab):
         assert state_gpu[6].tolist() == [0] * n
 
 
+def test_sample_rows_records_windows_and_finds_state_by_row():
+    """Three logits rows that belong to sequences 4, 0 and 2 of a batch of five: the kernel takes each
+    row's parameters, window and generator from its sequence's row, enters the drawn token into that
+    window, and leaves the other sequences' state alone; three draws in a row against the plain chain."""
+    vocab, n = 777, 5
+    params = [[0.9, 0.9, 0.05, 1.2]] * n
+    iparams = [[30, 6]] * n
+    state_gpu = _sampler_state(n, params, iparams, [11, 12, 13, 14, 15], cap=6)
+    state_cpu = [t.cpu().clone() for t in state_gpu]
+    rows = torch.tensor([4, 0, 2], dtype=torch.int32)
+    out_gpu, out_cpu = torch.zeros(3, dtype=torch.int32, device=DEV), torch.zeros(3, dtype=torch.int32)
+    for draw in range(8):                               # more draws than the window holds
+        logits = randn(3, vocab, seed=200 + draw, scale=2.0)
+        cpu_logits = logits.cpu().clone()
+        f, i, recent, recent_len, rng, _, status = state_gpu
+        ops().sample_rows(logits, f, i, recent, recent_len, rng, out_gpu, status, record=True,
+                          state_rows=rows.to(DEV))
+        f, i, recent, recent_len, rng, _, status = state_cpu
+        plain_ops.sample_rows(cpu_logits, f, i, recent, recent_len, rng, out_cpu, status, record=True,
+                              state_rows=rows)
+        assert out_gpu.tolist() == out_cpu.tolist(), draw
+        for g, c in zip(state_gpu[2:5], state_cpu[2:5]):
+            assert g.tolist() == c.tolist(), draw
+    assert state_gpu[3].tolist() == [8, 0, 8, 0, 8]
+
+
 def test_sample_rows_refuses_what_it_cannot_rank():
     f, i, recent, recent_len, rng, out, status = _sampler_state(
         2, [[1.0, 0.9, 0.0, 1.0], [1.0, 1.0, 0.0, 1.0]], [[0, 0], [2000, 0]], [1, 2])
