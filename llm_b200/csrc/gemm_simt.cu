@@ -17,12 +17,50 @@ using namespace llmb;
 
 LLMB_DEFINE_LAST_ERROR(llmb_gemm_simt)
 
+// Loads rows [row0, row0 + ROWS) x columns [k0, k0 + BK) of a row-major matrix into `held`: every
+// thread takes items of four consecutive k (one 16-byte load where `vector` holds: 32-bit elements,
+// rows that start on 16-byte boundaries, K a multiple of 4); outside the matrix the value is 0.
+template <typename TIn, int ROWS, int BK, int THREADS, int ITEMS>
+__device__ __forceinline__ void fetch_tile(const TIn* __restrict__ base, int n_rows, int K, int ld, int row0, int k0,
+                                           bool vector, float (&held)[ITEMS][4]) {
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        int item = threadIdx.x + it * THREADS;            // item = (row, group of four k)
+        int r = item / (BK / 4), kk = (item % (BK / 4)) * 4;
+        int row = row0 + r, k = k0 + kk;
+        bool inside = item < ROWS * (BK / 4) && row < n_rows;
+        if (inside && vector && k + 3 < K) {
+            float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + (size_t)row * ld + k);
+            held[it][0] = v.x; held[it][1] = v.y; held[it][2] = v.z; held[it][3] = v.w;
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                held[it][q] = (inside && k + q < K) ? to_float(base[(size_t)row * ld + k + q]) : 0.f;
+        }
+    }
+}
+
+template <int ROWS, int BK, int THREADS, int ITEMS, int LD>
+__device__ __forceinline__ void park_tile(float (*tile)[LD], const float (&held)[ITEMS][4]) {
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        int item = threadIdx.x + it * THREADS;
+        if (item >= ROWS * (BK / 4)) continue;
+        int r = item / (BK / 4), kk = (item % (BK / 4)) * 4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) tile[kk + q][r] = held[it][q];
+    }
+}
+
+// The next tiles are on their way from memory (into registers) while the current ones, in shared
+// memory, are multiplied; the order of a thread's additions is k = 0, 1, 2, ... as before.
 template <typename TIn, typename TOut, int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w,
                  const float* __restrict__ bias, TOut* __restrict__ out,
-                 float* __restrict__ residual, int M, int N, int K, int lda, int ldc) {
+                 float* __restrict__ residual, int M, int N, int K, int lda, int ldc, int vector) {
     constexpr int THREADS = (BM / TM) * (BN / TN);
+    constexpr int A_ITEMS = (BM * BK / 4 + THREADS - 1) / THREADS, W_ITEMS = (BN * BK / 4 + THREADS - 1) / THREADS;
     __shared__ float a_tile[BK][BM + 4];
     __shared__ float w_tile[BK][BN + 4];
     int tid = threadIdx.x;
@@ -34,18 +72,17 @@ gemm_simt_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w,
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
 
+    float a_held[A_ITEMS][4], w_held[W_ITEMS][4];
+    fetch_tile<TIn, BM, BK, THREADS, A_ITEMS>(a, M, K, lda, m0, 0, vector != 0, a_held);
+    fetch_tile<TIn, BN, BK, THREADS, W_ITEMS>(w, N, K, K, n0, 0, vector != 0, w_held);
     for (int k0 = 0; k0 < K; k0 += BK) {
-        for (int idx = tid; idx < BM * BK; idx += THREADS) {
-            int r = idx / BK, kk = idx % BK;
-            int m = m0 + r, k = k0 + kk;
-            a_tile[kk][r] = (m < M && k < K) ? to_float(a[(size_t)m * lda + k]) : 0.f;
-        }
-        for (int idx = tid; idx < BN * BK; idx += THREADS) {
-            int r = idx / BK, kk = idx % BK;
-            int n = n0 + r, k = k0 + kk;
-            w_tile[kk][r] = (n < N && k < K) ? to_float(w[(size_t)n * K + k]) : 0.f;
-        }
+        park_tile<BM, BK, THREADS, A_ITEMS, BM + 4>(a_tile, a_held);
+        park_tile<BN, BK, THREADS, W_ITEMS, BN + 4>(w_tile, w_held);
         __syncthreads();
+        if (k0 + BK < K) {
+            fetch_tile<TIn, BM, BK, THREADS, A_ITEMS>(a, M, K, lda, m0, k0 + BK, vector != 0, a_held);
+            fetch_tile<TIn, BN, BK, THREADS, W_ITEMS>(w, N, K, K, n0, k0 + BK, vector != 0, w_held);
+        }
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             float av[TM], wv[TN];
@@ -79,14 +116,17 @@ gemm_simt_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w,
 template <typename TIn, typename TOut>
 static int launch(const void* a, const void* w, const float* bias, void* out, float* residual,
                   int M, int N, int K, int lda, int ldc, cudaStream_t stream) {
+    // 16-byte loads: 32-bit elements, every row of both operands on a 16-byte boundary
+    int vector = sizeof(TIn) == 4 && K % 4 == 0 && lda % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     if (M > 64) {
         dim3 grid(ceil_div(N, 128), ceil_div(M, 128));
         gemm_simt_kernel<TIn, TOut, 128, 128, 8, 8, 8><<<grid, 256, 0, stream>>>(
-            (const TIn*)a, (const TIn*)w, bias, (TOut*)out, residual, M, N, K, lda, ldc);
+            (const TIn*)a, (const TIn*)w, bias, (TOut*)out, residual, M, N, K, lda, ldc, vector);
     } else {
         dim3 grid(ceil_div(N, 64), ceil_div(M, 32));
         gemm_simt_kernel<TIn, TOut, 32, 64, 16, 2, 4><<<grid, 256, 0, stream>>>(
-            (const TIn*)a, (const TIn*)w, bias, (TOut*)out, residual, M, N, K, lda, ldc);
+            (const TIn*)a, (const TIn*)w, bias, (TOut*)out, residual, M, N, K, lda, ldc, vector);
     }
     return check_launch("gemm_simt");
 }
