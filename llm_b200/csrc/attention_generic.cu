@@ -3,7 +3,7 @@
 // path and the fallback of the bfloat16 path.
 //
 // One block per (token, query head), four warps; warp w takes the visible keys
-// first + w, first + w + 4, ... one key per iteration with the lanes spread over
+// first + w, first + w + 4, ... key after key (four of them fetched at a time) with the lanes spread over
 // the head dimension (the shape of attention_split in MythEclipse/llm,
 // apps/engine/kernels/gpu.cu:649-733), keeps a running (max, sum, weighted
 // values) and the four partial results are merged in a fixed order with
@@ -25,7 +25,10 @@ LLMB_DEFINE_LAST_ERROR(llmb_attention_generic)
 constexpr int MAX_PER_LANE = LLMB_MAX_HEAD_DIM / 32;   // elements of a head per lane
 constexpr int WARPS = 4;
 
-template <typename T>
+// AHEAD: keys a warp fetches together. Four hide the loads' latency where a step has few blocks
+// (decoding); with thousands of blocks the SMs are full of other blocks' work and the registers
+// of one key at a time keep more of them resident.
+template <typename T, int AHEAD>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_cache,
                          const T* __restrict__ v_cache, const int* __restrict__ block_table,
@@ -50,28 +53,45 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
     }
     float running_max = -INFINITY, running_sum = 0.f;
 
-    for (int j = first + warp; j <= pos; j += WARPS) {
-        int page = pages[(j / LLMB_PAGE) % ring_pages];
-        size_t offset = (((size_t)page * n_kv_heads + kv_head) * LLMB_PAGE + (j % LLMB_PAGE)) * head_dim;
-        const T* k_row = k_cache + offset;
-        const T* v_row = v_cache + offset;
-        float dot = 0.f;
+    // AHEAD keys of this warp are read together (their loads overlap), then folded into the running
+    // state one after the other: the arithmetic and its order are those of one key per iteration.
+    for (int j0 = first + warp; j0 <= pos; j0 += WARPS * AHEAD) {
+        float kv[AHEAD][MAX_PER_LANE], vv[AHEAD][MAX_PER_LANE];
 #pragma unroll
-        for (int i = 0; i < MAX_PER_LANE; ++i) {
-            int d = lane + 32 * i;
-            if (d < head_dim) dot = fmaf(qv[i], to_float(k_row[d]), dot);
-        }
-        float score = warp_sum(dot) * scale;
-        float new_max = fmaxf(running_max, score);
-        float rescale = expf(running_max - new_max);    // exp(-inf) = 0 on the first key
-        float p = expf(score - new_max);
-        running_sum = running_sum * rescale + p;
+        for (int u = 0; u < AHEAD; ++u) {
+            int j = j0 + u * WARPS;
+            bool visible = j <= pos;
+            int page = visible ? pages[(j / LLMB_PAGE) % ring_pages] : 0;
+            size_t offset = (((size_t)page * n_kv_heads + kv_head) * LLMB_PAGE + (j % LLMB_PAGE)) * head_dim;
 #pragma unroll
-        for (int i = 0; i < MAX_PER_LANE; ++i) {
-            int d = lane + 32 * i;
-            if (d < head_dim) acc[i] = fmaf(p, to_float(v_row[d]), acc[i] * rescale);
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                int d = lane + 32 * i;
+                bool live = visible && d < head_dim;
+                kv[u][i] = live ? to_float(k_cache[offset + d]) : 0.f;
+                vv[u][i] = live ? to_float(v_cache[offset + d]) : 0.f;
+            }
         }
-        running_max = new_max;
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u) {
+            if (j0 + u * WARPS > pos) break;
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                int d = lane + 32 * i;
+                if (d < head_dim) dot = fmaf(qv[i], kv[u][i], dot);
+            }
+            float score = warp_sum(dot) * scale;
+            float new_max = fmaxf(running_max, score);
+            float rescale = expf(running_max - new_max);    // exp(-inf) = 0 on the first key
+            float p = expf(score - new_max);
+            running_sum = running_sum * rescale + p;
+#pragma unroll
+            for (int i = 0; i < MAX_PER_LANE; ++i) {
+                int d = lane + 32 * i;
+                if (d < head_dim) acc[i] = fmaf(p, vv[u][i], acc[i] * rescale);
+            }
+            running_max = new_max;
+        }
     }
 
     __shared__ float part_acc[WARPS][MAX_PER_LANE * 32];
@@ -117,17 +137,18 @@ LLMB_EXPORT int llmb_attention_generic(const void* q, int q_stride, const void* 
                  "attention_generic: %d heads are no multiple of %d kv heads", n_heads, n_kv_heads);
     LLMB_REQUIRE(n_heads <= 65535 && ring_pages > 0 && window >= 0, "attention_generic: bad sizes");
     dim3 grid(n_tokens, n_heads);
-    if (dtype == LLMB_DTYPE_F32)
-        attention_generic_kernel<float><<<grid, WARPS * 32, 0, stream>>>(
-            (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, block_table,
-            table_stride, ring_pages, tok_pos, tok_seq, (float*)out, out_stride, n_heads,
-            n_kv_heads, head_dim, scale, window);
-    else if (dtype == LLMB_DTYPE_BF16)
-        attention_generic_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
-            (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, tok_pos, tok_seq,
-            (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window);
-    else
+    bool few = (long long)n_tokens * n_heads < 4096;       // the result is the same either way
+#define LLMB_GENERIC(T, AHEAD)                                                                          \
+    attention_generic_kernel<T, AHEAD><<<grid, WARPS * 32, 0, stream>>>(                                 \
+        (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride,         \
+        ring_pages, tok_pos, tok_seq, (T*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window)
+    if (dtype == LLMB_DTYPE_F32) {
+        if (few) LLMB_GENERIC(float, 4); else LLMB_GENERIC(float, 1);
+    } else if (dtype == LLMB_DTYPE_BF16) {
+        if (few) LLMB_GENERIC(__nv_bfloat16, 4); else LLMB_GENERIC(__nv_bfloat16, 1);
+    } else {
         return fail(LLMB_ERR_ARGUMENT, "attention_generic: unknown dtype %d", dtype);
+    }
+#undef LLMB_GENERIC
     return check_launch("attention_generic");
 }
