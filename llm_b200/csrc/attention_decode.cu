@@ -71,6 +71,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // this block's slice are fetched before griddep_wait(), except the page that holds the
     // newest position.
     griddep_launch();
+    LLMB_STAMP(0, 0);                               // the block has started
     // blocks start in the order of blockIdx; seq_order (optional) lists the sequences by falling
     // length, so that the longest ones start first and the short ones fill the end of the step
     int split = blockIdx.x, n_splits = gridDim.x, kv_head = blockIdx.y;
@@ -119,6 +120,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         cp_async_commit();
     }
     griddep_wait();
+    LLMB_STAMP(1, 0);                               // the kernel before this one has completed
     if (late_unit >= 0) {
         load_page(page_begin + late_unit * UNIT + late_place, late_unit, late_place);
         cp_async_commit();
@@ -148,6 +150,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (late_unit >= 0 && i == n_units - 1) cp_async_wait<0>();
         else cp_async_wait<STAGES - 2>();
         __syncthreads();                            // unit i landed; everyone is done with unit i - 1
+        if (i == 0) LLMB_STAMP(2, 0);               // the first pages have landed
         if (i + STAGES - 1 < n_units) load_unit(i + STAGES - 1, (i + STAGES - 1) % STAGES, false);
         cp_async_commit();
 
@@ -205,6 +208,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     cp_async_wait<0>();
     __syncthreads();                                 // the stage buffers are free: reuse them
+    LLMB_STAMP(3, 0);                                // the slice's keys are done
 
     // merge the four warps: [WARPS][8 heads][D] weighted values, [WARPS][8] max and sum
     run_sum += __shfl_xor_sync(0xffffffffu, run_sum, 1);
@@ -240,6 +244,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         part_acc[slot * D + d] = value;
         if (d == 0) { part_stats[slot * 2] = m; part_stats[slot * 2 + 1] = sum; }
     }
+    LLMB_STAMP(4, 0);                                // the partial result is written
 }
 
 template <int D>
@@ -294,6 +299,10 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                  (const float*)part_acc, (const float*)part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_splits);
     return check_launch("attention_decode_combine");
 }
+
+// The stamps of the last launches in a build with -DLLMB_TRACE (see common.cuh): rows are linear block
+// ids (x fastest), only the first LLMB_TRACE_BLOCKS of them; 1 in a build without.
+LLMB_EXPORT int llmb_attention_decode_trace(unsigned long long* out, int clear) { return llmb_read_trace(out, clear); }
 
 // Floats of scratch for a call: partial values and (max, sum) per (sequence, head, split).
 LLMB_EXPORT long long llmb_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim,

@@ -121,7 +121,9 @@ inline cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size
 
 // Built with -DLLMB_TRACE (LLMB_NVCC_FLAGS=-DLLMB_TRACE), a kernel stamps the GPU's global timer
 // (nanoseconds) at the phases it names with LLMB_STAMP(slot, thread): thread `thread` of each of the
-// first LLMB_TRACE_BLOCKS blocks writes slot `slot` of its block's row. Otherwise the macro is empty.
+// first LLMB_TRACE_BLOCKS blocks (numbered x fastest) writes slot `slot` of its block's row. Otherwise the
+// macro is empty. llmb_read_trace copies the rows to the host (and zeroes them if `clear`): 0, or 1 in a
+// build without stamps, 2 on a CUDA error. Each library has a buffer of its own.
 #define LLMB_TRACE_BLOCKS 296
 #define LLMB_TRACE_SLOTS 12
 #ifdef LLMB_TRACE
@@ -133,11 +135,23 @@ __device__ __forceinline__ unsigned long long llmb_global_timer() {
 }
 #define LLMB_STAMP(slot, thread)                                                          \
     do {                                                                                  \
-        if (threadIdx.x == (thread) && blockIdx.x < LLMB_TRACE_BLOCKS)                    \
-            llmb_trace_buffer[blockIdx.x * LLMB_TRACE_SLOTS + (slot)] = llmb_global_timer(); \
+        unsigned block_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;  \
+        if (threadIdx.x == (thread) && block_ < LLMB_TRACE_BLOCKS)                        \
+            llmb_trace_buffer[block_ * LLMB_TRACE_SLOTS + (slot)] = llmb_global_timer();  \
     } while (0)
+inline int llmb_read_trace(unsigned long long* out, int clear) {
+    size_t bytes = sizeof(unsigned long long) * LLMB_TRACE_BLOCKS * LLMB_TRACE_SLOTS;
+    if (cudaMemcpyFromSymbol(out, llmb_trace_buffer, bytes) != cudaSuccess) return 2;
+    if (clear) {
+        void* address = nullptr;
+        if (cudaGetSymbolAddress(&address, llmb_trace_buffer) != cudaSuccess || cudaMemset(address, 0, bytes) != cudaSuccess)
+            return 2;
+    }
+    return 0;
+}
 #else
 #define LLMB_STAMP(slot, thread) do { } while (0)
+inline int llmb_read_trace(unsigned long long*, int) { return 1; }
 #endif
 
 #define LLMB_EXPORT extern "C" __attribute__((visibility("default")))

@@ -1009,22 +1009,7 @@ Plan make_plan(int M, int N, int K) {
 // wait that ran out (1 producer, 2 mma, 3 epilogue). Call after a synchronisation.
 // The stamps of the last launches (a build with -DLLMB_TRACE): LLMB_TRACE_BLOCKS rows of
 // LLMB_TRACE_SLOTS global-timer values, 0 where nothing was stamped. Returns 1 in a build without.
-LLMB_EXPORT int llmb_gemm_tc_trace(unsigned long long* out, int clear) {
-#ifdef LLMB_TRACE
-    size_t bytes = sizeof(unsigned long long) * LLMB_TRACE_BLOCKS * LLMB_TRACE_SLOTS;
-    if (cudaMemcpyFromSymbol(out, llmb_trace_buffer, bytes) != cudaSuccess) return 2;
-    if (clear) {
-        void* address = nullptr;
-        if (cudaGetSymbolAddress(&address, llmb_trace_buffer) != cudaSuccess || cudaMemset(address, 0, bytes) != cudaSuccess)
-            return 2;
-    }
-    return 0;
-#else
-    (void)out;
-    (void)clear;
-    return 1;
-#endif
-}
+LLMB_EXPORT int llmb_gemm_tc_trace(unsigned long long* out, int clear) { return llmb_read_trace(out, clear); }
 
 LLMB_EXPORT int llmb_gemm_tc_status() {
     int* s = status_word();

@@ -406,14 +406,7 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
 }
 
 // The stamps of the last sampling launch in a build with -DLLMB_TRACE (see common.cuh); 1 otherwise.
-LLMB_EXPORT int llmb_sampling_trace(unsigned long long* out) {
-#ifdef LLMB_TRACE
-    return cudaMemcpyFromSymbol(out, llmb_trace_buffer, sizeof(unsigned long long) * LLMB_TRACE_BLOCKS * LLMB_TRACE_SLOTS) == cudaSuccess ? 0 : 2;
-#else
-    (void)out;
-    return 1;
-#endif
-}
+LLMB_EXPORT int llmb_sampling_trace(unsigned long long* out, int clear) { return llmb_read_trace(out, clear); }
 
 LLMB_EXPORT int llmb_sample_rows(float* logits, int stride, int n_rows, int vocab,
                                  const float* params, const int* iparams, int* recent,

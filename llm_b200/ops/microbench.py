@@ -13,8 +13,8 @@ HBM. `--once` runs a single plain launch after warm-up instead (for a profiler).
 Default sizes are those of a Llama-3.1-8B layer. The per-kernel table that
 MythEclipse/llm prints with LLM_PROFILE=1 (apps/engine/src/cuda/mod.rs:1917-1972)
 is the precedent; this tool isolates one kernel instead of wrapping every launch.
-`--timeline` (tcgen05 product, a build with -DLLMB_TRACE) prints when the blocks of the
-last launch passed the phases the kernel stamps with the GPU's global timer.
+`--timeline` (tcgen05 product and decode attention, a build with -DLLMB_TRACE) prints when
+the blocks of the last launch passed the phases the kernel stamps with the GPU's global timer.
 """
 from __future__ import annotations
 
@@ -66,35 +66,41 @@ def run(fn, args, work_bytes=0.0, work_flops=0.0, label=""):
     print(line)
 
 
-PHASES = ["block started", "set-up done", "predecessor complete", "first tiles landed", "last product issued",
-          "partial written and fenced", "counter answered", "summed and stored (last arriver)"]
+PHASES = {
+    "gemm_tc": ["block started", "set-up done", "predecessor complete", "first tiles landed",
+                "last product issued", "partial written and fenced", "counter answered",
+                "summed and stored (last arriver)"],
+    "attention_decode": ["block started", "predecessor complete", "first pages landed", "keys done",
+                         "partial written"],
+}
 
 
-def timeline(fn, label: str) -> int:
+def timeline(fn, label: str, library: str = "gemm_tc") -> int:
     """Back-to-back launches of fn, then the global-timer stamps of the last one, in microseconds
     after its first block started: earliest, median and latest block for every phase."""
     import ctypes
     from .build import load_library
-    lib = load_library("gemm_tc")
+    lib = load_library(library)
+    read = getattr(lib, f"llmb_{library}_trace")
     rows, slots = 296, 12
     stamps = (ctypes.c_ulonglong * (rows * slots))()
     for _ in range(20):
         fn()
     torch.cuda.synchronize()
-    if lib.llmb_gemm_tc_trace(stamps, 1) != 0:
+    if read(stamps, 1) != 0:
         print("this build has no stamps: set LLMB_NVCC_FLAGS=-DLLMB_TRACE", file=sys.stderr)
         return 1
     for _ in range(3):                       # the chain that is measured: the last of three launches
         fn()
     torch.cuda.synchronize()
-    lib.llmb_gemm_tc_trace(stamps, 0)
+    read(stamps, 0)
     table = torch.tensor(list(stamps), dtype=torch.float64).view(rows, slots)
     table = table[table[:, 0] > 0]
     # every block of every launch overwrites its row: what is left belongs to the last launch,
     # except phases that only some blocks reach (they may be older): those are cut at the start
     start = table[:, 0].min()
     print(f"{label}: {table.shape[0]} blocks; microseconds after the first block started")
-    for slot, name in enumerate(PHASES):
+    for slot, name in enumerate(PHASES[library]):
         column = table[:, slot]
         column = column[column >= start]
         if column.numel():
@@ -121,7 +127,7 @@ def main(argv=None) -> int:
     p.add_argument("--residual", action="store_true", help="linear: add into a 32-bit residual")
     p.add_argument("--reps", type=int, default=20)
     p.add_argument("--once", action="store_true")
-    p.add_argument("--timeline", action="store_true", help="linear: phases of the last launch's blocks")
+    p.add_argument("--timeline", action="store_true", help="linear, attention_decode: phases of the last launch's blocks")
     args = p.parse_args(argv)
     torch.manual_seed(0)
     bf16 = torch.bfloat16
@@ -166,6 +172,9 @@ def main(argv=None) -> int:
             seq = torch.arange(batch, dtype=torch.int32, device=DEV)
             fn = lambda: attention(qkv, kc, vc, table, pages_per, pos, seq, hq, hkv, d, d ** -0.5, 0,
                                    decode=True, seq_lens=lens, max_len=ctx)
+            if args.timeline:
+                return timeline(fn, f"attention_decode batch={batch} context={ctx} heads={hq}/{hkv} D={d}",
+                                "attention_decode")
             run(fn, args, batch * ctx * hkv * d * 2 * 2, 0.0,
                 f"attention_decode batch={batch} context={ctx} heads={hq}/{hkv} D={d}")
         else:
