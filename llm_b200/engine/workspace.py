@@ -112,11 +112,13 @@ class Workspace:
         self.plans: dict = {}
         self.arena = None
         self._retired: list = []
+        self._views: dict = {}                              # n_tokens -> Views of the current arena
 
     def plan_for(self, n_tokens: int) -> Plan:
         if n_tokens not in self.plans:
             if len(self.plans) > 64:
                 self.plans.clear()
+                self._views.clear()
             self.plans[n_tokens] = plan(self.requests_for_tokens(n_tokens))
         return self.plans[n_tokens]
 
@@ -126,25 +128,40 @@ class Workspace:
             if self.arena is not None:
                 self._retired.append(self.arena)
             self.arena = torch.empty(max(p.total, 1), dtype=torch.uint8, device=self.device)
-        return Views(p, self.arena)
+            self._views.clear()
+        views = self._views.get(n_tokens)
+        if views is None:
+            views = self._views[n_tokens] = Views(p, self.arena)
+        views.prefix = ""
+        return views
 
     def bytes(self) -> int:
         return 0 if self.arena is None else self.arena.numel()
 
 
 class Views:
-    """Named tensors inside the arena for one step."""
+    """Named tensors inside the arena for the steps of one token count (made once, then reused:
+    every step of that size gets the same addresses)."""
 
     def __init__(self, plan_: Plan, arena: torch.Tensor):
         self.plan = plan_
         self.arena = arena
         self.prefix = ""
+        self._tensors: dict = {}
 
     def get(self, name: str):
         """The planned buffer `name` (of the current layer prefix), or None if no part declared it."""
-        placement = self.plan.placements.get(self.prefix + name)
+        full = self.prefix + name
+        try:
+            return self._tensors[full]
+        except KeyError:
+            pass
+        placement = self.plan.placements.get(full)
         if placement is None:
-            return None
-        r = placement.request
-        flat = self.arena[placement.offset:placement.offset + r.nbytes]
-        return flat.view(r.dtype).view(r.shape)
+            tensor = None
+        else:
+            r = placement.request
+            flat = self.arena[placement.offset:placement.offset + r.nbytes]
+            tensor = flat.view(r.dtype).view(r.shape)
+        self._tensors[full] = tensor
+        return tensor

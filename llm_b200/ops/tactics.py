@@ -41,17 +41,26 @@ def rows(family: str) -> list:
     return out
 
 
+_chosen: dict = {}       # arguments of a choice -> the variant's name, until a variant is switched
+
+
 def disable(name: str) -> None:
     """Take a variant out of the choice (tests use it to reach a fallback)."""
     native.lib().llmh_tactics_set_disabled(name.encode(), 1)
+    _chosen.clear()
 
 
 def enable(name: str) -> None:
     native.lib().llmh_tactics_set_disabled(name.encode(), 0)
+    _chosen.clear()
 
 
 def is_disabled(name: str) -> bool:
-    return bool(native.lib().llmh_tactics_is_disabled(name.encode()))
+    key = ("disabled", name)
+    answer = _chosen.get(key)
+    if answer is None:
+        answer = _chosen[key] = bool(native.lib().llmh_tactics_is_disabled(name.encode()))
+    return answer
 
 
 def _choose(family: str, m=0, n=0, k=0, lda=0, decode=False, n_heads=1, n_kv_heads=1, head_dim=0,
@@ -65,14 +74,25 @@ def _choose(family: str, m=0, n=0, k=0, lda=0, decode=False, n_heads=1, n_kv_hea
 
 
 def choose_linear(m, n, k, in_dtype, out_dtype, lda, aligned=True) -> str:
-    return _choose("linear", m=m, n=n, k=k, in_dtype=in_dtype, out_dtype=out_dtype, lda=lda,
-                   aligned=aligned)[0]
+    key = ("linear", m, n, k, in_dtype, out_dtype, lda, aligned)
+    name = _chosen.get(key)
+    if name is None:
+        if len(_chosen) > 8192:
+            _chosen.clear()
+        name = _chosen[key] = _choose("linear", m=m, n=n, k=k, in_dtype=in_dtype, out_dtype=out_dtype,
+                                      lda=lda, aligned=aligned)[0]
+    return name
 
 
 def choose_attention(decode, dtype, n_heads, n_kv_heads, head_dim, window, packed=False,
                      aligned=True) -> str:
-    return _choose("attention", decode=decode, dtype=dtype, n_heads=n_heads, n_kv_heads=n_kv_heads,
-                   head_dim=head_dim, window=window, packed=packed, aligned=aligned)[0]
+    key = ("attention", decode, dtype, n_heads, n_kv_heads, head_dim, window, packed, aligned)
+    name = _chosen.get(key)
+    if name is None:
+        name = _chosen[key] = _choose("attention", decode=decode, dtype=dtype, n_heads=n_heads,
+                                      n_kv_heads=n_kv_heads, head_dim=head_dim, window=window,
+                                      packed=packed, aligned=aligned)[0]
+    return name
 
 
 def explain(family: str, **shape) -> str:
