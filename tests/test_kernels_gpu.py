@@ -117,7 +117,8 @@ def _check_decode_product(m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(65, 256, 64), (128, 128, 128), (129, 300, 200), (200, 1000, 520),
                                    (513, 6144, 4096), (2048, 4096, 1024), (70, 72, 72),
-                                   (300, 4104, 2048)])
+                                   (300, 4104, 2048), (256, 4096, 4096), (1000, 2304, 1536),
+                                   (140, 19200, 128), (2500, 8192, 192)])
 def test_linear_tensor_core_kernel(m, n, k):
     """tcgen05 product for more than 64 tokens: tile edges in M, N and K. Shapes with few output
     tiles run with the weights on the 128-row side, several token tiles and split K (513 x 6144,
@@ -148,7 +149,7 @@ def test_linear_tensor_core_kernel(m, n, k):
 
 @pytest.mark.parametrize("m,f,k", [(1, 64, 64), (8, 14336, 4096), (5, 208, 72), (64, 320, 128),
                                    (70, 320, 128), (300, 1024, 520), (2048, 1024, 256),
-                                   (8, 320, 1024), (40, 320, 1024)])
+                                   (8, 320, 1024), (40, 320, 1024), (512, 2048, 2048)])
 def test_linear_with_gated_epilogue(m, f, k):
     """silu(gate) * up in the epilogue of the tensor-core product, both orientations,
     against the product followed by the plain activation. The last two shapes split K: the
