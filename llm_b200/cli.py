@@ -43,6 +43,9 @@ def _int_list(text, flag):
 
 def main(argv=None) -> int:
     args = list(sys.argv[1:] if argv is None else argv)
+    if not args or args[0] in ("-h", "--help", "help"):
+        print(__doc__.strip())
+        return 0 if args else 2
     if args and args[0] == "bench":
         return bench(args[1:])
     if args and args[0] == "random":
