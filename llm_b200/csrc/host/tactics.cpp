@@ -56,6 +56,12 @@ std::string tc_guard(const Shape& s) {
     return "";
 }
 
+std::string generic_guard(const Shape& s) {
+    if (s.head_dim > LLMB_MAX_HEAD_DIM)
+        return "head_dim " + std::to_string(s.head_dim) + " exceeds " + std::to_string(LLMB_MAX_HEAD_DIM);
+    return "";
+}
+
 bool mma_head_dim(int d) { return d == 32 || d == 64 || d == 96 || d == 128; }
 
 std::string decode_guard(const Shape& s) {
@@ -110,7 +116,7 @@ const std::vector<Row>& table(int family) {
          "flash attention over the paged cache for steps with several new tokens a sequence: 64-query tiles, "
          "mma.sync, online softmax, heaviest tile first; head sizes 32, 64, 96, 128. Measured: 170 us at 2,048 "
          "tokens with 32/8 heads of 128, 90 us with heads of 64"},
-        {"attention_generic", 0, always,
+        {"attention_generic", 0, generic_guard,
          "one block per (token, head), 32-bit arithmetic, any head size up to 256, any group, window and ring; "
          "the only variant of the 32-bit path"},
     };

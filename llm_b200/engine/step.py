@@ -92,6 +92,9 @@ class Engine:
         self.step_tokens = step_tokens or self.max_seq_len
         self.pass_tokens = max(int(pass_tokens), 1)
         ops.ensure_built(model.libraries())
+        # every product and attention shape of this model must have a kernel: a size that none
+        # accepts (a head size above the kernels' limit) is refused here, not in the first step
+        self.kernel_plan = model.plan_identity()
         model.prepare(self.max_seq_len)
         kv, states = model.cache_requests()
         self.cache = PagedCache(kv, states, max_tokens, self.max_seq_len, self.max_slots,

@@ -281,3 +281,18 @@ def test_stop_tokens_and_context_end_sequences(folders, plain):
     assert results[0].tokens == want and results[0].stop_reason == reason == "context_full"
     llm.engine.cache.check()
     assert llm.engine.cache.slots.n_held == 0
+
+
+def test_an_engine_refuses_a_model_no_kernel_serves(tmp_path):
+    """A head size above the kernels' limit is refused when the engine is built, by name."""
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine import Engine, load_model
+    from llm_b200.errors import LlmError
+    from llm_b200.weights import write_random_model
+    raw = dict(CONFIGS["A"][0])
+    raw["head_dim"] = 272
+    folder = tmp_path / "wide_heads"
+    write_random_model(folder, config_from_dict(raw), 0, torch.bfloat16)
+    for dtype in DTYPES:
+        with pytest.raises(LlmError, match="head_dim 272 exceeds 256"):
+            Engine(load_model(folder, dtype, DEV), max_tokens=256)

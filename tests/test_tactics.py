@@ -66,3 +66,19 @@ def test_refusals_name_the_assumption_that_fails():
     assert text.startswith("attention: attention_generic") and "no window" in text
     text = tactics.explain("linear", m=2048, n=4096, k=4100, in_dtype=BF16, out_dtype=BF16, lda=4100)
     assert text.startswith("linear: gemm_simt") and "multiple of 8" in text and "exceed 64" in text
+
+
+def test_a_head_size_no_kernel_takes_is_refused_by_name():
+    """Above 256 no attention kernel runs: the choice fails and says so, for the model as a whole
+    too (an engine computes the model's kernel plan when it is built)."""
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine.model import DecoderModel
+    from llm_b200.errors import LlmError
+    with pytest.raises(LlmError, match="head_dim 272 exceeds 256"):
+        tactics.choose_attention(True, BF16, 4, 2, 272, 0)
+    raw = shape("llama-3.2-1b", 1)
+    raw["head_dim"] = 272
+    model = DecoderModel(config_from_dict(raw).model_spec())
+    with pytest.raises(LlmError, match="no kernel accepts the shape"):
+        model.plan_identity(BF16)
+    assert tactics.choose_attention(False, F32, 4, 2, 256, 0) == "attention_generic"
