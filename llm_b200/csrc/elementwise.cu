@@ -60,6 +60,17 @@ LLMB_EXPORT int llmb_embed(const int* tokens, const void* table, int table_dtype
 // (apps/engine/src/ops.rs:4-12, apps/engine/kernels/gpu.cu:266-316). One block per
 // row; the sum of squares is 32-bit and is reduced in a fixed order, so a row's
 // result does not depend on the batch it is in. `rows` (optional) gathers rows.
+// Four consecutive results in one store (the address is a multiple of the store's size).
+__device__ __forceinline__ void store_quad(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store_quad(__nv_bfloat16* p, float a, float b, float c, float d) {
+    uint2 packed;
+    *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(a, b);
+    *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = packed;
+}
+
 template <typename TOut, int PER_THREAD>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
@@ -118,10 +129,7 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
             if (q >= quads) continue;
             float4 g = reinterpret_cast<const float4*>(gain)[q];
             float4 v = held[i];
-            o[4 * q] = from_float<TOut>(v.x * scale * g.x);
-            o[4 * q + 1] = from_float<TOut>(v.y * scale * g.y);
-            o[4 * q + 2] = from_float<TOut>(v.z * scale * g.z);
-            o[4 * q + 3] = from_float<TOut>(v.w * scale * g.w);
+            store_quad(o + 4 * q, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
         }
     } else {
         for (int e = threadIdx.x; e < hidden; e += blockDim.x)
@@ -133,7 +141,7 @@ template <typename TOut>
 static void launch_rmsnorm(const float* x, const float* gain, const int* rows, TOut* out, int n_rows,
                            int hidden, float eps, cudaStream_t stream) {
     bool vector = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
-                  (reinterpret_cast<uintptr_t>(gain) & 15) == 0;
+                  (reinterpret_cast<uintptr_t>(gain) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     if (vector && hidden <= 1024) llmb::launch(rmsnorm_kernel<TOut, 1>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
     else if (vector && hidden <= 2048) llmb::launch(rmsnorm_kernel<TOut, 2>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
     else if (vector && hidden <= 4096) llmb::launch(rmsnorm_kernel<TOut, 4>, n_rows, 256, 0, stream, true, x, gain, rows, out, hidden, eps);
