@@ -27,6 +27,7 @@ from .workspace import Workspace
 
 
 GRAPH_AFTER_STEPS = 2      # plain steps of a shape before it is captured
+MAX_GRAPHS = 128           # captured shapes (batch size, bucket of pages) an engine keeps
 
 
 @dataclass
@@ -278,6 +279,8 @@ class Engine:
                 self._graph_pool = cuda_graph.pool()
             graph = (cuda_graph, meta, out, ops.launch_count() - before)
             ops.count_launches(-graph[3])            # capturing ran nothing
+            if len(self._graphs) >= MAX_GRAPHS:      # the shape captured longest ago goes
+                self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = graph
         cuda_graph, meta, out, kernels = graph
         meta.copy_(host[:total], non_blocking=True)

@@ -296,3 +296,29 @@ def test_an_engine_refuses_a_model_no_kernel_serves(tmp_path):
     for dtype in DTYPES:
         with pytest.raises(LlmError, match="head_dim 272 exceeds 256"):
             Engine(load_model(folder, dtype, DEV), max_tokens=256)
+
+
+def test_captured_steps_are_dropped_and_captured_again(folders, plain, monkeypatch):
+    """With room for two captured shapes only, a batch that shrinks from four sequences to one
+    (four shapes) and a second batch after it still decode right: a dropped shape runs plain again
+    until it is captured anew."""
+    from llm_b200.engine import Entry, step
+    monkeypatch.setattr(step, "MAX_GRAPHS", 2)
+    config, weights = plain["D"]
+    engine = engine_for(folders["D"], torch.bfloat16, max_slots=4)
+    for round_ in range(2):
+        seqs = [random_tokens(6 + 8 * (b + 1), config["vocab_size"], 50 + 10 * round_ + b) for b in range(4)]
+        expected = [plain_llama.forward(config, weights, s) for s in seqs]
+        slots = engine.acquire(4)
+        engine.step([Entry(s, q[:6], []) for s, q in zip(slots, seqs)])
+        live = [0, 1, 2, 3]
+        for k in range(6, max(len(s) for s in seqs)):
+            ended = [b for b in live if k >= len(seqs[b])]
+            engine.release([slots[b] for b in ended])
+            live = [b for b in live if b not in ended]
+            logits = engine.step([Entry(slots[b], [seqs[b][k]], [0]) for b in live])
+            for row, b in enumerate(live):
+                assert close(logits[row], expected[b][k], torch.bfloat16), (round_, b, k)
+        engine.release([slots[b] for b in live])
+        assert len(engine._graphs) <= 2
+    engine.cache.check()
