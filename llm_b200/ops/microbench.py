@@ -4,6 +4,7 @@
     python -m llm_b200.ops.microbench attention_decode --batch 8 --context 8192
     python -m llm_b200.ops.microbench attention_prefill --tokens 2048
     python -m llm_b200.ops.microbench rmsnorm --m 8 --k 4096
+    python -m llm_b200.ops.microbench sample --batch 8 --n 128256 [--temperature 0.7]
     LLMB_NVCC_FLAGS=-DLLMB_TRACE python -m llm_b200.ops.microbench linear --m 8 --n 6144 --k 4096 --timeline
 
 Each call is timed inside a CUDA graph of `--reps` back-to-back launches (so that
@@ -113,7 +114,7 @@ def timeline(fn, label: str, library: str = "gemm_tc") -> int:
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     p.add_argument("op", choices=["linear", "attention_decode", "attention_prefill", "rmsnorm",
-                                  "swiglu", "rope"])
+                                  "swiglu", "rope", "sample"])
     p.add_argument("--m", type=int, default=8, help="rows (tokens)")
     p.add_argument("--n", type=int, default=6144)
     p.add_argument("--k", type=int, default=4096)
@@ -125,6 +126,9 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=128)
     p.add_argument("--variant", default=None, help="force a kernel variant by disabling higher ranks")
     p.add_argument("--residual", action="store_true", help="linear: add into a 32-bit residual")
+    p.add_argument("--temperature", type=float, default=0.0,
+                   help="sample: 0 is greedy; above it the default chain (top-k 40, top-p 0.75, min-p 0.25, "
+                        "repeat penalty 1.1 over the last 64) runs")
     p.add_argument("--reps", type=int, default=20)
     p.add_argument("--once", action="store_true")
     p.add_argument("--timeline", action="store_true", help="linear, attention_decode: phases of the last launch's blocks")
@@ -187,6 +191,18 @@ def main(argv=None) -> int:
             args.reps = min(args.reps, 5)
             run(fn, args, 0.0, 2.0 * 2.0 * ctx * ctx / 2 * d * hq,
                 f"attention_prefill tokens={ctx} heads={hq}/{hkv} D={d} (causal flops)")
+    elif args.op == "sample":
+        from ..sampling import BatchSampler, SamplingParams
+        vocab, rows = args.n, list(range(args.batch))
+        sampler = BatchSampler([SamplingParams(temperature=args.temperature)] * args.batch, vocab, DEV)
+        base = torch.randn(args.batch, vocab, device=DEV)
+        logits = base.clone()
+
+        def fn():
+            logits.copy_(base)                      # the penalty changes logits in place
+            sampler.sample(logits, rows)
+        run(fn, args, 0.0, 0.0, f"sample (with a copy of the logits) rows={args.batch} vocab={vocab} "
+                                f"temperature={args.temperature}")
     elif args.op == "rmsnorm":
         x = torch.randn(args.m, args.k, device=DEV)
         g = torch.ones(args.k, device=DEV)
