@@ -1,7 +1,6 @@
 """Reading typed values out of a config.json dictionary."""
 from __future__ import annotations
 
-import json
 from pathlib import Path
 
 from ..errors import FormatError, MissingKey

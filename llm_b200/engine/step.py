@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import os
 from array import array
-from ctypes import byref, c_int, c_longlong, c_void_p
+from ctypes import byref, c_int, c_longlong
 from dataclasses import dataclass
 from itertools import chain
 

@@ -307,8 +307,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
 
 # ----------------------------------------------------------------------------- attention
 
-_attention_scratch: dict = {}
-_retired: list = []      # outgrown scratch buffers, kept alive for CUDA graphs that hold their address
+_attention_scratch: dict = {}      # outgrown buffers join `_retired` above
 
 
 def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:

@@ -6,7 +6,6 @@ import torch
 
 from .. import ops
 from ..errors import KernelError
-from .params import SamplingParams
 
 MASK64 = (1 << 64) - 1
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_llama
-from tiny import CONFIGS, make_folder, random_tokens
+from tiny import make_folder, random_tokens
 
 from llm_b200.engine import Engine, Entry, load_model
 

@@ -2,7 +2,7 @@
 the placement of scratch buffers, and the JSON reader behind the safetensors reader."""
 import json
 import struct
-from ctypes import byref, c_int, c_longlong
+from ctypes import byref, c_longlong
 
 import pytest
 import torch

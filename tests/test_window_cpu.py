@@ -6,7 +6,6 @@ result equals the plain implementation with the same windows. Host logic only
 test_toy_parts_gpu.py."""
 from dataclasses import dataclass
 
-import pytest
 import torch
 
 import plain_llama as P

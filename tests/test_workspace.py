@@ -6,7 +6,7 @@ import random
 import pytest
 import torch
 
-from tiny import TINY_B, make_folder
+from tiny import make_folder
 
 from llm_b200.engine.workspace import ALIGNMENT, BufferRequest, Workspace, plan
 
