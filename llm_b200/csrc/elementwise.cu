@@ -12,9 +12,10 @@ LLMB_DEFINE_LAST_ERROR(llmb_elementwise)
 // x[t, :] = table[token[t], :], widened to 32-bit (the residual stream).
 // Formula: apps/engine/kernels/gpu.cu:1752-1766 of MythEclipse/llm (one thread per
 // (token, column)); here one block per token, columns strided over the threads.
+// `scale` multiplies every value (1 for Llama; an architecture's embedding scale otherwise).
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ x, int hidden, int vocab, int vector) {
+                             float* __restrict__ x, int hidden, int vocab, int vector, float scale) {
     int t = blockIdx.x;
     int token = tokens[t];
     griddep_launch();
@@ -31,25 +32,25 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
             float4* dst = reinterpret_cast<float4*>(out + (size_t)v * PER);
 #pragma unroll
             for (int q = 0; q < PER / 4; ++q)
-                dst[q] = make_float4(to_float(e[4 * q]), to_float(e[4 * q + 1]), to_float(e[4 * q + 2]),
-                                     to_float(e[4 * q + 3]));
+                dst[q] = make_float4(to_float(e[4 * q]) * scale, to_float(e[4 * q + 1]) * scale,
+                                     to_float(e[4 * q + 2]) * scale, to_float(e[4 * q + 3]) * scale);
         }
         return;
     }
-    for (int e = threadIdx.x; e < hidden; e += blockDim.x) out[e] = to_float(row[e]);
+    for (int e = threadIdx.x; e < hidden; e += blockDim.x) out[e] = to_float(row[e]) * scale;
 }
 
 LLMB_EXPORT int llmb_embed(const int* tokens, const void* table, int table_dtype, float* x,
-                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+                           int n_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
     int aligned = (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     if (table_dtype == LLMB_DTYPE_F32)
         embed_kernel<float><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, x, hidden, vocab,
-                                                         aligned && hidden % 4 == 0);
+                                                         aligned && hidden % 4 == 0, scale);
     else if (table_dtype == LLMB_DTYPE_BF16)
         embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, hidden,
-                                                                 vocab, aligned && hidden % 8 == 0);
+                                                                 vocab, aligned && hidden % 8 == 0, scale);
     else
         return fail(LLMB_ERR_ARGUMENT, "embed: unknown dtype %d", table_dtype);
     return check_launch("embed");
@@ -166,24 +167,27 @@ LLMB_EXPORT int llmb_rmsnorm(const float* x, const float* gain, const int* rows,
 // ----------------------------------------------------------------------------- rotary + cache write
 // One launch per layer: rotate the queries in place, rotate the keys and store
 // them into the paged cache, copy the values into the cache (the job of
-// rope_append, apps/engine/kernels/gpu.cu:525-581). Angles come from a 32-bit
-// table [max_positions, head_dim] (cos in the first half of a row, sin in the
-// second) built once on the host; `interleaved` chooses the pairs (2p, 2p+1) of
-// MythEclipse/llm (apps/engine/src/ops.rs:152-165), otherwise (p, p + D/2).
-// With table == nullptr nothing is rotated (a mixer without position encoding).
-// A token's position and sequence come from device arrays; position p of
-// sequence b lives in page block_table[b][(p / 64) % ring_pages], row p % 64.
+// rope_append, apps/engine/kernels/gpu.cu:525-581). Only the first n_rot
+// elements of a head are rotated, the rest passes through (the rope dimension
+// count that MythEclipse/llm reads beside the head size, apps/engine/src/model.rs:93-95).
+// Angles come from a 32-bit table [max_positions, n_rot] (cos in the first half
+// of a row, sin in the second) built once on the host; `interleaved` chooses the
+// pairs (2p, 2p+1) of MythEclipse/llm (apps/engine/src/ops.rs:152-165), otherwise
+// (p, p + n_rot/2). With table == nullptr nothing is rotated (a mixer without
+// position encoding). A token's position and sequence come from device arrays;
+// position p of sequence b lives in page block_table[b][(p / 64) % ring_pages],
+// row p % 64.
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__ table,
                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                   const int* __restrict__ block_table, int table_stride,
                                   int ring_pages, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                                  int n_heads, int n_kv_heads, int head_dim, int interleaved,
+                                  int n_heads, int n_kv_heads, int head_dim, int n_rot, int interleaved,
                                   int write_cache) {
     int t = blockIdx.x;
     int head = blockIdx.y;               // [0, Hq): q; [Hq, Hq+Hkv): k; then v
     int pos = tok_pos[t];
-    int half = head_dim >> 1;
+    int half = n_rot >> 1;
     size_t row_stride = (size_t)(n_heads + 2 * n_kv_heads) * head_dim;
     T* src = qkv + (size_t)t * row_stride + (size_t)head * head_dim;
     bool is_q = head < n_heads;
@@ -198,7 +202,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__
         dst = (is_k ? k_cache : v_cache) + offset;
     }
     if (is_q || is_k) {
-        const float* angles = table ? table + (size_t)pos * head_dim : nullptr;
+        const float* angles = table ? table + (size_t)pos * n_rot : nullptr;
         T* out = is_q ? src : dst;
         for (int p = threadIdx.x; p < half; p += blockDim.x) {
             int i0 = interleaved ? 2 * p : p;
@@ -208,37 +212,43 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__
             out[i0] = from_float<T>(low * c - high * s);
             out[i1] = from_float<T>(low * s + high * c);
         }
+        if (is_k)                                                      // the part that is not rotated
+            for (int d = n_rot + threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
     } else {
         for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = src[d];
     }
 }
 
-// The same work for bfloat16 with 16-byte accesses: one block per token, every thread takes
-// items of 8 rotation pairs (two 16-byte pieces of a head) or 8 values of a v head.
+// The same work for bfloat16 with 16-byte accesses (head_dim and n_rot multiples of 16): one
+// block per token, every thread takes items of 8 rotation pairs (two 16-byte pieces of a head)
+// or 8 values that are only copied (a key's elements beyond n_rot, a v head).
 __global__ void __launch_bounds__(256)
 rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ table,
                       const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                       const int* __restrict__ block_table, int table_stride, int ring_pages,
                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                      int n_heads, int n_kv_heads, int head_dim, int interleaved, int write_cache) {
+                      int n_heads, int n_kv_heads, int head_dim, int n_rot, int interleaved, int write_cache) {
     griddep_launch();
     griddep_wait();
     int t = blockIdx.x;
     int pos = tok_pos[t];
-    int half = head_dim >> 1;
-    int items_rot = head_dim >> 4;                       // items of 8 pairs per rotated head
+    int half = n_rot >> 1;
+    int items_rot = n_rot >> 4;                          // items of 8 pairs per rotated head
+    int items_tail = (head_dim - n_rot) >> 3;            // items of 8 values of a key beyond n_rot
     int items_copy = head_dim >> 3;                      // items of 8 values per v head
     int n_rot_heads = n_heads + n_kv_heads;
-    int total = n_rot_heads * items_rot + (write_cache ? n_kv_heads * items_copy : 0);
+    int rot_total = n_rot_heads * items_rot;
+    int tail_total = write_cache ? n_kv_heads * items_tail : 0;
+    int total = rot_total + tail_total + (write_cache ? n_kv_heads * items_copy : 0);
     __nv_bfloat16* row = qkv + (size_t)t * (n_heads + 2 * n_kv_heads) * head_dim;
     size_t page_base = 0;
     if (write_cache) {
         int page = block_table[(size_t)tok_seq[t] * table_stride + ((pos / LLMB_PAGE) % ring_pages)];
         page_base = (size_t)page * n_kv_heads * LLMB_PAGE * head_dim + (size_t)(pos % LLMB_PAGE) * head_dim;
     }
-    const float* angles = table ? table + (size_t)pos * head_dim : nullptr;
+    const float* angles = table ? table + (size_t)pos * n_rot : nullptr;
     for (int item = threadIdx.x; item < total; item += blockDim.x) {
-        if (item < n_rot_heads * items_rot) {
+        if (item < rot_total) {
             int head = item / items_rot, piece = item - head * items_rot;
             bool is_q = head < n_heads;
             if (!is_q && !write_cache) continue;
@@ -280,8 +290,14 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__
             }
             *reinterpret_cast<uint4*>(dst + at_lo) = raw_lo;
             *reinterpret_cast<uint4*>(dst + at_hi) = raw_hi;
+        } else if (item < rot_total + tail_total) {
+            int rest = item - rot_total;
+            int kv_head = rest / items_tail, piece = rest - kv_head * items_tail;
+            const __nv_bfloat16* src = row + (size_t)(n_heads + kv_head) * head_dim + n_rot + piece * 8;
+            __nv_bfloat16* dst = k_cache + page_base + (size_t)kv_head * LLMB_PAGE * head_dim + n_rot + piece * 8;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
         } else {
-            int rest = item - n_rot_heads * items_rot;
+            int rest = item - rot_total - tail_total;
             int kv_head = rest / items_copy, piece = rest - kv_head * items_copy;
             const __nv_bfloat16* src = row + (size_t)(n_rot_heads + kv_head) * head_dim + piece * 8;
             __nv_bfloat16* dst = v_cache + page_base + (size_t)kv_head * LLMB_PAGE * head_dim + piece * 8;
@@ -294,19 +310,21 @@ LLMB_EXPORT int llmb_rope_cache_write(void* qkv, int dtype, const float* table,
                                       const int* tok_pos, const int* tok_seq,
                                       const int* block_table, int table_stride, int ring_pages,
                                       void* k_cache, void* v_cache, int n_tokens, int n_heads,
-                                      int n_kv_heads, int head_dim, int interleaved,
+                                      int n_kv_heads, int head_dim, int n_rot, int interleaved,
                                       int write_cache, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "rope: head_dim %d must be even", head_dim);
+    LLMB_REQUIRE(n_rot >= 0 && n_rot <= head_dim && n_rot % 2 == 0,
+                 "rope: the rotated part %d must be even and at most head_dim %d", n_rot, head_dim);
     LLMB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && ring_pages > 0, "rope: bad sizes");
     LLMB_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope: too many heads");
-    if (dtype == LLMB_DTYPE_BF16 && head_dim % 16 == 0 &&
+    if (dtype == LLMB_DTYPE_BF16 && head_dim % 16 == 0 && n_rot % 16 == 0 &&
         ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) |
           reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0) {
         llmb::launch(rope_cache_vec_kernel, n_tokens, 256, 0, stream, true,
                      (__nv_bfloat16*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
-                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim, interleaved,
-                     write_cache);
+                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim, n_rot,
+                     interleaved, write_cache);
         return check_launch("rope_cache_write");
     }
     dim3 grid(n_tokens, n_heads + 2 * n_kv_heads);
@@ -314,15 +332,30 @@ LLMB_EXPORT int llmb_rope_cache_write(void* qkv, int dtype, const float* table,
     if (dtype == LLMB_DTYPE_F32)
         rope_cache_kernel<float><<<grid, threads, 0, stream>>>(
             (float*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
-            (float*)k_cache, (float*)v_cache, n_heads, n_kv_heads, head_dim, interleaved, write_cache);
+            (float*)k_cache, (float*)v_cache, n_heads, n_kv_heads, head_dim, n_rot, interleaved, write_cache);
     else if (dtype == LLMB_DTYPE_BF16)
         rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
             (__nv_bfloat16*)qkv, table, tok_pos, tok_seq, block_table, table_stride, ring_pages,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, head_dim, n_rot,
             interleaved, write_cache);
     else
         return fail(LLMB_ERR_ARGUMENT, "rope: unknown dtype %d", dtype);
     return check_launch("rope_cache_write");
+}
+
+// ----------------------------------------------------------------------------- scaling in place
+// x *= scale over n 32-bit values (the logits of an architecture with a logit scale).
+__global__ void scale_kernel(float* __restrict__ x, long long n, float scale) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] *= scale;
+}
+
+LLMB_EXPORT int llmb_scale(float* x, long long n, float scale, cudaStream_t stream) {
+    if (n <= 0) return LLMB_OK;
+    int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    scale_kernel<<<blocks, 256, 0, stream>>>(x, n, scale);
+    return check_launch("scale");
 }
 
 // ----------------------------------------------------------------------------- gated activation

@@ -8,6 +8,7 @@ from ..errors import FormatError
 from ..parts import build_block, build_norm
 from ..parts.base import to_run_dtype
 from ..weights.loader import ParamSpec, load_checkpoint
+from .workspace import BufferRequest
 
 
 class DecoderModel:
@@ -115,22 +116,24 @@ class DecoderModel:
         return total
 
     def scratch_requests(self, n_tokens: int) -> list:
-        """Scratch of one layer pass for n_tokens tokens. Layers run one after the other, so
-        the plan of the layer with the largest needs serves all (blocks with equal specs
-        declare equal lists)."""
-        best, best_bytes = [], -1
+        """Scratch of one layer pass for n_tokens tokens. Layers run one after the other and
+        share one plan: per buffer name the largest request of any block (in bytes) with the
+        union of the lifetimes, so that blocks whose sizes differ all fit. A block asks for
+        its own shape (`ctx.scratch(name, shape, dtype)`) and gets a view of the front of the
+        planned buffer."""
+        merged, order = {}, []
         for block in self.blocks:
-            requests = block.scratch_requests(n_tokens, self.dtype)
-            size = sum(r.nbytes for r in requests)
-            if size > best_bytes:
-                best, best_bytes = requests, size
-        names = {r.name for r in best}
-        for block in self.blocks:                          # buffers other blocks add, at the end
             for r in block.scratch_requests(n_tokens, self.dtype):
-                if r.name not in names:
-                    best = best + [r]
-                    names.add(r.name)
-        return best
+                held = merged.get(r.name)
+                if held is None:
+                    merged[r.name] = r
+                    order.append(r.name)
+                    continue
+                larger = r if r.nbytes > held.nbytes else held
+                merged[r.name] = BufferRequest(r.name, larger.shape, larger.dtype,
+                                               min(r.first_use, held.first_use),
+                                               max(r.last_use, held.last_use))
+        return [merged[name] for name in order]
 
     # ------------------------------------------------------------------ cache needs
 
@@ -149,14 +152,17 @@ class DecoderModel:
     def forward(self, tokens, ctx, logit_rows):
         """tokens int32 [T] on the device; logit_rows int32 [R]: packed token
         indices whose logits are wanted. Returns float32 [R, vocab]."""
-        x = ops.embed(tokens, self.embedding)
+        x = ops.embed(tokens, self.embedding, scale=getattr(self.spec, "embedding_scale", 1.0))
         for entry, item in enumerate(self.spec.schedule):
             cache_entry = entry if item.cache_of is None else item.cache_of
             self.blocks[item.layer].forward(x, ctx, entry, cache_entry)
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=x.device)
         z = self.final_norm.forward(x, ctx.dtype, rows=logit_rows)
-        return ops.linear(z, self.head, out_dtype=torch.float32)
+        logits = ops.linear(z, self.head, out_dtype=torch.float32)
+        if getattr(self.spec, "logit_scale", 1.0) != 1.0:
+            ops.scale_(logits, self.spec.logit_scale)
+        return logits
 
 
 def declared_parameters(spec) -> dict:

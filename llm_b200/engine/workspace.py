@@ -149,11 +149,15 @@ class Views:
         self.prefix = ""
         self._tensors: dict = {}
 
-    def get(self, name: str):
-        """The planned buffer `name` (of the current layer prefix), or None if no part declared it."""
+    def get(self, name: str, shape=None, dtype=None):
+        """The planned buffer `name` (of the current layer prefix), or None if no part declared
+        it. With `shape` (and `dtype`) the front of the buffer is returned in that form: blocks
+        of one model may ask for different sizes under one name; the plan holds the largest.
+        A shape that does not fit into the planned buffer is refused."""
         full = self.prefix + name
+        key = full if shape is None else (full, tuple(shape), dtype)
         try:
-            return self._tensors[full]
+            return self._tensors[key]
         except KeyError:
             pass
         placement = self.plan.placements.get(full)
@@ -162,6 +166,14 @@ class Views:
         else:
             r = placement.request
             flat = self.arena[placement.offset:placement.offset + r.nbytes]
-            tensor = flat.view(r.dtype).view(r.shape)
-        self._tensors[full] = tensor
+            if shape is None:
+                tensor = flat.view(r.dtype).view(r.shape)
+            else:
+                want = BufferRequest(full, tuple(shape), dtype or r.dtype, r.first_use, r.last_use)
+                if want.nbytes > r.nbytes:
+                    raise ValueError(f"scratch buffer '{full}' was planned with {r.nbytes} bytes "
+                                     f"({r.shape}, {r.dtype}); {tuple(shape)} {want.dtype} needs "
+                                     f"{want.nbytes}")
+                tensor = flat[:want.nbytes].view(want.dtype).view(want.shape)
+        self._tensors[key] = tensor
         return tensor

@@ -62,6 +62,19 @@ def _require_cuda(*tensors):
             raise KernelError("llm_b200 kernels need tensors on a CUDA device; there is no CPU path")
 
 
+def _check_out(out, shape, dtype, what: str):
+    """Refuse a caller's `out` that the kernel would not fill as the caller thinks: the kernels
+    write rows of the result's own width one after the other, so a buffer of another shape,
+    dtype or layout would be overrun or garbled without a word."""
+    if out is None:
+        return
+    _require_cuda(out)
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype or not out.is_contiguous():
+        raise KernelError(f"{what}: out is {tuple(out.shape)} {out.dtype}"
+                          f"{'' if out.is_contiguous() else ' (not contiguous)'}, the result is "
+                          f"{tuple(shape)} {dtype}")
+
+
 _launches = 0
 
 
@@ -122,15 +135,25 @@ def _call(lib_name: str, fn_name: str, *args, kernels: int = 1):
 
 # ----------------------------------------------------------------------------- row-wise
 
-def embed(tokens, table, out=None):
-    """x[t, :] = table[tokens[t], :] as float32 [T, hidden]."""
+def embed(tokens, table, out=None, scale: float = 1.0):
+    """x[t, :] = table[tokens[t], :] * scale as float32 [T, hidden]."""
     _require_cuda(tokens, table)
     n, (vocab, hidden) = tokens.numel(), table.shape
+    _check_out(out, (n, hidden), torch.float32, "embed")
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _call("elementwise", "llmb_embed", _ptr(tokens), _ptr(table), _c_int(_code(table.dtype)),
-          _ptr(out), _c_int(n), _c_int(hidden), _c_int(vocab), _stream())
+          _ptr(out), _c_int(n), _c_int(hidden), _c_int(vocab), _c_float(scale), _stream())
     return out
+
+
+def scale_(x, scale: float):
+    """x *= scale in place (float32, contiguous)."""
+    _require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_: the tensor must be contiguous float32")
+    _call("elementwise", "llmb_scale", _ptr(x), ctypes.c_longlong(x.numel()), _c_float(scale), _stream())
+    return x
 
 
 def rmsnorm(x, gain, eps, out_dtype, rows=None, out=None):
@@ -138,6 +161,9 @@ def rmsnorm(x, gain, eps, out_dtype, rows=None, out=None):
     _require_cuda(x, gain, rows)
     hidden = x.shape[-1]
     n = rows.numel() if rows is not None else x.shape[0]
+    if x.dtype != torch.float32 or gain.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("rmsnorm: x and gain must be float32, x contiguous")
+    _check_out(out, (n, hidden), out_dtype, "rmsnorm")
     if out is None:
         out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
     _call("elementwise", "llmb_rmsnorm", _ptr(x), _ptr(gain), _ptr(rows), _ptr(out),
@@ -150,6 +176,9 @@ def swiglu(gate_up, out=None):
     _require_cuda(gate_up)
     n, two_f = gate_up.shape
     width = two_f // 2
+    if not gate_up.is_contiguous():
+        raise KernelError("swiglu: the input must be contiguous")
+    _check_out(out, (n, width), gate_up.dtype, "swiglu")
     if out is None:
         out = torch.empty((n, width), dtype=gate_up.dtype, device=gate_up.device)
     _call("elementwise", "llmb_swiglu", _ptr(gate_up), _ptr(out), _c_int(_code(gate_up.dtype)),
@@ -160,14 +189,23 @@ def swiglu(gate_up, out=None):
 def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages, k_cache, v_cache,
                      n_heads, n_kv_heads, head_dim, interleaved=False, write_cache=True):
     """Rotate q (in place) and k of the fused [T, (Hq + 2 Hkv) D] projection by the
-    angles of `rope_table` [positions, D] (None: no rotation) and store k and v
-    of every token into the paged cache [pages, Hkv, 64, D]."""
-    _require_cuda(qkv, tok_pos, tok_seq, block_table, k_cache, v_cache)
+    angles of `rope_table` [positions, n_rot] (None: no rotation; n_rot <= D: only the
+    first n_rot elements of a head are rotated) and store k and v of every token into the
+    paged cache [pages, Hkv, 64, D]."""
+    _require_cuda(qkv, rope_table, tok_pos, tok_seq, block_table, k_cache, v_cache)
     n = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim or not qkv.is_contiguous():
+        raise KernelError(f"rope_cache_write: qkv {tuple(qkv.shape)} is not contiguous "
+                          f"[T, ({n_heads} + 2 * {n_kv_heads}) * {head_dim}]")
+    n_rot = head_dim if rope_table is None else rope_table.shape[1]
+    if rope_table is not None and (rope_table.dtype != torch.float32 or not rope_table.is_contiguous()
+                                   or n_rot > head_dim or n_rot % 2):
+        raise KernelError(f"rope_cache_write: the table of angles must be contiguous float32 "
+                          f"[positions, n_rot] with an even n_rot <= {head_dim}")
     _call("elementwise", "llmb_rope_cache_write", _ptr(qkv), _c_int(_code(qkv.dtype)),
           _ptr(rope_table), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
           _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(k_cache), _ptr(v_cache),
-          _c_int(n), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim),
+          _c_int(n), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(n_rot),
           _c_int(1 if interleaved else 0), _c_int(1 if write_cache else 0), _stream())
 
 
@@ -259,6 +297,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
         if not glu_fusable(n, k, a.dtype) or bias is not None or residual is not None or a.stride(0) % 8:
             raise KernelError("linear: the gated epilogue needs bfloat16, 2 F rows with F % 16 == 0, "
                               "K % 8 == 0, no bias and no residual")
+        _check_out(out, (m, n // 2), a.dtype, "linear")
         result = out if out is not None else torch.empty((m, n // 2), dtype=a.dtype, device=a.device)
         partials, counters = _tc_scratch(a.device, m, n, k)
         _call("gemm_tc", "llmb_gemm_tc", _ptr(a), _c_int(a.stride(0)), _ptr(w), None, _ptr(result),
@@ -277,6 +316,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
             raise KernelError("linear: residual must be contiguous float32 [M, N]")
     else:
         target_dtype = out_dtype or a.dtype
+        _check_out(out, (m, n), target_dtype, "linear")
         result = out if out is not None else torch.empty((m, n), dtype=target_dtype, device=a.device)
     variant = tactics.choose_linear(m, n, k, a.dtype, target_dtype, a.stride(0),
                                     a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -350,6 +390,7 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     take one block of work per sequence then start the longest first."""
     _require_cuda(qkv, k_cache, v_cache, block_table, tok_pos, tok_seq)
     n = qkv.shape[0]
+    _check_out(out, (n, n_heads * head_dim), qkv.dtype, "attention")
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window,
@@ -435,6 +476,6 @@ def required_libraries() -> list:
             "attention_decode", "attention_prefill", "attention_prefill_tc", "sampling"]
 
 
-__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
+__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

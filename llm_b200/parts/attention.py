@@ -86,14 +86,16 @@ class AttentionMixer(Mixer):
         group, keys, values = ctx.cache.layer_view(cache_entry)
         table = ctx.block_tables[group]
         ring = ctx.cache.table_width(group)
-        qkv = ops.linear(h, self.w_qkv, self.b_qkv, out=ctx.scratch("qkv"))
+        n = h.shape[0]
+        qkv = ops.linear(h, self.w_qkv, self.b_qkv,
+                         out=ctx.scratch("qkv", (n, self.q_width + 2 * self.kv_width), h.dtype))
         ops.rope_cache_write(
             qkv, self.position.table if self.position is not None else None, ctx.tok_pos,
             ctx.tok_seq, table, ring, keys, values, s.n_heads, s.n_kv_heads, s.head_dim,
             interleaved=self.position.interleaved if self.position is not None else False,
             write_cache=(entry == cache_entry))
         mixed = ops.attention(qkv, keys, values, table, ring, ctx.tok_pos, ctx.tok_seq, s.n_heads,
-                              s.n_kv_heads, s.head_dim, s.scale, s.window, out=ctx.scratch("mixed"),
+                              s.n_kv_heads, s.head_dim, s.scale, s.window, out=ctx.scratch("mixed", (n, self.q_width), h.dtype),
                               decode=ctx.decode,
                               seq_lens=ctx.seq_lens, max_len=ctx.max_len,
                               cu_seqlens=ctx.cu_seqlens, max_new=max(ctx.new_counts),

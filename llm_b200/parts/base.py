@@ -45,9 +45,10 @@ class StepContext:
     seq_order: torch.Tensor = None # [B] the sequences by falling length (work lists start the longest first)
     extras: dict = field(default_factory=dict)
 
-    def scratch(self, name: str):
-        """The planned buffer `name` of the part that is running, or None."""
-        return self.workspace.get(name) if self.workspace is not None else None
+    def scratch(self, name: str, shape=None, dtype=None):
+        """The planned buffer `name` of the part that is running, or None. With `shape` the
+        front of the buffer in that form (blocks of different sizes share one plan)."""
+        return self.workspace.get(name, shape, dtype) if self.workspace is not None else None
 
 
 class Part:

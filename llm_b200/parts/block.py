@@ -66,13 +66,13 @@ class PreNormBlock(Block):
 
     def forward(self, x, ctx, entry, cache_entry):
         views = ctx.workspace
-        h = self.mixer_norm.forward(x, ctx.dtype, out=ctx.scratch("h_mixer"))
+        h = self.mixer_norm.forward(x, ctx.dtype, out=ctx.scratch("h_mixer", tuple(x.shape), ctx.dtype))
         if views is not None:
             views.prefix = "mixer."
         self.mixer.forward(h, ctx, entry, cache_entry, x)
         if views is not None:
             views.prefix = ""
-        h = self.ffn_norm.forward(x, ctx.dtype, out=ctx.scratch("h_ffn"))
+        h = self.ffn_norm.forward(x, ctx.dtype, out=ctx.scratch("h_ffn", tuple(x.shape), ctx.dtype))
         if views is not None:
             views.prefix = "ffn."
         self.feed_forward.forward(h, ctx, x)

@@ -63,11 +63,12 @@ class GatedMlp(FeedForward):
         return [BufferRequest("gate_up", (n_tokens, 2 * s.intermediate), dtype, 0, 1), act]
 
     def forward(self, h, ctx, residual):
+        n, width = h.shape[0], self.spec.intermediate
         if self.fused:
-            act = ops.linear(h, self.w_gate_up, glu=True, out=ctx.scratch("act"))
+            act = ops.linear(h, self.w_gate_up, glu=True, out=ctx.scratch("act", (n, width), h.dtype))
         else:
-            gate_up = ops.linear(h, self.w_gate_up, out=ctx.scratch("gate_up"))
-            act = ops.swiglu(gate_up, out=ctx.scratch("act"))
+            gate_up = ops.linear(h, self.w_gate_up, out=ctx.scratch("gate_up", (n, 2 * width), h.dtype))
+            act = ops.swiglu(gate_up, out=ctx.scratch("act", (n, width), h.dtype))
         ops.linear(act, self.w_down, residual=residual)
 
 

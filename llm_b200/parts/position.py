@@ -10,7 +10,7 @@ from .base import PositionEncoding, register_position
 
 
 def inverse_frequencies(head_dim: int, theta: float, scaling: dict | None) -> torch.Tensor:
-    """theta^(-2p/D) for pair p, in float64 (apps/engine/src/ops.rs:128-131 of
+    """theta^(-2p/D) for pair p (D: the rotated part of a head), in float64 (apps/engine/src/ops.rs:128-131 of
     MythEclipse/llm), then config.json's `rope_scaling` of type llama3: pairs
     whose wavelength exceeds original/low_freq_factor are slowed by `factor`,
     those below original/high_freq_factor are kept, and the band between is
@@ -35,16 +35,20 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: dict | None) -> to
 
 
 class Rope(PositionEncoding):
-    """Holds a float32 table [positions, head_dim] on the device: cos of
-    position * inv_freq[p] in columns [0, D/2), sin in [D/2, D). Angles are
-    computed in float64 and rounded once."""
+    """Holds a float32 table [positions, n] on the device, n = rotary_dim or head_dim: cos
+    of position * inv_freq[p] in columns [0, n/2), sin in [n/2, n). Angles are computed in
+    float64 and rounded once. With n < head_dim the elements of a head beyond n are not
+    rotated (the rope dimension count of apps/engine/src/model.rs:93-95 of MythEclipse/llm)."""
 
     def __init__(self, spec):
         if spec.pairing not in ("half", "interleaved"):
             raise Unsupported(f"rope pairing '{spec.pairing}'")
         self.spec = spec
         self.interleaved = spec.pairing == "interleaved"
-        self.inv_freq = inverse_frequencies(spec.head_dim, spec.theta, spec.scaling_dict)
+        self.rotary_dim = spec.head_dim if getattr(spec, "rotary_dim", None) is None else spec.rotary_dim
+        if self.rotary_dim % 2 or not 0 < self.rotary_dim <= spec.head_dim:
+            raise Unsupported(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {spec.head_dim}")
+        self.inv_freq = inverse_frequencies(self.rotary_dim, spec.theta, spec.scaling_dict)
         self.table = None
 
     def prepare(self, max_positions, device):

@@ -31,8 +31,9 @@ class PositionSpec:
     theta: float
     max_positions: int
     scaling: Optional[tuple] = None  # sorted (key, value) pairs of rope_scaling, or None
-    pairing: str = "half"            # 'half': (p, p + D/2); 'interleaved': (2p, 2p + 1)
+    pairing: str = "half"            # 'half': (p, p + n/2); 'interleaved': (2p, 2p + 1)
     kind: str = "rope"
+    rotary_dim: Optional[int] = None # n: how many leading elements of a head rotate (None: all)
 
     @property
     def scaling_dict(self):
@@ -100,6 +101,8 @@ class ModelSpec:
     final_norm: object
     head: Optional[str]              # tensor name of the [vocab, hidden] head; None: tied to the embedding
     stop_tokens: tuple = field(default_factory=tuple)
+    embedding_scale: float = 1.0     # multiplies the embedded tokens
+    logit_scale: float = 1.0         # multiplies the logits
 
 
 def names(**roles) -> tuple:

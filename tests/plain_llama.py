@@ -92,22 +92,24 @@ def rope_inverse_frequencies(head_dim, theta, scaling=None):
 def rope_rotate(x, positions, inv_freq, pairing="half"):
     """Rotate every head of x [n, heads, D] by angle position * inv_freq[p]
     (apps/engine/src/ops.rs:152-165). pairing 'interleaved' is the
-    project's (2p, 2p+1); 'half' pairs (p, p + D/2)."""
-    n, heads, dim = x.shape
+    project's (2p, 2p+1); 'half' pairs (p, p + n_rot/2). n_rot = 2 * len(inv_freq) may be
+    smaller than D: the elements beyond it pass through (the rope dimension count,
+    apps/engine/src/model.rs:93-95)."""
+    n_rot = 2 * len(inv_freq)
     angle = torch.as_tensor(positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
     cos = angle.cos().to(x.dtype)[:, None, :]
     sin = angle.sin().to(x.dtype)[:, None, :]
     if pairing == "interleaved":
-        low, high = x[..., 0::2], x[..., 1::2]
+        low, high = x[..., 0:n_rot:2], x[..., 1:n_rot:2]
     else:
-        low, high = x[..., : dim // 2], x[..., dim // 2:]
+        low, high = x[..., : n_rot // 2], x[..., n_rot // 2:n_rot]
     new_low = low * cos - high * sin
     new_high = low * sin + high * cos
-    out = torch.empty_like(x)
+    out = x.clone()
     if pairing == "interleaved":
-        out[..., 0::2], out[..., 1::2] = new_low, new_high
+        out[..., 0:n_rot:2], out[..., 1:n_rot:2] = new_low, new_high
     else:
-        out[..., : dim // 2], out[..., dim // 2:] = new_low, new_high
+        out[..., : n_rot // 2], out[..., n_rot // 2:n_rot] = new_low, new_high
     return out
 
 

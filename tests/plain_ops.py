@@ -14,8 +14,13 @@ import torch
 PAGE = 64
 
 
-def embed(tokens, table, out=None):
-    return table[tokens.long()].to(torch.float32)
+def embed(tokens, table, out=None, scale=1.0):
+    return table[tokens.long()].to(torch.float32) * scale
+
+
+def scale_(x, scale):
+    x *= scale
+    return x
 
 
 def rmsnorm(x, gain, eps, out_dtype, rows=None, out=None):
@@ -50,18 +55,20 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
 
 
 def _rotate(x, cos, sin, interleaved):
-    """x [n, heads, D] float32; cos, sin [n, D/2]."""
-    half = x.shape[-1] // 2
+    """x [n, heads, D] float32; cos, sin [n, n_rot/2]: the first n_rot elements of a head rotate,
+    the rest passes through."""
+    half = cos.shape[-1]
+    n_rot = 2 * half
     cos, sin = cos[:, None, :], sin[:, None, :]
-    out = torch.empty_like(x)
+    out = x.clone()
     if interleaved:
-        low, high = x[..., 0::2], x[..., 1::2]
-        out[..., 0::2] = low * cos - high * sin
-        out[..., 1::2] = low * sin + high * cos
+        low, high = x[..., 0:n_rot:2], x[..., 1:n_rot:2]
+        out[..., 0:n_rot:2] = low * cos - high * sin
+        out[..., 1:n_rot:2] = low * sin + high * cos
     else:
-        low, high = x[..., :half], x[..., half:]
+        low, high = x[..., :half], x[..., half:n_rot]
         out[..., :half] = low * cos - high * sin
-        out[..., half:] = low * sin + high * cos
+        out[..., half:n_rot] = low * sin + high * cos
     return out
 
 
@@ -76,7 +83,7 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
     k = qkv[:, qw:qw + kw].to(torch.float32).view(n, n_kv_heads, head_dim)
     v = qkv[:, qw + kw:].view(n, n_kv_heads, head_dim)
     if rope_table is not None:
-        half = head_dim // 2
+        half = rope_table.shape[1] // 2
         cos, sin = rope_table[pos, :half], rope_table[pos, half:]
         q = _rotate(q, cos, sin, interleaved)
         k = _rotate(k, cos, sin, interleaved)
@@ -227,7 +234,7 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 
 
 
-OPS = {"embed": embed, "rmsnorm": rmsnorm, "swiglu": swiglu, "linear": linear,
+OPS = {"embed": embed, "scale_": scale_, "rmsnorm": rmsnorm, "swiglu": swiglu, "linear": linear,
        "rope_cache_write": rope_cache_write, "attention": attention, "argmax_rows": argmax_rows,
        "sample_rows": sample_rows}
 
