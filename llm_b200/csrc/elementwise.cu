@@ -3,6 +3,7 @@
 // activation. Every kernel exists for 32-bit and for bfloat16 activations;
 // sums, angles and the residual stream are 32-bit in both.
 #include "common.cuh"
+#include "random_normal.h"
 
 using namespace llmb;
 
@@ -420,4 +421,28 @@ LLMB_EXPORT int llmb_swiglu(const void* gu, void* act, int dtype, int n_tokens, 
     else
         return fail(LLMB_ERR_ARGUMENT, "swiglu: unknown dtype %d", dtype);
     return check_launch("swiglu");
+}
+
+// ----------------------------------------------------------------------------- random weights
+// out[i] = mean + deviation * N(0, 1) keyed by (key, i): the formulas of random_normal.h, the same
+// bits as the host library's llmh_random_normal gives.
+template <typename T>
+__global__ void random_normal_kernel(T* __restrict__ out, long long n, unsigned long long key, float mean,
+                                     float deviation) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = from_float<T>(llmb_random::value(key, (uint64_t)i, mean, deviation));
+}
+
+LLMB_EXPORT int llmb_random_normal(void* out, int dtype, long long n, unsigned long long key, float mean,
+                                   float deviation, cudaStream_t stream) {
+    if (n <= 0) return LLMB_OK;
+    int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (dtype == LLMB_DTYPE_F32)
+        random_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, n, key, mean, deviation);
+    else if (dtype == LLMB_DTYPE_BF16)
+        random_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, n, key, mean, deviation);
+    else
+        return fail(LLMB_ERR_ARGUMENT, "random_normal: unknown dtype %d", dtype);
+    return check_launch("random_normal");
 }

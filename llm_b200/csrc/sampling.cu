@@ -147,7 +147,9 @@ __device__ unsigned block_exclusive_sum(unsigned value, unsigned* warp_totals) {
 // {top_k, repeat_last_n}. recent[row, 0..recent_cap) holds the row's generated
 // tokens as a ring: token number i (counted from 0) is at recent[row, i % cap],
 // recent_len[row] counts all of them. `logits` is modified in place (the penalty
-// on the recent tokens' entries). status[row] = 0, or 1 if the parameters were refused.
+// on the recent tokens' entries). status[row] is set to 1 when the row was refused (its parameters, or
+// more equal logits at the top-k cut than the kernel ranks) and token 0 stands in its place; the kernel
+// never clears it, so a refusal in any step stays visible until the host has read and cleared it.
 __global__ void __launch_bounds__(THREADS)
 sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
                    const float4* __restrict__ params, const int2* __restrict__ iparams,
@@ -184,7 +186,6 @@ sample_rows_kernel(float* __restrict__ logits, int stride, int vocab,
         }
     };
 
-    if (tid == 0) status[row_id] = 0;
     if (penalty != 1.0f && last_n > 0 && recent != nullptr) {
         // A token that occurs c times in the window is penalised c times, one after the other
         // (apps/engine/src/sampler.rs:115-127). One thread per window place; the first place of a

@@ -160,7 +160,9 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
 
     # ids travel device -> pinned host memory while the next step is already queued
     on_gpu = str(getattr(engine, "device", "cpu")).startswith("cuda")
-    staging = torch.empty(len(batch), dtype=torch.int32, pin_memory=on_gpu)
+    # (and behind them the sampler's refusal flags, read with every step's ids)
+    staging = torch.empty(2 * len(batch), dtype=torch.int32, pin_memory=on_gpu)
+    flags = staging[len(batch):]
     copied = torch.cuda.Event() if on_gpu else None
 
     try:
@@ -184,6 +186,8 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
                     break
             sampled = sampler.sample(logits, live)               # int32 on the device
             staging[:len(live)].copy_(sampled, non_blocking=True)
+            if not sampler.all_greedy:
+                flags.copy_(sampler.status, non_blocking=True)
             if copied is not None:
                 copied.record()
             # Who goes on is known before the ids are: everyone whose limits allow one more
@@ -199,6 +203,7 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
             if copied is not None:
                 copied.synchronize()                             # the ids, not the queued step
             tokens = staging[:len(live)].tolist()
+            sampler.check_status(flags)
             engine.check()
             now = time.perf_counter()
             if prefill_done is None:
@@ -217,7 +222,6 @@ def _run_batch(engine, requests, batch, results, on_token, cancel) -> None:
             live = schedule.live()
             if live:
                 logits = next_logits if len(going_rows) == len(onward) else next_logits[going_rows]
-        sampler.check_status()
     finally:
         for b in range(len(batch)):
             if b not in released:

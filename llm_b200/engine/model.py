@@ -182,24 +182,31 @@ def load_model(folder, dtype=torch.bfloat16, device="cuda:0") -> DecoderModel:
     return model.bind(tensors, dtype, device)
 
 
+class _RandomTensors:
+    """What `bind` reads its tensors from when there is no checkpoint: every declared tensor is
+    made on the device at the moment a part asks for it, and nothing is kept, so a large
+    model is never held twice."""
+
+    def __init__(self, expected: dict, seed: int, std: float, gain_noise: float, device):
+        self.expected, self.seed, self.std, self.gain_noise, self.device = expected, seed, std, gain_noise, device
+
+    def __getitem__(self, name):
+        from ..weights.random_init import random_tensors
+        return random_tensors({name: self.expected[name]}, self.seed, torch.bfloat16, self.std,
+                              self.gain_noise, self.device)[name]
+
+    def __contains__(self, name):
+        return name in self.expected
+
+    def pop(self, name, default=None):
+        return default
+
+
 def random_model(config, seed: int, dtype=torch.bfloat16, device="cuda:0", std: float = 0.02,
                  gain_noise: float = 0.02) -> DecoderModel:
-    """A model with random weights made on `device`, without a model folder."""
-    from ..weights.random_init import random_tensors
+    """A model with random weights made on `device`, without a model folder: the same
+    tensors, bit for bit, that `write_random_model(folder, config, seed)` writes (bfloat16
+    storage) and `load_model` reads back, bound by the same `bind`."""
     model = DecoderModel(config.model_spec())
     model.config = config
-    model.dtype, model.device = dtype, torch.device(device)
-    expected = model.parameters()
-    # layer by layer, so that a large model is never held twice
-    def make(names):
-        return random_tensors({n: expected[n] for n in names}, seed, torch.bfloat16, std,
-                              gain_noise, device)
-    top = [model.spec.embedding] + ([model.spec.head] if model.spec.head else [])
-    tensors = make(top)
-    model.embedding = to_run_dtype(tensors[model.spec.embedding], dtype, device)
-    model.head = (model.embedding if model.spec.head is None
-                  else to_run_dtype(tensors[model.spec.head], dtype, device))
-    for block in model.blocks:
-        block.bind(make(list(block.parameters())), dtype, device)
-    model.final_norm.bind(make(list(model.final_norm.parameters())), dtype, device)
-    return model
+    return model.bind(_RandomTensors(model.parameters(), seed, std, gain_noise, device), dtype, device)

@@ -164,7 +164,7 @@ class Engine:
         done = [0] * len(entries)
         pieces, order = [], []
         while any(done[i] < len(e.tokens) for i, e in enumerate(entries)):
-            part, keys, budget = [], [], self.pass_tokens
+            part, keys, members, budget = [], [], [], self.pass_tokens
             for i, e in enumerate(entries):
                 start = done[i]
                 take = min(len(e.tokens) - start, self.step_tokens, budget)
@@ -173,9 +173,13 @@ class Engine:
                 want = [(j, w - start) for j, w in enumerate(e.want) if start <= w < start + take]
                 part.append(Entry(e.slot, e.tokens[start:start + take], [w for _, w in want]))
                 keys += [(i, j) for j, _ in want]
+                members.append(i)
                 done[i] += take
                 budget -= take
-            pieces.append(self._pass(part))
+            # ids that are still on the device (one per entry): each pass takes its entries' ids
+            feed = None if device_tokens is None else device_tokens[
+                torch.tensor(members, dtype=torch.long, device=device_tokens.device)]
+            pieces.append(self._pass(part, feed))
             order += keys
         logits = torch.cat(pieces)
         wanted = sorted(range(len(order)), key=lambda r: order[r])

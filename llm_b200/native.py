@@ -77,6 +77,7 @@ _SIGNATURES = {
     "llmh_tactics_is_disabled": (c_int, [c_char_p]),
     "llmh_tactics_rows": (c_int, [c_int]),
     "llmh_tactics_row": (c_int, [c_int, c_int, POINTER(c_char_p), _INTS, POINTER(c_char_p)]),
+    "llmh_random_normal": (c_int, [_P, c_int, c_longlong, ctypes.c_ulonglong, ctypes.c_float, ctypes.c_float]),
     "llmh_safetensors_open": (c_int, [c_char_p, POINTER(_P)]),
     "llmh_safetensors_close": (None, [_P]),
     "llmh_safetensors_count": (c_int, [_P]),

@@ -147,6 +147,17 @@ def embed(tokens, table, out=None, scale: float = 1.0):
     return out
 
 
+def random_normal_(out, key: int, mean: float, deviation: float):
+    """out[i] = mean + deviation * N(0, 1) drawn from (key, i); float32 or bfloat16, contiguous."""
+    _require_cuda(out)
+    if not out.is_contiguous():
+        raise KernelError("random_normal_: the tensor must be contiguous")
+    _call("elementwise", "llmb_random_normal", _ptr(out), _c_int(_code(out.dtype)),
+          ctypes.c_longlong(out.numel()), ctypes.c_ulonglong(key), _c_float(mean), _c_float(deviation),
+          _stream())
+    return out
+
+
 def scale_(x, scale: float):
     """x *= scale in place (float32, contiguous)."""
     _require_cuda(x)
@@ -476,6 +487,6 @@ def required_libraries() -> list:
             "attention_decode", "attention_prefill", "attention_prefill_tc", "sampling"]
 
 
-__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
+__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

@@ -202,7 +202,8 @@ def build_identity() -> str:
 # ----------------------------------------------------------------------------- the host library
 
 HOST = CSRC / "host"
-HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+# -ffp-contract=off: the random-weights generator must round every operation as the device does
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-ffp-contract=off", "-pthread"]
 _host_lib = None
 
 
@@ -211,12 +212,13 @@ def _host_compiler() -> list:
         if candidate and (Path(candidate).is_file() or shutil.which(candidate)):
             return [candidate, *HOST_FLAGS]
     # nvcc drives a host compiler of its own choice
-    return [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+    return [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+            "-Xcompiler", "-ffp-contract=off", "-Xcompiler", "-pthread"]
 
 
 def _host_digest() -> str:
     h = hashlib.sha256()
-    for path in sorted(HOST.glob("*.cpp")) + sorted(HOST.glob("*.hpp")) + [CSRC / "plan.h"]:
+    for path in sorted(HOST.glob("*.cpp")) + sorted(HOST.glob("*.hpp")) + [CSRC / "plan.h", CSRC / "random_normal.h"]:
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join(HOST_FLAGS).encode())

@@ -64,7 +64,14 @@ class BatchSampler:
                         self.status, record=True, state_rows=state_rows)
         return out
 
-    def check_status(self) -> None:
-        if bool((self.status != 0).any()):
-            raise KernelError("the device sampler refused a row's parameters "
-                              "(top_k beyond its limit, or too many equal logits at the cut)")
+    def check_status(self, status=None) -> None:
+        """Raise if the kernel refused a row since the last check. The kernel only ever sets
+        the flags; they are cleared here, after they were read. `status`: a host copy that the
+        caller fetched together with the ids (else the device array is read)."""
+        if self.all_greedy:
+            return
+        flags = self.status if status is None else status
+        if bool((flags != 0).any()):
+            self.status.zero_()
+            raise KernelError("the device sampler refused a row (top_k beyond its limit, or too many "
+                              "equal logits at the top-k cut); token 0 was emitted in its place")

@@ -6,6 +6,7 @@ folder layout this library reads: config.json and model.safetensors.
 """
 from __future__ import annotations
 
+import ctypes
 import zlib
 from pathlib import Path
 
@@ -14,29 +15,49 @@ import torch
 from .safetensors_io import write_safetensors
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    return (int(seed) * 0x9E3779B1 + zlib.crc32(name.encode("utf-8"))) & 0x7FFFFFFFFFFFFFFF
+def tensor_key(seed: int, name: str) -> int:
+    """The 64-bit key of one tensor: every element is a function of (key, index)."""
+    return (int(seed) * 0x9E3779B1 + zlib.crc32(name.encode("utf-8"))) & 0xFFFFFFFFFFFFFFFF
+
+
+def normal_(out: torch.Tensor, key: int, mean: float, deviation: float) -> torch.Tensor:
+    """Fill `out` (contiguous float32 or bfloat16, on the CPU or on a CUDA device) with
+    mean + deviation * N(0, 1), element i drawn from (key, i) by the counter-based generator of
+    csrc/random_normal.h. The host library and the device kernel give the same bits."""
+    if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
+        raise ValueError("normal_: a contiguous float32 or bfloat16 tensor is needed")
+    code = 0 if out.dtype == torch.float32 else 1
+    if out.is_cuda:
+        from .. import ops
+        with torch.cuda.device(out.device):
+            ops.random_normal_(out, key, mean, deviation)
+    else:
+        from .. import native
+        native.check(native.lib().llmh_random_normal(
+            ctypes.c_void_p(out.data_ptr()), code, ctypes.c_longlong(out.numel()),
+            ctypes.c_ulonglong(key), ctypes.c_float(mean), ctypes.c_float(deviation)))
+    return out
 
 
 def random_tensors(expected: dict, seed: int, dtype=torch.bfloat16, std: float = 0.02,
                    gain_noise: float = 0.02, device="cpu") -> dict:
-    """One tensor per declared parameter. Each tensor's values depend only on
-    (seed, its name, its shape), not on the order or on the other tensors.
-    Matrices and biases are N(0, std); gains are 1 + N(0, gain_noise)."""
+    """One tensor per declared parameter. Each value depends only on (seed, the tensor's
+    name, its index in the tensor), not on the order, on the other tensors or on the
+    device that makes it: a model made on the GPU and one written to a folder on the CPU
+    from the same seed are the same model. Matrices and biases are N(0, std); gains are
+    1 + N(0, gain_noise). Values are drawn in 32-bit and rounded once to `dtype`."""
     out = {}
     for name in sorted(expected):
         spec = expected[name]
-        gen = torch.Generator(device=device)
-        gen.manual_seed(_tensor_seed(seed, name))
         if spec.role == "table":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        noise = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+        tensor = torch.empty(spec.shape, dtype=dtype, device=device)
         if spec.role == "gain":
-            value = 1.0 + gain_noise * noise
+            normal_(tensor, tensor_key(seed, name), 1.0, gain_noise)
         else:
-            value = std * noise
-        out[name] = value.to(dtype)
+            normal_(tensor, tensor_key(seed, name), 0.0, std)
+        out[name] = tensor
     return out
 
 

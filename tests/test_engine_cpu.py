@@ -100,3 +100,17 @@ def test_slots_are_reused_between_batches(tmp_path, plain_kernels):
             assert torch.allclose(logits[b], expected[-1], atol=2e-5, rtol=1e-5)
         engine.release(slots)
         engine.cache.check()
+
+
+def test_ids_that_are_still_on_the_device_follow_their_entries_into_every_pass(tmp_path, plain_kernels):
+    """A decode step of five sequences with at most two tokens a pass, fed by a tensor of ids
+    instead of host ids: every pass must take its own entries' ids (not placeholder zeros)."""
+    config, weights, engine = _setup(tmp_path, "A", pass_tokens=2)
+    seqs = [random_tokens(n, config["vocab_size"], 80 + n) for n in (9, 4, 12, 6, 3)]
+    slots = engine.acquire(5)
+    engine.step([Entry(s, q[:-1], []) for s, q in zip(slots, seqs)])
+    feed = torch.tensor([q[-1] for q in seqs], dtype=torch.int32)
+    logits = engine.step([Entry(s, [0], [0]) for s in slots], device_tokens=feed)
+    for b, q in enumerate(seqs):
+        expected = plain_llama.forward(config, weights, q)
+        assert torch.allclose(logits[b], expected[-1], atol=2e-5, rtol=1e-5)

@@ -338,6 +338,10 @@ def _check_prefill_attention(heads, kv_heads, dim):
                               dim ** -0.5, 0, seq_lens=seq_lens, max_len=max(lens), cu_seqlens=cu,
                               max_new=max(counts), seq_order=order)
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        # and relative to each row's norm: random softmax outputs are small, a lost key must show
+        g, w = got.float().view(-1, heads, dim), want.float().view(-1, heads, dim)
+        relative = (g - w).norm(dim=-1) / w.norm(dim=-1).clamp_min(1e-3)
+        assert float(relative.max()) < 0.03
 
 
 @pytest.mark.parametrize("variant", ["attention_prefill", "attention_prefill_tc"])
@@ -368,6 +372,50 @@ def test_attention_prefill_growing_scores(variant, dim):
         got = ops().attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads, dim,
                               dim ** -0.5, 0, seq_lens=seq_lens, max_len=n, cu_seqlens=cu, max_new=n)
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        ops().check_device_status()
+    finally:
+        tactics.enable("attention_prefill_tc")
+
+
+@pytest.mark.parametrize("variant", ["attention_prefill", "attention_prefill_tc"])
+@pytest.mark.parametrize("start,count", [(173, 2), (173, 129), (100, 130), (0, 300)])
+def test_prefill_attention_finds_planted_keys(variant, start, count):
+    """Random scores over hundreds of keys hide one lost or wrongly masked key, so keys are
+    planted: one early key (position 3), the key just before a continued chunk's first token,
+    and the chunk's last key. A query that points at a planted key must return that key's value
+    (a query in the chunk's last tile, a chunk that starts off the tile and page edges); the query
+    one position before the last key must not see it."""
+    from llm_b200.ops import tactics
+    heads, kv_heads, dim, dtype = 4, 2, 128, torch.bfloat16
+    n = start + count
+    if variant == "attention_prefill":
+        tactics.disable("attention_prefill_tc")
+    try:
+        assert tactics.choose_attention(False, dtype, heads, kv_heads, dim, 0, True) == variant
+        direction = torch.zeros(dim, device=DEV)
+        direction[5] = 40.0
+        tok_pos = torch.arange(start, n, dtype=torch.int32, device=DEV)
+        tok_seq = torch.zeros(count, dtype=torch.int32, device=DEV)
+        cu = torch.tensor([0, count], dtype=torch.int32, device=DEV)
+        seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+        cases = [(3, n - 1, True), (n - 1, n - 1, True)]
+        if start > 0:
+            cases += [(start - 1, start, True), (start - 1, n - 1, True)]
+        if count >= 2:
+            cases += [(n - 1, n - 2, False)]
+        for key_pos, query_pos, seen in cases:
+            table, width, k_cache, v_cache = make_cache(1, [n], kv_heads, dim, dtype, 130)
+            keys, values = fill_cache(table, width, k_cache, v_cache, [n], 131)
+            k_cache[int(table[0, key_pos // 64]), :, key_pos % 64, :] = direction.to(dtype)
+            q = randn(count, (heads + 2 * kv_heads) * dim, dtype=dtype, seed=132, scale=0.1)
+            q[query_pos - start, :heads * dim] = direction.repeat(heads).to(dtype)
+            got = ops().attention(q, k_cache, v_cache, table, width, tok_pos, tok_seq, heads, kv_heads, dim,
+                                  dim ** -0.5, 0, seq_lens=seq_lens, max_len=n, cu_seqlens=cu, max_new=count)
+            row = got[query_pos - start].float().view(heads, dim)
+            for h in range(heads):
+                expect = values[0][key_pos, h // 2].to(dtype).float()
+                hit = torch.allclose(row[h], expect, atol=2e-2)
+                assert hit == seen, (key_pos, query_pos, h)
         ops().check_device_status()
     finally:
         tactics.enable("attention_prefill_tc")
@@ -502,3 +550,16 @@ def test_sample_rows_refuses_what_it_cannot_rank():
     logits = randn(2, 5000, seed=70)
     ops().sample_rows(logits, f, i, recent, recent_len, rng, out, status)
     assert status.tolist() == [1, 1]
+
+
+def test_a_refused_row_stays_flagged_over_later_steps():
+    """4,096 equal logits at a top-k cut of 40 are more ties than the kernel ranks: the row is refused.
+    The next launch, on logits it can rank, must not erase the flag (only the host clears it)."""
+    f, i, recent, recent_len, rng, out, status = _sampler_state(
+        2, [[1.0, 0.9, 0.0, 1.0], [1.0, 0.9, 0.0, 1.0]], [[40, 0], [40, 0]], [1, 2])
+    logits = torch.zeros(2, 4096, device=DEV)
+    logits[1] = randn(1, 4096, seed=71)[0]
+    ops().sample_rows(logits, f, i, recent, recent_len, rng, out, status)
+    assert status.tolist() == [1, 0] and out.tolist()[0] == 0
+    ops().sample_rows(randn(2, 4096, seed=72), f, i, recent, recent_len, rng, out, status)
+    assert status.tolist() == [1, 0]

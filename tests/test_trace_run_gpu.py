@@ -48,7 +48,7 @@ def check(got, want, dtype):
     scale = max(float(np.abs(want).max()), 1.0)
     error = np.abs(got - want)
     if dtype == "float32":
-        assert error.max() <= 2e-4 * scale
+        assert error.max() <= 5e-5 * scale
     else:
         assert error.max() <= 0.04 * scale and error.mean() <= 0.008 * scale
 
@@ -104,5 +104,64 @@ def test_replay(tmp_path, dtype, which):
                     assert got is None
                 live = [n for n in live if n not in ending]
                 k += 1
+    finally:
+        replay.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_three_modes_of_a_trace_file(tmp_path, dtype):
+    """--trace FILE --mode whole|tail32|batches: the program makes the steps itself and writes
+    one logits file and one sidecar per request; all three modes agree with the plain
+    implementation at every position, on a cache that holds one batch but not both."""
+    folder = make_folder(tmp_path, "D", torch.bfloat16)
+    config, weights = plain_llama.read_model_folder(folder)
+    vocab = config["vocab_size"]
+    requests = {name: random_tokens(n, vocab, 60 + n) for name, n in
+                (("a", 70), ("b", 33), ("c", 100), ("d", 1), ("e", 64))}
+    trace = tmp_path / "trace.json"
+    trace.write_text(json.dumps({"requests": [{"id": k, "tokens": t} for k, t in requests.items()],
+                                 "batches": [["a", "b", "c"], ["d", "e", "b"]]}))
+    expected = {name: plain_llama.forward(config, weights, t) for name, t in requests.items()}
+    for mode in ("whole", "tail32", "batches"):
+        out = tmp_path / f"out_{dtype}_{mode}"
+        done = subprocess.run(
+            [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
+             "--out", str(out), "--max-tokens", str(64 * 5), "--trace", str(trace), "--mode", mode],
+            stdin=subprocess.DEVNULL, stdout=subprocess.PIPE, text=True, timeout=600)
+        assert done.returncode == 0
+        assert done.stdout.strip().splitlines()[-1].startswith("done ")
+        for name, tokens in requests.items():
+            side = json.loads((out / f"logits_{name}.json").read_text())
+            assert side["id"] == name and side["vocab"] == vocab and side["mode"] == mode
+            assert side["positions"] == list(range(len(tokens)))
+            check(np.fromfile(out / f"logits_{name}.f32", dtype="<f4"), expected[name], dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_of_continued_prompts_and_a_mixed_step(tmp_path, dtype):
+    """Through the program: a prompt that arrives in three pieces (the later pieces attend to the
+    cache of the earlier ones), and a step in which two requests bring one token while a third
+    brings 70 tokens onto a slot that already holds 50."""
+    folder = make_folder(tmp_path, "F", torch.bfloat16)
+    config, weights = plain_llama.read_model_folder(folder)
+    vocab = config["vocab_size"]
+    a, b, c = (random_tokens(n, vocab, 70 + n) for n in (300, 90, 130))
+    want = {k: plain_llama.forward(config, weights, t) for k, t in (("a", a), ("b", b), ("c", c))}
+    replay = Replay(folder, dtype, tmp_path / f"out_{dtype}", max_tokens=64 * 10)
+    try:
+        at = 0
+        for piece in (48, 152, 100):
+            got = replay.step([{"id": "a", "tokens": a[at:at + piece], "want": list(range(piece))}],
+                              end=["a"] if at + piece == len(a) else [])
+            check(got, want["a"][at:at + piece], dtype)
+            at += piece
+        got = replay.step([{"id": "b", "tokens": b[:80], "want": [79]}, {"id": "c", "tokens": c[:50], "want": [49]}])
+        check(got, torch.stack([want["b"][79], want["c"][49]]), dtype)
+        got = replay.step([{"id": "b", "tokens": [b[80]], "want": [0]},
+                           {"id": "c", "tokens": c[50:120], "want": [0, 69]}])
+        check(got, torch.stack([want["b"][80], want["c"][50], want["c"][119]]), dtype)
+        got = replay.step([{"id": "b", "tokens": [b[81]], "want": [0]}, {"id": "c", "tokens": [c[120]], "want": [0]}],
+                          end=["b", "c"])
+        check(got, torch.stack([want["b"][81], want["c"][120]]), dtype)
     finally:
         replay.close()

@@ -116,6 +116,37 @@ def test_random_model_folder_is_seeded_and_order_independent(tmp_path):
     assert torch.equal(alone["lm_head.weight"], f.tensor("lm_head.weight"))
 
 
+def test_the_host_generator_equals_its_plain_statement_bit_for_bit():
+    import numpy as np
+    import plain_random
+    from llm_b200.weights.random_init import normal_, tensor_key
+    for seed, name, n in ((0, "model.embed_tokens.weight", 70001), (7, "x", 33), (123456789, "lm_head.weight", 1 << 17)):
+        key = tensor_key(seed, name)
+        assert key == plain_random.tensor_key(seed, name)
+        want = plain_random.normal(key, n, 0.0, 0.02)
+        got = normal_(torch.empty(n), key, 0.0, 0.02).numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        half = normal_(torch.empty(n, dtype=torch.bfloat16), key, 1.0, 0.02)
+        want_half = torch.from_numpy(plain_random.normal(key, n, 1.0, 0.02)).to(torch.bfloat16)
+        assert torch.equal(half.view(torch.int16), want_half.view(torch.int16))
+    z = normal_(torch.empty(400000), tensor_key(1, "z"), 0.0, 1.0)
+    assert abs(float(z.mean())) < 0.01 and abs(float(z.std()) - 1.0) < 0.01
+    assert abs(float((z ** 4).mean()) - 3.0) < 0.1 and float(z.abs().max()) > 4.0      # normal tails
+
+
+def test_a_model_made_in_memory_equals_the_folder_of_the_same_seed(tmp_path):
+    from llm_b200.engine import random_model
+    config = config_from_dict(dict(TINY_B))
+    folder = write_random_model(tmp_path / "m", config, seed=9, std=0.05)
+    loaded = load_model(folder, torch.bfloat16, "cpu")
+    made = random_model(config, 9, torch.bfloat16, "cpu", std=0.05)
+    assert torch.equal(loaded.embedding, made.embedding) and torch.equal(loaded.head, made.head)
+    for a, b in zip(loaded.blocks, made.blocks):
+        for x, y in zip(a.weights(), b.weights()):
+            assert x.dtype == y.dtype and torch.equal(x, y)
+    assert torch.equal(loaded.final_norm.gain, made.final_norm.gain)
+
+
 def test_storage_dtypes_and_32_bit_run(tmp_path):
     folder = make_folder(tmp_path, "A", torch.float32)
     assert SafetensorsFile(folder / "model.safetensors").dtype("model.norm.weight") == torch.float32
