@@ -142,7 +142,7 @@ def test_gated_mlp_alone(dtype, hidden, inter):
         want = P.gated_mlp(h.to(dtype).float(), w["f.g"].float(), w["f.u"].float(), w["f.d"].float())
         residual = torch.ones(n, hidden, device=DEV)
         from types import SimpleNamespace
-        ffn.forward(h.to(DEV).to(dtype), SimpleNamespace(scratch=lambda name: None, extras={}), residual)
+        ffn.forward(h.to(DEV).to(dtype), SimpleNamespace(scratch=lambda name, shape=None, dtype=None: None, extras={}), residual)
         assert close(residual - 1.0, want, dtype)
 
 
