@@ -1,13 +1,18 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py --workload llama-2-7b | llama-3.2-1b | 8b-decode512
 
 The default run has the layer sizes of a Llama-3.1-8B (32 layers, hidden 4096,
 32 heads over 8 kv heads of 128, feed-forward 14336, vocabulary 128256, llama3
 rope scaling) with random bfloat16 weights, a batch of 8 and a context of 8192.
 A step is one decode step of the whole batch; `value` is decoded tokens a
 second, timed with CUDA events over exactly K steps after W warm-up steps.
-One JSON line goes to standard output. The test names follow the `pp`/`tg`
+One JSON line goes to standard output. `--workload` runs one of the other workloads of the
+baseline instead and prints its own line: a Llama-2-7B shape with 16 prompts of 64 to 2,048
+tokens and 128 new tokens each, a Llama-3.2-1B shape with 64 prompts of 1 to 8,192 tokens and
+256 new tokens at temperature 0.7 (both through `LLM.generate`, host ids in and out), and the
+Llama-3.1-8B shape decoding 256 tokens after prompts of 512 at batch 1, 8 and 64. The test names follow the `pp`/`tg`
 split of MythEclipse/llm's bench (apps/cli/src/bench.rs:10-12): prefill alone,
 and decoding alone on a cache that is already filled.
 """
@@ -109,6 +114,124 @@ def reference_arm():
     return 0
 
 
+# ----------------------------------------------------------------------------- the other workloads
+
+def _generate_workload(args, shape_name, model_label, n_prompts, low, high, new_tokens, context, sampling, note):
+    """`n_prompts` prompts with lengths uniform in [low, high], `new_tokens` new tokens each, through
+    LLM.generate: tokens a second over the decode steps (host ids in and out), the bytes a decode
+    step has to read at the mean context and their fraction of the copy rate."""
+    import time
+
+    import torch
+    import llm_b200
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine import random_model
+    from llm_b200.shapes import shape
+
+    torch.cuda.set_device(0)
+    config = config_from_dict(shape(shape_name))
+    peak, peak_source = peaks()
+    model = random_model(config, seed=0)
+    gen = torch.Generator().manual_seed(0)
+    lengths = torch.randint(low, high + 1, (n_prompts,), generator=gen).tolist()
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    llm = llm_b200.LLM(model, context=context, batch=n_prompts)
+    llm.generate([p[:8] for p in prompts[:2]], max_tokens=4, temperature=0.0, stop_tokens=[])
+    clocks = ClockSampler()
+    clocks.start()
+    runs = []
+    for repeat in range(max(1, min(args.steps, 3))):
+        started = time.perf_counter()
+        results = llm.generate(prompts, max_tokens=new_tokens, stop_tokens=[], details=True, **sampling)
+        total_s = time.perf_counter() - started
+        decode_s = max(r.decode_ms for r in results) * 1e-3
+        runs.append({"decode_tok_s": sum(r.generated_tokens - 1 for r in results) / decode_s,
+                     "prefill_tok_s": sum(lengths) / (results[0].prefill_ms * 1e-3),
+                     "total_s": total_s, "ttft_ms": results[0].ttft_ms, "decode_s": decode_s})
+    clocks.stop()
+    llm.engine.cache.check()
+    best = max(runs, key=lambda r: r["decode_tok_s"])
+    mean = sum(r["decode_tok_s"] for r in runs) / len(runs)
+    spread = (sum((r["decode_tok_s"] - mean) ** 2 for r in runs) / len(runs)) ** 0.5
+    kv_bytes_per_token = 2 * config.num_key_value_heads * config.head_dim * config.num_hidden_layers * 2
+    mean_context = sum(lengths) / n_prompts + new_tokens / 2
+    step_bytes = model.weight_bytes() + n_prompts * mean_context * kv_bytes_per_token
+    step_s = best["decode_s"] / (new_tokens - 1)
+    print(json.dumps({
+        "metric": f"decode tokens/s through LLM.generate, {model_label} shape bf16, {note}",
+        "value": round(mean, 1), "stddev": round(spread, 1), "repeats": len(runs), "unit": "tokens/s",
+        "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "prefill_tokens_per_s": round(best["prefill_tok_s"], 1), "ttft_ms": round(best["ttft_ms"], 1),
+        "total_s": round(best["total_s"], 3), "prompt_tokens": sum(lengths), "new_tokens": new_tokens,
+        "config": {"model": model_label, "layers": config.num_hidden_layers, "hidden": config.hidden_size,
+                   "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+                   "head_dim": config.head_dim, "intermediate": config.intermediate_size,
+                   "vocab": config.vocab_size, "global_batch": n_prompts, "context": context,
+                   "prompt_lengths": f"uniform in [{low}, {high}]", "weights": "random N(0,0.02) seed 0",
+                   "peaks": peak_source},
+        "roofline": {"bound": "hbm", "bytes_per_step": int(step_bytes),
+                     "achieved": round(step_bytes / step_s / 1e9, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(step_bytes / step_s / 1e9 / peak["hbm_gbs"], 4)},
+        "clocks": clocks.summary()}))
+    return 0
+
+
+def workload_llama_2_7b(args):
+    return _generate_workload(args, "llama-2-7b", "llama-2-7b", 16, 64, 2048, 128, 4096,
+                              dict(temperature=0.0), "16 prompts of 64 to 2,048 tokens, 128 new tokens, greedy")
+
+
+def workload_llama_3_2_1b(args):
+    return _generate_workload(args, "llama-3.2-1b", "llama-3.2-1b", 64, 1, 8192, 256, 8192 + 256,
+                              dict(temperature=0.7), "64 prompts of 1 to 8,192 tokens, 256 new tokens at temperature 0.7")
+
+
+def workload_8b_decode512(args):
+    """Llama-3.1-8B shape: prompts of 512 tokens and 256 new tokens at batch 1, 8 and 64, through
+    LLM.generate (the baseline's own decode workload; the default run decodes at a full context)."""
+    import torch
+    import llm_b200
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine import random_model
+    from llm_b200.shapes import shape
+
+    torch.cuda.set_device(0)
+    config = config_from_dict(shape("llama-3.1-8b", args.layers))
+    peak, peak_source = peaks()
+    model = random_model(config, seed=0)
+    kv_bytes_per_token = 2 * config.num_key_value_heads * config.head_dim * args.layers * 2
+    clocks = ClockSampler()
+    clocks.start()
+    points = {}
+    for batch in (1, 8, 64):
+        llm = llm_b200.LLM(model, context=1024, batch=batch)
+        gen = torch.Generator().manual_seed(batch)
+        prompts = [torch.randint(0, config.vocab_size, (512,), generator=gen).tolist() for _ in range(batch)]
+        llm.generate(prompts, max_tokens=8, temperature=0.0, stop_tokens=[])
+        results = llm.generate(prompts, max_tokens=256, temperature=0.0, stop_tokens=[], details=True)
+        decode_s = max(r.decode_ms for r in results) * 1e-3
+        step_bytes = model.weight_bytes() + batch * 640 * kv_bytes_per_token
+        points[f"b{batch}"] = {"decode_tok_s": round(batch * 255 / decode_s, 1),
+                               "prefill_tok_s": round(batch * 512 / (results[0].prefill_ms * 1e-3), 1),
+                               "hbm_frac": round(step_bytes / (decode_s / 255) / 1e9 / peak["hbm_gbs"], 3)}
+        del llm
+        torch.cuda.empty_cache()
+    clocks.stop()
+    print(json.dumps({
+        "metric": "decode tokens/s through LLM.generate, Llama-3.1-8B shape bf16, prompts 512, 256 new tokens",
+        "value": points["b8"]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
+        "dtype": "bf16", "data": "synthetic", "points": points,
+        "config": {"model": "llama-3.1-8b-shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "prompt": 512, "new_tokens": 256, "weights": "random N(0,0.02) seed 0", "peaks": peak_source},
+        "clocks": clocks.summary()}))
+    return 0
+
+
+WORKLOADS = {"llama-2-7b": workload_llama_2_7b, "llama-3.2-1b": workload_llama_3_2_1b,
+             "8b-decode512": workload_8b_decode512}
+
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -125,6 +248,8 @@ def main() -> int:
     parser.add_argument("--e2e-context", type=int, default=None,
                         help="context of the run through the entry point (default: --context)")
     parser.add_argument("--dtype", default="bfloat16")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
+                        help="run one of the baseline's other workloads and print its line")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -132,6 +257,8 @@ def main() -> int:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not built (single-GPU library)")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload:
+        return WORKLOADS[args.workload](args)
 
     import torch
     import llm_b200
@@ -240,26 +367,45 @@ def main() -> int:
         for b in (1, 64):
             r = time_decode(b, args.context, max(8, args.steps // 4), 3)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peak["hbm_gbs"], 3)
+        # the baseline's own decode workload: prompts of 512 tokens, 256 new tokens (contexts 512 to 768)
+        for b in (1, 8, 64):
+            r = time_decode(b, 768, 252, 3)
+            points[f"p512_n256_b{b}"] = round(r["tok_s"], 1)
+            points[f"p512_n256_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peak["hbm_gbs"], 3)
 
     e2e = None
     if not args.no_e2e:
         # the same decode metric through the Python entry point: host token ids in
-        # (pinned, copied every step with the step's index arrays), sampled ids out
+        # (pinned, copied every step with the step's index arrays), sampled ids out.
+        # 256 tokens are generated after prompts that fill the context up to them; the
+        # prefill of those prompts runs at the power cap and leaves the clock low for the
+        # first steps, so the steps after the first 64 are also reported on their own.
+        import time
         llm = llm_b200.LLM(model, context=args.context, batch=args.batch)
-        e2e_steps = args.steps
-        prompt_len = (args.e2e_context or args.context) - e2e_steps - 1
+        e2e_new = 256
+        prompt_len = (args.e2e_context or args.context) - e2e_new - 1
         prompts = [torch.randint(0, config.vocab_size, (prompt_len,),
                                  generator=torch.Generator().manual_seed(100 + i)).tolist()
                    for i in range(args.batch)]
         llm.generate(prompts, max_tokens=4, temperature=0.0, stop_tokens=[])      # warm-up
-        results = llm.generate(prompts, max_tokens=e2e_steps, temperature=0.0, stop_tokens=[],
-                               details=True)
+        stamps = []
+        mark = clocks.mark()
+        results = llm.generate(prompts, max_tokens=e2e_new, temperature=0.0, stop_tokens=[], details=True,
+                               on_token=lambda index, token: stamps.append(time.perf_counter()) if index == 0 else None)
+        e2e_clock = clocks.summary(mark, clocks.mark())
         decode_s = max(r.decode_ms for r in results) * 1e-3
         generated = sum(r.generated_tokens - 1 for r in results)
+        steady_s = stamps[-1] - stamps[64]
+        steady_steps = len(stamps) - 1 - 64
         table_ints = sum(llm.engine.cache.table_width(g) for g in range(len(llm.engine.cache.groups)))
         e2e = {"value": round(generated / decode_s, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": 4 * args.batch * (7 + table_ints),
-               "d2h_bytes_per_step": 4 * args.batch, "prompt_tokens": prompt_len}
+               "d2h_bytes_per_step": 4 * args.batch, "prompt_tokens": prompt_len, "new_tokens": e2e_new,
+               "steady_value": round(args.batch * steady_steps / steady_s, 1),
+               "steady_ms_per_step": round(steady_s / steady_steps * 1e3, 4), "steady_after_steps": 64,
+               "sm_mhz": e2e_clock["sm_mhz"],
+               "ms_x_ghz": round(steady_s / steady_steps * 1e3 * (e2e_clock["sm_mhz"] or 0) / 1e3, 3)}
     clocks.stop()
 
     line = {
@@ -288,6 +434,8 @@ def main() -> int:
         "gpu_launches": main_run["launches"],
         "clocks": clocks.summary(*main_run["clock_mark"]),
     }
+    main_clock = line["clocks"]
+    line["ms_x_ghz"] = round(main_run["ms"] * (main_clock["sm_mhz"] or 0) / 1e3, 3)
     print(json.dumps(line))
     return 0
 

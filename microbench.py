@@ -1,11 +1,11 @@
 """Time one kernel of the library alone, at a given shape.
 
-    python -m llm_b200.ops.microbench linear --m 8 --n 6144 --k 4096 [--variant gemm_skinny]
-    python -m llm_b200.ops.microbench attention_decode --batch 8 --context 8192
-    python -m llm_b200.ops.microbench attention_prefill --tokens 2048
-    python -m llm_b200.ops.microbench rmsnorm --m 8 --k 4096
-    python -m llm_b200.ops.microbench sample --batch 8 --n 128256 [--temperature 0.7]
-    LLMB_NVCC_FLAGS=-DLLMB_TRACE python -m llm_b200.ops.microbench linear --m 8 --n 6144 --k 4096 --timeline
+    python microbench.py linear --m 8 --n 6144 --k 4096 [--variant gemm_skinny]
+    python microbench.py attention_decode --batch 8 --context 8192
+    python microbench.py attention_prefill --tokens 2048
+    python microbench.py rmsnorm --m 8 --k 4096
+    python microbench.py sample --batch 8 --n 128256 [--temperature 0.7]
+    LLMB_NVCC_FLAGS=-DLLMB_TRACE python microbench.py linear --m 8 --n 6144 --k 4096 --timeline
 
 Each call is timed inside a CUDA graph of `--reps` back-to-back launches (so that
 the host's launch cost is not in the number), with CUDA events, after warm-up.
@@ -21,10 +21,13 @@ from __future__ import annotations
 
 import argparse
 import sys
+from pathlib import Path
 
 import torch
 
-from . import attention, linear, rmsnorm, rope_cache_write, swiglu, tactics
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+from llm_b200.ops import attention, linear, rmsnorm, rope_cache_write, swiglu, tactics  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -80,7 +83,7 @@ def timeline(fn, label: str, library: str = "gemm_tc") -> int:
     """Back-to-back launches of fn, then the global-timer stamps of the last one, in microseconds
     after its first block started: earliest, median and latest block for every phase."""
     import ctypes
-    from .build import load_library
+    from llm_b200.ops.build import load_library
     lib = load_library(library)
     read = getattr(lib, f"llmb_{library}_trace")
     rows, slots = 296, 12
@@ -192,7 +195,7 @@ def main(argv=None) -> int:
             run(fn, args, 0.0, 2.0 * 2.0 * ctx * ctx / 2 * d * hq,
                 f"attention_prefill tokens={ctx} heads={hq}/{hkv} D={d} (causal flops)")
     elif args.op == "sample":
-        from ..sampling import BatchSampler, SamplingParams
+        from llm_b200.sampling import BatchSampler, SamplingParams
         vocab, rows = args.n, list(range(args.batch))
         sampler = BatchSampler([SamplingParams(temperature=args.temperature)] * args.batch, vocab, DEV)
         base = torch.randn(args.batch, vocab, device=DEV)

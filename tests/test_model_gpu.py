@@ -404,3 +404,36 @@ def test_a_mixed_step(folders, plain, dtype, which):
     assert close(last, torch.stack([expected[0][82], expected[1][39], expected[2][120]]), dtype)
     engine.release(slots)
     engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_family_size_layers_against_the_plain_implementation(tmp_path, dtype):
+    """The layer sizes of a Llama-3.1-8B (hidden 4096, 32 heads over 8 kv heads of 128,
+    feed-forward 14336, vocabulary 128256, llama3 rope scaling), 2 of its 32 layers plus the head,
+    with the weights the benchmark runs on (seed 0, N(0, 0.02)), written to a folder and read
+    back: a 64-token prompt and 8 greedy decode steps. 32-bit: logits within 1e-3 of the plain
+    implementation on the CPU and the same greedy tokens; bfloat16: the usual tolerance."""
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine import Engine, Entry, load_model
+    from llm_b200.shapes import shape
+    from llm_b200.weights import write_random_model
+    config = config_from_dict(shape("llama-3.1-8b", 2))
+    folder = write_random_model(tmp_path / "family", config, seed=0)
+    engine = Engine(load_model(folder, dtype, DEV), max_tokens=128)
+    prompt = random_tokens(64, config.vocab_size, 17)
+    (slot,) = engine.acquire()
+    rows = [engine.step([Entry(slot, prompt, [63])])]
+    tokens = list(prompt)
+    for _ in range(8):
+        tokens.append(int(rows[-1][0].argmax()))
+        rows.append(engine.step([Entry(slot, [tokens[-1]], [0])]))
+    got = torch.cat(rows).cpu()
+    del engine
+    torch.cuda.empty_cache()
+    config_plain, weights = plain_llama.read_model_folder(folder)
+    want = plain_llama.forward(config_plain, weights, tokens)[63:]
+    if dtype == torch.float32:
+        assert float((got - want).abs().max()) <= 1e-3
+        assert [int(r.argmax()) for r in want[:-1]] == tokens[64:]
+    else:
+        assert close(got, want, dtype)
