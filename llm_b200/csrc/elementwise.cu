@@ -3,6 +3,7 @@
 // activation. Every kernel exists for 32-bit and for bfloat16 activations;
 // sums, angles and the residual stream are 32-bit in both.
 #include "common.cuh"
+#include "fusion.h"
 #include "random_normal.h"
 
 using namespace llmb;
@@ -14,15 +15,41 @@ LLMB_DEFINE_LAST_ERROR(llmb_elementwise)
 // Formula: apps/engine/kernels/gpu.cu:1752-1766 of MythEclipse/llm (one thread per
 // (token, column)); here one block per token, columns strided over the threads.
 // `scale` multiplies every value (1 for Llama; an architecture's embedding scale otherwise).
+// With `rows` and `sumsq` the kernel also leaves the first norm's input: the row as bfloat16 and the
+// sum of its squares (one partial sum, see fusion.h).
+__device__ __forceinline__ float block_sum_256(float v, float* scratch) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += scratch[i];               // the same order in every thread
+    return total;
+}
+
 template <typename T>
-__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ x, int hidden, int vocab, int vector, float scale) {
+__global__ void __launch_bounds__(256)
+embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ x, int hidden,
+             int vocab, int vector, float scale, __nv_bfloat16* __restrict__ rows, float* __restrict__ sumsq) {
+    __shared__ float scratch[8];
     int t = blockIdx.x;
     int token = tokens[t];
     griddep_launch();
     if (token < 0 || token >= vocab) token = 0;   // host checks ids; device-sampled ids are in range
     const T* row = table + (size_t)token * hidden;
     float* out = x + (size_t)t * hidden;
+    if (rows) {                                   // any width; the row is short enough to take element by element
+        float sq = 0.f;
+        for (int e = threadIdx.x; e < hidden; e += blockDim.x) {
+            float v = to_float(row[e]) * scale;
+            out[e] = v;
+            rows[(size_t)t * hidden + e] = __float2bfloat16_rn(v);
+            sq = fmaf(v, v, sq);
+        }
+        float total = block_sum_256(sq, scratch);
+        if (threadIdx.x == 0) sumsq[(size_t)t * LLMB_SUMSQ_LD] = total;
+        return;
+    }
     if (vector) {
         // 16 bytes of the table per load (hidden is a multiple of 16 / sizeof(T), rows are aligned)
         constexpr int PER = 16 / sizeof(T);
@@ -42,16 +69,20 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 }
 
 LLMB_EXPORT int llmb_embed(const int* tokens, const void* table, int table_dtype, float* x,
-                           int n_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
+                           int n_tokens, int hidden, int vocab, float scale, void* rows, float* sumsq,
+                           cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
+    LLMB_REQUIRE((rows != nullptr) == (sumsq != nullptr), "embed: give both the bfloat16 rows and the sums, or neither");
     int aligned = (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     if (table_dtype == LLMB_DTYPE_F32)
         embed_kernel<float><<<n_tokens, 256, 0, stream>>>(tokens, (const float*)table, x, hidden, vocab,
-                                                         aligned && hidden % 4 == 0, scale);
+                                                         aligned && hidden % 4 == 0, scale,
+                                                         (__nv_bfloat16*)rows, sumsq);
     else if (table_dtype == LLMB_DTYPE_BF16)
         embed_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, hidden,
-                                                                 vocab, aligned && hidden % 8 == 0, scale);
+                                                                 vocab, aligned && hidden % 8 == 0, scale,
+                                                                 (__nv_bfloat16*)rows, sumsq);
     else
         return fail(LLMB_ERR_ARGUMENT, "embed: unknown dtype %d", table_dtype);
     return check_launch("embed");
@@ -163,6 +194,80 @@ LLMB_EXPORT int llmb_rmsnorm(const float* x, const float* gain, const int* rows,
     else
         return fail(LLMB_ERR_ARGUMENT, "rmsnorm: unknown dtype %d", out_dtype);
     return check_launch("rmsnorm");
+}
+
+// ----------------------------------------------------------------------------- a norm's input without the norm
+// rows[t, :] = bfloat16(x[t, :]) and sumsq[t, 0] = sum of x[t, :]^2: what a product with a folded norm reads
+// (fusion.h) when no product's epilogue has left it. One block per row, the sum in a fixed order.
+__global__ void __launch_bounds__(256)
+cast_sumsq_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ rows, float* __restrict__ sumsq,
+                  int hidden, int vector) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float scratch[8];
+    int t = blockIdx.x;
+    const float* in = x + (size_t)t * hidden;
+    __nv_bfloat16* out = rows + (size_t)t * hidden;
+    float sq = 0.f;
+    if (vector) {
+        for (int q = threadIdx.x; q < hidden / 4; q += blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(in)[q];
+            sq = fmaf(v.x, v.x, sq);
+            sq = fmaf(v.y, v.y, sq);
+            sq = fmaf(v.z, v.z, sq);
+            sq = fmaf(v.w, v.w, sq);
+            store_quad(out + 4 * q, v.x, v.y, v.z, v.w);
+        }
+    } else {
+        for (int e = threadIdx.x; e < hidden; e += blockDim.x) {
+            float v = in[e];
+            sq = fmaf(v, v, sq);
+            out[e] = __float2bfloat16_rn(v);
+        }
+    }
+    float total = block_sum_256(sq, scratch);
+    if (threadIdx.x == 0) sumsq[(size_t)t * LLMB_SUMSQ_LD] = total;
+}
+
+LLMB_EXPORT int llmb_cast_sumsq(const float* x, void* rows, float* sumsq, int n_rows, int hidden,
+                                cudaStream_t stream) {
+    if (n_rows == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_rows > 0 && hidden > 0, "cast_sumsq: bad sizes");
+    int vector = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(rows) & 7) == 0;
+    llmb::launch(cast_sumsq_kernel, n_rows, 256, 0, stream, true, x, (__nv_bfloat16*)rows, sumsq, hidden, vector);
+    return check_launch("cast_sumsq");
+}
+
+// out[t, :] = out[t, :] * rstd(t) + bias: the folded norm's scale for a product whose kernel does not
+// apply it itself (rstd from the partial sums of squares as in fusion.h).
+template <typename T>
+__global__ void scale_rows_kernel(T* __restrict__ out, int width, const float* __restrict__ sumsq, int parts,
+                                  float eps, float norm_width, const float* __restrict__ bias) {
+    __shared__ float scale_s;
+    int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        float s = 0.f;
+        for (int i = 0; i < parts; ++i) s += sumsq[(size_t)t * LLMB_SUMSQ_LD + i];
+        scale_s = 1.0f / sqrtf(s / norm_width + eps);
+    }
+    __syncthreads();
+    float scale = scale_s;
+    for (int e = threadIdx.x; e < width; e += blockDim.x)
+        out[(size_t)t * width + e] = from_float<T>(to_float(out[(size_t)t * width + e]) * scale + (bias ? bias[e] : 0.f));
+}
+
+LLMB_EXPORT int llmb_scale_rows(void* out, int dtype, int n_rows, int width, const float* sumsq, int parts,
+                                float eps, float norm_width, const float* bias, cudaStream_t stream) {
+    if (n_rows == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_rows > 0 && width > 0 && parts >= 1 && parts <= LLMB_SUMSQ_LD, "scale_rows: bad sizes");
+    if (dtype == LLMB_DTYPE_F32)
+        scale_rows_kernel<float><<<n_rows, 256, 0, stream>>>((float*)out, width, sumsq, parts, eps, norm_width, bias);
+    else if (dtype == LLMB_DTYPE_BF16)
+        scale_rows_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>((__nv_bfloat16*)out, width, sumsq, parts, eps,
+                                                                   norm_width, bias);
+    else
+        return fail(LLMB_ERR_ARGUMENT, "scale_rows: unknown dtype %d", dtype);
+    return check_launch("scale_rows");
 }
 
 // ----------------------------------------------------------------------------- rotary + cache write

@@ -41,6 +41,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "fusion.h"
 #include "tc.cuh"
 
 using namespace llmb;
@@ -64,7 +65,26 @@ struct Epilogue {
     int tokens, outs;        // valid tokens and output columns (rows of the weight matrix)
     int glu;                 // gated activation: the weight rows alternate 16 gate rows, 16 up rows;
                              // out is bfloat16 [tokens, ldo] with outs / 2 columns silu(gate) * up
+    llmb_gemm_fusion f;      // what else the epilogue does (fusion.h); all zero: nothing
 };
+
+// 1 / sqrt(mean of squares + eps) of an input row from the partial sums its producer left, added in
+// the order of the parts (every consumer of a row gets the same bits)
+__device__ __forceinline__ float row_rstd(const llmb_gemm_fusion& f, int token) {
+    const float* p = f.norm_sumsq + (size_t)token * LLMB_SUMSQ_LD;
+    float s = 0.f;
+    for (int i = 0; i < f.norm_parts; ++i) s += __ldcg(p + i);
+    return 1.0f / sqrtf(s / f.norm_width + f.norm_eps);
+}
+
+// The scales of a tile's token rows into shared memory, by the 128 epilogue threads (local = 0..127),
+// before the tile's accumulator is awaited. The caller synchronises the epilogue warps afterwards.
+__device__ __forceinline__ void tile_rstd(const Epilogue& ep, float* rstd, int local, int first_token, int n_tile_tokens) {
+    if (local < n_tile_tokens) {
+        int token = first_token + local;
+        rstd[local] = token < ep.tokens ? row_rstd(ep.f, token) : 1.f;
+    }
+}
 
 static_assert(LLMB_GLU_BLOCK == 16, "the gated epilogue reads 16 gate and 16 up columns of tensor memory per pair");
 
@@ -86,9 +106,21 @@ __device__ __forceinline__ Unit unit_of(int u, int tiles_a, int splits) {
 // Stores 16 consecutive accumulator columns (c .. c+15) of this thread's row.
 // `preloaded` (swapped products with a residual only): the residual's values at these 16 places,
 // read by the caller earlier so that their latency ran under other loads.
+// `rstd` (shared memory, or nullptr): the scales of the tile's token rows (a folded norm).
 template <int BN>
 __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int a_row, int tile_b,
-                                              int c, float (&v)[16], const float* preloaded = nullptr) {
+                                              int c, float (&v)[16], const float* preloaded = nullptr,
+                                              const float* rstd = nullptr, int tile_row = 0) {
+    if (rstd) {
+        if (swap) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= rstd[c + j];
+        } else {
+            float r = rstd[tile_row];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= r;
+        }
+    }
     if (swap && ep.glu) {
         // lanes 0-15 of a warp hold 16 gate rows, lanes 16-31 the up rows of the same features
         int lane = threadIdx.x & 31;
@@ -185,6 +217,99 @@ __device__ __forceinline__ void store_columns(const Epilogue& ep, int swap, int 
     }
 }
 
+// ---- the fused epilogues of a decode tile (weights on the 128-row side, tiles of 16 tokens), run by the
+// four epilogue warps of the block that arrived last at the tile; v[j] is the summed (and scaled) product
+// for output column a_row and token first_token + j, j < valid.
+
+// Adds into the residual and also leaves what the next norm needs: the updated rows as bfloat16 and,
+// per token, the sum of their squares over this tile's 128 columns as partial `tile_a` of the row.
+// The sum runs over lanes, then over the four warps in a fixed order. exch: 64 floats.
+__device__ __forceinline__ void finish_emit(const Epilogue& ep, int a_row, int tile_a, int first_token, int valid,
+                                            float (&v)[16], const float (&old)[16], float* exch) {
+    int lane = threadIdx.x & 31, quarter = (threadIdx.x >> 5) & 3;
+    bool live = a_row < ep.outs;
+    float b = (ep.bias && live) ? ep.bias[a_row] : 0.f;
+    __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(ep.f.emit_rows);
+    float sq[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        float updated = old[j] + (v[j] + b);
+        bool here = live && j < valid;
+        if (here) {
+            size_t at = (size_t)(first_token + j) * ep.ldo + a_row;
+            ep.residual[at] = updated;
+            rows[at] = __float2bfloat16_rn(updated);
+        }
+        sq[j] = here ? updated * updated : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sq[j] = warp_sum(sq[j]);
+    if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) exch[quarter * 16 + j] = sq[j];
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    int local = (int)threadIdx.x - 64;
+    if (local < valid)
+        ep.f.emit_sumsq[(size_t)(first_token + local) * LLMB_SUMSQ_LD + tile_a] =
+            ((exch[local] + exch[16 + local]) + exch[32 + local]) + exch[48 + local];
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// The q/k/v product's epilogue: bias, rotation of the query and key heads, queries to `out`, keys and
+// values into the paged cache (what llmb_rope_cache_write does in a kernel of its own). A head's values
+// lie in one tile (128 % head_dim == 0); pairs (p, p + head_dim/2) are exchanged through shared memory
+// (exch: 16 x 128 floats), interleaved pairs (2p, 2p+1) between neighbouring lanes.
+__device__ __forceinline__ void finish_rope(const Epilogue& ep, int a_row, int tile_row, int first_token, int valid,
+                                            float (&v)[16], float* exch) {
+    const llmb_gemm_fusion& f = ep.f;
+    int dim = f.head_dim, half = dim >> 1;
+    int head = a_row / dim, r = a_row - head * dim;
+    bool live = a_row < ep.outs;
+    float b = (ep.bias && live) ? ep.bias[a_row] : 0.f;
+    float partner[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] += b;
+    if (f.interleaved) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) partner[j] = __shfl_xor_sync(0xffffffffu, v[j], 1);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) exch[j * BM + tile_row] = v[j];
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        int other = r < half ? tile_row + half : tile_row - half;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) partner[j] = exch[j * BM + other];
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    if (!live) return;
+    bool is_q = head < f.n_heads, is_k = !is_q && head < f.n_heads + f.n_kv_heads;
+    bool rotates = f.rope_table != nullptr && (is_q || is_k);
+    bool low = f.interleaved ? (r & 1) == 0 : r < half;
+    int pair = f.interleaved ? r >> 1 : (r < half ? r : r - half);
+    __nv_bfloat16* q_out = reinterpret_cast<__nv_bfloat16*>(ep.out);
+    __nv_bfloat16* cache = reinterpret_cast<__nv_bfloat16*>(is_k ? f.k_cache : f.v_cache);
+    int kv_head = is_k ? head - f.n_heads : head - f.n_heads - f.n_kv_heads;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (j >= valid) break;
+        int token = first_token + j;
+        int pos = f.tok_pos[token];
+        float value = v[j];
+        if (rotates) {
+            float c = f.rope_table[(size_t)pos * dim + pair], s = f.rope_table[(size_t)pos * dim + half + pair];
+            value = low ? v[j] * c - partner[j] * s : partner[j] * s + v[j] * c;
+        }
+        if (is_q) {
+            q_out[(size_t)token * ep.ldo + a_row] = __float2bfloat16_rn(value);
+        } else if (f.write_cache) {
+            int page = f.block_table[(size_t)f.tok_seq[token] * f.table_stride + ((pos / LLMB_PAGE) % f.ring_pages)];
+            cache[(((size_t)page * f.n_kv_heads + kv_head) * LLMB_PAGE + (pos % LLMB_PAGE)) * dim + r] =
+                __float2bfloat16_rn(value);
+        }
+    }
+}
+
 // Persistent: the grid has at most as many blocks as fit on the GPU at once, and block b
 // takes the units b, b + gridDim.x, ... . The shared-memory ring and the two accumulator
 // buffers in tensor memory run on across units, so the loads and products of the next unit
@@ -217,6 +342,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+    float* exch = reinterpret_cast<float*>(tmem_slot + 4);      // the fused epilogues' exchange (sized by the host)
+    __shared__ float rstd_s[2][BM];                             // scales of a tile's token rows (a folded norm)
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     LLMB_STAMP(0, 0);                                           // the block has started
@@ -336,6 +463,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++n_done) {
             Unit w = unit_of(u, tiles_a, splits);
             uint32_t buffer = n_done & 1, use = n_done >> 1;
+            // a folded norm: the scales of this tile's token rows, computed while the products run
+            // (two buffers in turn and one barrier a unit: a warp that runs ahead writes the other one)
+            const float* rstd = nullptr;
+            if (ep.f.norm_sumsq) {
+                tile_rstd(ep, rstd_s[n_done & 1], (int)threadIdx.x - 64, swap ? w.tile_b * BN : w.tile_a * BM,
+                          swap ? (BN < BM ? BN : BM) : BM);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                rstd = rstd_s[n_done & 1];
+            }
             ok = mbar_wait(smem_u32(&acc_full_bar[buffer]), use & 1, abort_flag, status, 3);
             if (!ok) break;
             tcgen05_fence_after();
@@ -343,6 +479,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int a_row = w.tile_a * BM + row;             // swap: output column; else: token
             size_t tile_id = (size_t)w.tile_b * tiles_a + w.tile_a;
             if (splits == 1 && ep.glu && !swap) {
+                float r = rstd ? rstd[row] : 1.f;
                 // columns alternate 16 gate, 16 up: this thread's row gets 16 activations per pair
                 __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out);
 #pragma unroll 1
@@ -357,8 +494,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             h[j] = __floats2bfloat162_rn(
-                                silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(u[2 * j])),
-                                silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1])));
+                                silu_mul(__uint_as_float(g[2 * j]) * r, __uint_as_float(u[2 * j]) * r),
+                                silu_mul(__uint_as_float(g[2 * j + 1]) * r, __uint_as_float(u[2 * j + 1]) * r));
                         __nv_bfloat16* dst = o + (size_t)a_row * ep.ldo + n0 / 2;
                         if ((ep.ldo & 7) == 0) {
                             reinterpret_cast<uint4*>(dst)[0] = packed[0];
@@ -383,7 +520,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_ld16(taddr + c, r);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-                    store_columns<BN>(ep, swap, a_row, w.tile_b, c, v);
+                    store_columns<BN>(ep, swap, a_row, w.tile_b, c, v, nullptr, rstd, row);
                 }
                 tcgen05_fence_before();
                 __syncwarp();
@@ -433,6 +570,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         old[j] = j < valid ? ep.residual[(size_t)(w.tile_b * BN + c + j) * ep.ldo + a_row] : 0.f;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) old[j] = 0.f;
                 }
                 // Partials are added in split order. With at most 8 valid columns, 8 splits' loads
                 // are in flight at once (a decode step of up to 8 sequences sums 9 splits in two
@@ -468,7 +608,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (int j = 0; j < 16; ++j) v[j] += t[i][j];
                     }
                 }
-                store_columns<BN>(ep, swap, a_row, w.tile_b, c, v, preload ? old : nullptr);
+                if (swap && (ep.f.rope || ep.f.emit_rows)) {
+                    // the fused decode epilogues (tiles of 16 tokens: this loop runs once)
+                    if (rstd) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] *= rstd[c + j];
+                    }
+                    if (ep.f.rope) finish_rope(ep, a_row, row, w.tile_b * BN + c, valid, v, exch);
+                    else finish_emit(ep, a_row, w.tile_a, w.tile_b * BN + c, valid, v, old, exch);
+                } else {
+                    store_columns<BN>(ep, swap, a_row, w.tile_b, c, v, preload ? old : nullptr, rstd, row);
+                }
             }
             if (threadIdx.x == 64) counters[tile_id] = 0u;
             LLMB_STAMP(7, 64);                                      // the last arriver has summed and stored
@@ -490,42 +640,129 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // Sums the partial tiles of a swapped split-K product: one thread per (token, output feature),
-// the splits added in order, then bias / residual / store as the product's epilogue would.
+// the splits added in order, then scale / bias / residual / store as the product's epilogue would;
+// with a residual it can also leave the next norm's input (bfloat16 rows and one partial sum of
+// squares per block of 256 features).
 // Partials: [tile_b][tile_a][split][BN columns = tokens][128 rows = features].
+__device__ __forceinline__ float split_sum(const float* partials, int tiles_a, int splits, int bn, int token,
+                                           int weight_row) {
+    size_t tile_floats = (size_t)bn * BM;
+    int tile_a = weight_row / BM, row = weight_row % BM, tile_b = token / bn, col = token % bn;
+    const float* p = partials + ((size_t)tile_b * tiles_a + tile_a) * splits * tile_floats + (size_t)col * BM + row;
+    float v = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+        float t[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = s0 + i < splits ? __ldcg(p + (size_t)(s0 + i) * tile_floats) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v += t[i];
+    }
+    return v;
+}
+
 __global__ void __launch_bounds__(256)
 splitk_sum_kernel(const float* __restrict__ partials, Epilogue ep, int tiles_a, int splits, int bn) {
     griddep_launch();
     griddep_wait();
+    __shared__ float scale_s;
+    __shared__ float squares[8];
     int token = blockIdx.y;
     int feature = blockIdx.x * 256 + threadIdx.x;                  // with glu: the activated column
     int n_features = ep.glu ? ep.outs / 2 : ep.outs;
-    if (feature >= n_features) return;
-    size_t tile_floats = (size_t)bn * BM;
-    auto row_sum = [&](int weight_row) {
-        int tile_a = weight_row / BM, row = weight_row % BM, tile_b = token / bn, col = token % bn;
-        const float* p = partials + ((size_t)tile_b * tiles_a + tile_a) * splits * tile_floats + (size_t)col * BM + row;
-        float v = 0.f;
-        for (int s0 = 0; s0 < splits; s0 += 8) {
-            float t[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) t[i] = s0 + i < splits ? __ldcg(p + (size_t)(s0 + i) * tile_floats) : 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v += t[i];
-        }
-        return v;
-    };
-    if (ep.glu) {
-        // weight rows alternate 16 gate rows, 16 up rows
-        int gate_row = (feature / LLMB_GLU_BLOCK) * 2 * LLMB_GLU_BLOCK + feature % LLMB_GLU_BLOCK;
-        float gate = row_sum(gate_row), up = row_sum(gate_row + LLMB_GLU_BLOCK);
-        reinterpret_cast<__nv_bfloat16*>(ep.out)[(size_t)token * ep.ldo + feature] = __float2bfloat16_rn(silu_mul(gate, up));
-        return;
+    if (ep.f.norm_sumsq) {
+        if (threadIdx.x == 0) scale_s = row_rstd(ep.f, token);
+        __syncthreads();
     }
-    float v = row_sum(feature) + (ep.bias ? ep.bias[feature] : 0.f);
-    size_t at = (size_t)token * ep.ldo + feature;
-    if (ep.residual) ep.residual[at] = ep.residual[at] + v;
-    else if (ep.out_is_bf16) reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(v);
-    else reinterpret_cast<float*>(ep.out)[at] = v;
+    float scale = ep.f.norm_sumsq ? scale_s : 1.f;
+    float updated = 0.f;
+    if (feature < n_features) {
+        if (ep.glu) {
+            // weight rows alternate 16 gate rows, 16 up rows
+            int gate_row = (feature / LLMB_GLU_BLOCK) * 2 * LLMB_GLU_BLOCK + feature % LLMB_GLU_BLOCK;
+            float gate = split_sum(partials, tiles_a, splits, bn, token, gate_row) * scale;
+            float up = split_sum(partials, tiles_a, splits, bn, token, gate_row + LLMB_GLU_BLOCK) * scale;
+            reinterpret_cast<__nv_bfloat16*>(ep.out)[(size_t)token * ep.ldo + feature] = __float2bfloat16_rn(silu_mul(gate, up));
+        } else {
+            float v = split_sum(partials, tiles_a, splits, bn, token, feature) * scale + (ep.bias ? ep.bias[feature] : 0.f);
+            size_t at = (size_t)token * ep.ldo + feature;
+            if (ep.residual) {
+                updated = ep.residual[at] + v;
+                ep.residual[at] = updated;
+                if (ep.f.emit_rows) reinterpret_cast<__nv_bfloat16*>(ep.f.emit_rows)[at] = __float2bfloat16_rn(updated);
+            } else if (ep.out_is_bf16) {
+                reinterpret_cast<__nv_bfloat16*>(ep.out)[at] = __float2bfloat16_rn(v);
+            } else {
+                reinterpret_cast<float*>(ep.out)[at] = v;
+            }
+        }
+    }
+    if (ep.f.emit_sumsq) {                                          // uniform over the block
+        float sq = warp_sum(updated * updated);
+        if ((threadIdx.x & 31) == 0) squares[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float total = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) total += squares[i];
+            ep.f.emit_sumsq[(size_t)token * LLMB_SUMSQ_LD + blockIdx.x] = total;
+        }
+    }
+}
+
+// The same sum for the q/k/v product with the rotation and the cache write behind it (see finish_rope):
+// one thread per (token, item); an item is a rotation pair of a query or key head, or one value of a v head.
+__global__ void __launch_bounds__(256)
+splitk_sum_rope_kernel(const float* __restrict__ partials, Epilogue ep, int tiles_a, int splits, int bn) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float scale_s;
+    const llmb_gemm_fusion& f = ep.f;
+    int token = blockIdx.y;
+    int dim = f.head_dim, half = dim >> 1;
+    int n_pairs = (f.n_heads + f.n_kv_heads) * half;
+    int n_items = n_pairs + f.n_kv_heads * dim;
+    int item = blockIdx.x * 256 + threadIdx.x;
+    if (f.norm_sumsq) {
+        if (threadIdx.x == 0) scale_s = row_rstd(f, token);
+        __syncthreads();
+    }
+    float scale = f.norm_sumsq ? scale_s : 1.f;
+    if (item >= n_items) return;
+    int pos = f.tok_pos[token];
+    size_t cache_row = 0;
+    if (f.write_cache) {
+        int page = f.block_table[(size_t)f.tok_seq[token] * f.table_stride + ((pos / LLMB_PAGE) % f.ring_pages)];
+        cache_row = ((size_t)page * f.n_kv_heads) * LLMB_PAGE + (pos % LLMB_PAGE);      // + kv_head * 64, times dim
+    }
+    __nv_bfloat16* q_out = reinterpret_cast<__nv_bfloat16*>(ep.out) + (size_t)token * ep.ldo;
+    if (item < n_pairs) {
+        int head = item / half, pair = item - head * half;
+        int e0 = f.interleaved ? 2 * pair : pair, e1 = f.interleaved ? 2 * pair + 1 : pair + half;
+        int row0 = head * dim + e0, row1 = head * dim + e1;
+        float lo = split_sum(partials, tiles_a, splits, bn, token, row0) * scale + (ep.bias ? ep.bias[row0] : 0.f);
+        float hi = split_sum(partials, tiles_a, splits, bn, token, row1) * scale + (ep.bias ? ep.bias[row1] : 0.f);
+        if (f.rope_table) {
+            float c = f.rope_table[(size_t)pos * dim + pair], s = f.rope_table[(size_t)pos * dim + half + pair];
+            float a = lo * c - hi * s, b = lo * s + hi * c;
+            lo = a;
+            hi = b;
+        }
+        if (head < f.n_heads) {
+            q_out[row0] = __float2bfloat16_rn(lo);
+            q_out[row1] = __float2bfloat16_rn(hi);
+        } else if (f.write_cache) {
+            __nv_bfloat16* k = reinterpret_cast<__nv_bfloat16*>(f.k_cache) +
+                               (cache_row + (size_t)(head - f.n_heads) * LLMB_PAGE) * dim;
+            k[e0] = __float2bfloat16_rn(lo);
+            k[e1] = __float2bfloat16_rn(hi);
+        }
+    } else if (f.write_cache) {
+        int rest = item - n_pairs;
+        int kv_head = rest / dim, e = rest - kv_head * dim;
+        int row = (f.n_heads + f.n_kv_heads + kv_head) * dim + e;
+        float v = split_sum(partials, tiles_a, splits, bn, token, row) * scale + (ep.bias ? ep.bias[row] : 0.f);
+        reinterpret_cast<__nv_bfloat16*>(f.v_cache)[(cache_row + (size_t)kv_head * LLMB_PAGE) * dim + e] = __float2bfloat16_rn(v);
+    }
 }
 
 // ------------------------------------------------------------------------- two SMs on one tile
@@ -599,6 +836,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* acc_empty_bar = bars + 2 * stages + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    __shared__ float rstd_s[2][BM];                   // scales of this block's 128 token rows (a folded norm)
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t rank = cluster_rank();
@@ -707,12 +945,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int u = pair; u < n_units && ok; u += n_pairs, ++n_done) {
             Unit w = unit_of(u, tiles_a, 1);
             uint32_t buffer = n_done & 1, use = n_done >> 1;
+            const float* rstd = nullptr;
+            if (ep.f.norm_sumsq) {                    // as in gemm_tc_kernel: while the products run
+                tile_rstd(ep, rstd_s[n_done & 1], (int)threadIdx.x - 64, w.tile_a * 2 * BM + (int)rank * BM, BM);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                rstd = rstd_s[n_done & 1];
+            }
             ok = mbar_wait(smem_u32(&acc_full_bar[buffer]), use & 1, abort_flag, status, 3);
             if (!ok) break;
             tcgen05_fence_after();
             uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * PAIR_BN;
             int a_row = w.tile_a * 2 * BM + (int)rank * BM + row;
             if (ep.glu) {
+                float r = rstd ? rstd[row] : 1.f;
                 __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(ep.out);
 #pragma unroll 1
                 for (int c = 0; c < PAIR_BN; c += 32) {
@@ -726,8 +971,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             h[j] = __floats2bfloat162_rn(
-                                silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(uu[2 * j])),
-                                silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(uu[2 * j + 1])));
+                                silu_mul(__uint_as_float(g[2 * j]) * r, __uint_as_float(uu[2 * j]) * r),
+                                silu_mul(__uint_as_float(g[2 * j + 1]) * r, __uint_as_float(uu[2 * j + 1]) * r));
                         __nv_bfloat16* dst = o + (size_t)a_row * ep.ldo + n0 / 2;
                         if ((ep.ldo & 7) == 0) {
                             reinterpret_cast<uint4*>(dst)[0] = packed[0];
@@ -747,7 +992,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld16(taddr + c, r);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-                    store_columns<PAIR_BN>(ep, 0, a_row, w.tile_b, c, v);
+                    store_columns<PAIR_BN>(ep, 0, a_row, w.tile_b, c, v, nullptr, rstd, row);
                 }
             }
             tcgen05_fence_before();
@@ -789,12 +1034,16 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
     int stages = (200 * 1024) / (A_BYTES + B_BYTES);
     if (stages > 8) stages = 8;
     int blocks_per_sm = 1;
+    // the fused decode epilogues exchange values through shared memory behind the control words:
+    // 64 floats for the sums of squares, 16 x 128 for rotation pairs that sit half a head apart
+    size_t exchange = 256;
+    if (swap && BN == 16 && splits > 1 && ep.f.rope && !ep.f.interleaved) exchange = (size_t)16 * BM * 4;
     if (swap) {                                         // two blocks per SM for the decode stream
-        stages = (110 * 1024) / (A_BYTES + B_BYTES);
+        stages = (int)((110 * 1024 - (exchange > 256 ? exchange : 0)) / (A_BYTES + B_BYTES));
         if (stages > 6) stages = 6;
         blocks_per_sm = 2;
     }
-    size_t smem = 1024 + (size_t)stages * (A_BYTES + B_BYTES) + (2 * stages + 4) * 8 + 16;
+    size_t smem = 1024 + (size_t)stages * (A_BYTES + B_BYTES) + (2 * stages + 4) * 8 + 16 + exchange;
     static size_t configured = 0;
     if (smem > configured) {
         LLMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -816,6 +1065,12 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
                  splits, tiles_a, n_units, partials, counters, status_dev, stages, sum_later);
     int code = check_launch("gemm_tc");
     if (code || !sum_later) return code;
+    if (ep.f.rope) {
+        int n_items = (ep.f.n_heads + ep.f.n_kv_heads) * (ep.f.head_dim / 2) + ep.f.n_kv_heads * ep.f.head_dim;
+        llmb::launch(splitk_sum_rope_kernel, dim3((n_items + 255) / 256, ep.tokens), 256, 0, stream, true,
+                     (const float*)partials, ep, tiles_a, splits, BN);
+        return check_launch("gemm_tc (split-K sum with rotation)");
+    }
     int n_features = ep.glu ? ep.outs / 2 : ep.outs;
     llmb::launch(splitk_sum_kernel, dim3((n_features + 255) / 256, ep.tokens), 256, 0, stream, true,
                  (const float*)partials, ep, tiles_a, splits, BN);
@@ -921,14 +1176,35 @@ LLMB_EXPORT int llmb_gemm_tc_kernels(int M, int N, int K) {
     return 1 + sums_later(p.swap, p.splits, p.bn);
 }
 
+// Partial sums of squares per row that a call with emit_rows / emit_sumsq writes inside its kernels
+// (0: the shape's kernels do not, and the caller runs llmb_cast_sumsq behind the product).
+LLMB_EXPORT int llmb_gemm_tc_emit_parts(int M, int N, int K) {
+    Plan p = make_plan(M, N, K);
+    if (!p.swap || p.splits <= 1) return 0;
+    int parts = sums_later(p.swap, p.splits, p.bn) ? (N + 255) / 256 : p.tiles_a;
+    return parts <= LLMB_SUMSQ_LD ? parts : 0;
+}
+
+// Whether a call with `rope` rotates and writes the cache inside its kernels.
+LLMB_EXPORT int llmb_gemm_tc_fuses_rope(int M, int N, int K, int n_heads, int n_kv_heads, int head_dim) {
+    Plan p = make_plan(M, N, K);
+    return p.swap && p.splits > 1 && head_dim >= 2 && head_dim % 2 == 0 && BM % head_dim == 0 &&
+           (long long)(n_heads + 2 * n_kv_heads) * head_dim == N;
+}
+
 // out[M, N] = x[M, K] . w[N, K]^T (+ bias[N]); or residual[M, N] += the same.
 // allow_pair != 0: products with more than 128 rows run 256 x 256 tiles on pairs of SMs.
 // glu != 0: w holds gate and up rows alternating in blocks of 16 (N = 2 F rows, N % 32 == 0) and
 // out is bfloat16 [M, ldo] with F columns silu(gate) * up; no bias, no residual.
-LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
-                             int out_dtype, float* residual, float* partials, long long partial_floats,
-                             unsigned* counters, int n_counters, int M, int N, int K, int ldo, int glu,
-                             int allow_pair, cudaStream_t stream) {
+// fusion (optional): see fusion.h. *applied (optional) tells which parts ran inside the kernels:
+// a folded norm always does; the rows and sums for the next norm and the rotation with the cache
+// write only where the shape's kernels have them, else the caller runs them as kernels of their own.
+LLMB_EXPORT int llmb_gemm_tc_ex(const void* x, int ldx, const void* w, const float* bias, void* out,
+                                int out_dtype, float* residual, float* partials, long long partial_floats,
+                                unsigned* counters, int n_counters, int M, int N, int K, int ldo, int glu,
+                                int allow_pair, const llmb_gemm_fusion* fusion, int* applied,
+                                cudaStream_t stream) {
+    if (applied) *applied = 0;
     if (M == 0 || N == 0) return LLMB_OK;
     LLMB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes");
     LLMB_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
@@ -950,13 +1226,39 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
         LLMB_REQUIRE(partials && counters && partial_floats >= llmb_gemm_tc_scratch_floats(M, N, K) &&
                      n_counters >= p.tiles_a * p.tiles_b, "gemm_tc: scratch is missing or too small");
     }
+    Epilogue ep{bias, out, residual, out_dtype == LLMB_DTYPE_BF16, ldo, M, N, glu != 0, {}};
+    int did = 0;
+    if (fusion) {
+        llmb_gemm_fusion f = *fusion;
+        if (f.norm_sumsq) {
+            LLMB_REQUIRE(f.norm_parts >= 1 && f.norm_parts <= LLMB_SUMSQ_LD && f.norm_width > 0.f,
+                         "gemm_tc: a folded norm needs 1 to %d partial sums a row", LLMB_SUMSQ_LD);
+            did |= LLMB_FUSED_NORM;
+        } else {
+            f.norm_parts = 0;
+        }
+        if (f.emit_rows && f.emit_sumsq && residual && llmb_gemm_tc_emit_parts(M, N, K) > 0) {
+            did |= LLMB_FUSED_EMIT;
+        } else {
+            f.emit_rows = nullptr;
+            f.emit_sumsq = nullptr;
+        }
+        if (f.rope) {
+            LLMB_REQUIRE(out && out_dtype == LLMB_DTYPE_BF16 && !glu && !residual && f.tok_pos && f.tok_seq &&
+                         f.block_table && f.k_cache && f.v_cache && f.ring_pages > 0,
+                         "gemm_tc: the rotation needs a bfloat16 output, positions, a page table and the cache");
+            if (llmb_gemm_tc_fuses_rope(M, N, K, f.n_heads, f.n_kv_heads, f.head_dim)) did |= LLMB_FUSED_ROPE;
+            else f.rope = 0;
+        }
+        ep.f = f;
+    }
+    if (applied) *applied = did;
     CUtensorMap map_a, map_b;
     int code;
     if (allow_pair && !p.swap && M > 128 && N >= 256) {
         // 256 x 256 tiles over pairs of SMs; each block's boxes are 128 rows
         if ((code = make_map(&map_a, x, M, K, ldx, BM))) return code;
         if ((code = make_map(&map_b, w, N, K, K, PAIR_BN / 2))) return code;
-        Epilogue ep{bias, out, residual, out_dtype == LLMB_DTYPE_BF16, ldo, M, N, glu != 0};
         return launch_pair(map_a, map_b, ep, (M + 2 * BM - 1) / (2 * BM), (N + PAIR_BN - 1) / PAIR_BN,
                            p.n_kblocks, stream);
     }
@@ -967,7 +1269,6 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
         if ((code = make_map(&map_a, x, M, K, ldx, BM))) return code;
         if ((code = make_map(&map_b, w, N, K, K, p.bn))) return code;
     }
-    Epilogue ep{bias, out, residual, out_dtype == LLMB_DTYPE_BF16, ldo, M, N, glu != 0};
 #define GO(BN) return launch<BN>(map_a, map_b, ep, p.swap, p.tiles_a, p.tiles_b, p.n_kblocks, \
                                  p.per_split, p.splits, partials, counters, stream)
     switch (p.bn) {
@@ -978,4 +1279,12 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
         default: GO(256);
     }
 #undef GO
+}
+
+LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float* bias, void* out,
+                             int out_dtype, float* residual, float* partials, long long partial_floats,
+                             unsigned* counters, int n_counters, int M, int N, int K, int ldo, int glu,
+                             int allow_pair, cudaStream_t stream) {
+    return llmb_gemm_tc_ex(x, ldx, w, bias, out, out_dtype, residual, partials, partial_floats, counters,
+                           n_counters, M, N, K, ldo, glu, allow_pair, nullptr, nullptr, stream);
 }

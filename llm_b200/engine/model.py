@@ -152,10 +152,30 @@ class DecoderModel:
     def forward(self, tokens, ctx, logit_rows):
         """tokens int32 [T] on the device; logit_rows int32 [R]: packed token
         indices whose logits are wanted. Returns float32 [R, vocab]."""
-        x = ops.embed(tokens, self.embedding, scale=getattr(self.spec, "embedding_scale", 1.0))
-        for entry, item in enumerate(self.spec.schedule):
+        # A block that folds its first norm into the product behind it (PreNormBlock in bfloat16)
+        # reads that norm's input from where the last update of x left it: the embedding leaves it
+        # for the first block, every block's last product for the block that runs next.
+        schedule = self.spec.schedule
+        n = tokens.numel()
+
+        def wanted_by(position):
+            if position >= len(schedule):
+                return None
+            block = self.blocks[schedule[position].layer]
+            return block.input_emit(ctx, n, self.device) if getattr(block, "chains_norms", False) else None
+
+        emit = wanted_by(0)
+        x = ops.embed(tokens, self.embedding, scale=getattr(self.spec, "embedding_scale", 1.0), emit=emit)
+        for entry, item in enumerate(schedule):
             cache_entry = entry if item.cache_of is None else item.cache_of
-            self.blocks[item.layer].forward(x, ctx, entry, cache_entry)
+            block = self.blocks[item.layer]
+            if getattr(block, "chains_norms", False):
+                emit_next = wanted_by(entry + 1)
+                block.forward(x, ctx, entry, cache_entry, normed=emit, emit_next=emit_next)
+                emit = emit_next
+            else:
+                block.forward(x, ctx, entry, cache_entry)
+                emit = None
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=x.device)
         z = self.final_norm.forward(x, ctx.dtype, rows=logit_rows)

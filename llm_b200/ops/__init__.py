@@ -135,16 +135,93 @@ def _call(lib_name: str, fn_name: str, *args, kernels: int = 1):
 
 # ----------------------------------------------------------------------------- row-wise
 
-def embed(tokens, table, out=None, scale: float = 1.0):
-    """x[t, :] = table[tokens[t], :] * scale as float32 [T, hidden]."""
+def embed(tokens, table, out=None, scale: float = 1.0, emit=None):
+    """x[t, :] = table[tokens[t], :] * scale as float32 [T, hidden]. With `emit` (an Emit) the
+    rows are also written as bfloat16 with the sum of their squares: the first norm's input."""
     _require_cuda(tokens, table)
     n, (vocab, hidden) = tokens.numel(), table.shape
     _check_out(out, (n, hidden), torch.float32, "embed")
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    if emit is not None:
+        emit.check(n, hidden)
+        emit.parts = 1
     _call("elementwise", "llmb_embed", _ptr(tokens), _ptr(table), _c_int(_code(table.dtype)),
-          _ptr(out), _c_int(n), _c_int(hidden), _c_int(vocab), _c_float(scale), _stream())
+          _ptr(out), _c_int(n), _c_int(hidden), _c_int(vocab), _c_float(scale),
+          _ptr(emit.rows) if emit is not None else None, _ptr(emit.sumsq) if emit is not None else None,
+          _stream())
     return out
+
+
+SUMSQ_LD = 64          # floats per row of a sum-of-squares array (LLMB_SUMSQ_LD of csrc/fusion.h)
+
+
+class Emit:
+    """Where a product that adds into the residual stream (or the embedding) leaves the next
+    norm's input: `rows` bfloat16 [T, hidden], the updated residual rows, and `sumsq` float32
+    [T, 64], partial sums of their squares; `parts` says how many of the 64 are in use (set by
+    the op that wrote them)."""
+    __slots__ = ("rows", "sumsq", "parts")
+
+    def __init__(self, rows, sumsq):
+        self.rows, self.sumsq, self.parts = rows, sumsq, 0
+
+    def check(self, n: int, width: int) -> None:
+        _require_cuda(self.rows, self.sumsq)
+        if (tuple(self.rows.shape) != (n, width) or self.rows.dtype != torch.bfloat16 or not self.rows.is_contiguous()
+                or tuple(self.sumsq.shape) != (n, SUMSQ_LD) or self.sumsq.dtype != torch.float32
+                or not self.sumsq.is_contiguous()):
+            raise KernelError(f"emit: rows must be contiguous bfloat16 [{n}, {width}] and sumsq float32 "
+                              f"[{n}, {SUMSQ_LD}]")
+
+
+class FoldedNorm:
+    """The input of a product whose norm is folded into it: `rows` are the un-normalised rows as
+    bfloat16, the norm's gain is already multiplied into the weight's columns, and the product
+    scales result row t by 1 / sqrt(sum(sumsq[t, :parts]) / width + eps)."""
+    __slots__ = ("rows", "sumsq", "parts", "eps", "width")
+
+    def __init__(self, rows, sumsq, parts: int, eps: float, width: int):
+        self.rows, self.sumsq, self.parts, self.eps, self.width = rows, sumsq, parts, eps, width
+
+
+class RopeWrite:
+    """The rotation and cache write behind the q/k/v product (the arguments of rope_cache_write)."""
+    __slots__ = ("table", "tok_pos", "tok_seq", "block_table", "ring_pages", "k_cache", "v_cache",
+                 "n_heads", "n_kv_heads", "head_dim", "interleaved", "write_cache")
+
+    def __init__(self, table, tok_pos, tok_seq, block_table, ring_pages, k_cache, v_cache, n_heads,
+                 n_kv_heads, head_dim, interleaved=False, write_cache=True):
+        self.table, self.tok_pos, self.tok_seq, self.block_table = table, tok_pos, tok_seq, block_table
+        self.ring_pages, self.k_cache, self.v_cache = ring_pages, k_cache, v_cache
+        self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
+        self.interleaved, self.write_cache = interleaved, write_cache
+
+
+class _Fusion(ctypes.Structure):
+    """llmb_gemm_fusion of csrc/fusion.h."""
+    _fields_ = [("norm_sumsq", ctypes.c_void_p), ("norm_parts", ctypes.c_int), ("norm_eps", ctypes.c_float),
+                ("norm_width", ctypes.c_float), ("emit_rows", ctypes.c_void_p), ("emit_sumsq", ctypes.c_void_p),
+                ("rope", ctypes.c_int), ("interleaved", ctypes.c_int), ("write_cache", ctypes.c_int),
+                ("n_heads", ctypes.c_int), ("n_kv_heads", ctypes.c_int), ("head_dim", ctypes.c_int),
+                ("rope_table", ctypes.c_void_p), ("tok_pos", ctypes.c_void_p), ("tok_seq", ctypes.c_void_p),
+                ("block_table", ctypes.c_void_p), ("table_stride", ctypes.c_int), ("ring_pages", ctypes.c_int),
+                ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p)]
+
+
+FUSED_NORM, FUSED_EMIT, FUSED_ROPE = 1, 2, 4
+
+
+def cast_sumsq(x, emit: Emit):
+    """emit.rows = bfloat16(x), emit.sumsq[:, 0] = the rows' sums of squares (x float32 [T, hidden])."""
+    _require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("cast_sumsq: x must be contiguous float32")
+    emit.check(x.shape[0], x.shape[1])
+    _call("elementwise", "llmb_cast_sumsq", _ptr(x), _ptr(emit.rows), _ptr(emit.sumsq), _c_int(x.shape[0]),
+          _c_int(x.shape[1]), _stream())
+    emit.parts = 1
+    return emit
 
 
 def random_normal_(out, key: int, mean: float, deviation: float):
@@ -296,14 +373,59 @@ def _tc_kernels(m: int, n: int, k: int) -> int:
     return _tc_needs(m, n, k)[2]
 
 
-def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
+def _fusion_struct(norm, emit, rope):
+    f = _Fusion()
+    if norm is not None:
+        f.norm_sumsq, f.norm_parts = norm.sumsq.data_ptr(), norm.parts
+        f.norm_eps, f.norm_width = norm.eps, float(norm.width)
+    if emit is not None:
+        f.emit_rows, f.emit_sumsq = emit.rows.data_ptr(), emit.sumsq.data_ptr()
+    if rope is not None:
+        f.rope, f.interleaved, f.write_cache = 1, int(bool(rope.interleaved)), int(bool(rope.write_cache))
+        f.n_heads, f.n_kv_heads, f.head_dim = rope.n_heads, rope.n_kv_heads, rope.head_dim
+        f.rope_table = rope.table.data_ptr() if rope.table is not None else None
+        f.tok_pos, f.tok_seq = rope.tok_pos.data_ptr(), rope.tok_seq.data_ptr()
+        f.block_table, f.table_stride = rope.block_table.data_ptr(), rope.block_table.shape[1]
+        f.ring_pages, f.k_cache, f.v_cache = rope.ring_pages, rope.k_cache.data_ptr(), rope.v_cache.data_ptr()
+    return f
+
+
+@functools.lru_cache(maxsize=4096)
+def _tc_emit_parts(m: int, n: int, k: int) -> int:
+    return load_library("gemm_tc").llmb_gemm_tc_emit_parts(_c_int(m), _c_int(n), _c_int(k))
+
+
+def _check_norm(norm, m, k):
+    if (norm.sumsq.dtype != torch.float32 or tuple(norm.sumsq.shape) != (m, SUMSQ_LD)
+            or not norm.sumsq.is_contiguous() or not 1 <= norm.parts <= SUMSQ_LD):
+        raise KernelError(f"linear: a folded norm needs sums of squares as contiguous float32 [{m}, {SUMSQ_LD}] "
+                          f"with 1 to {SUMSQ_LD} parts in use")
+
+
+def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False, norm=None, emit=None,
+           rope=None):
     """a [M, K] . w [N, K]^T (+ bias [N], float32). With `residual` (float32
     [M, N]) the product is added to it in place and it is returned; otherwise a
     new [M, N] tensor of `out_dtype` (default: a's dtype). With `glu`, w holds
     gate and up rows alternating in blocks of 16 and the result is
-    silu(gate) * up as [M, N / 2] in a's dtype, computed in the product's epilogue."""
+    silu(gate) * up as [M, N / 2] in a's dtype, computed in the product's epilogue.
+
+    What can ride along (bfloat16; where the shape's kernel does not have it, a kernel of its
+    own runs behind the product, with the same result):
+    `norm` (FoldedNorm): a holds un-normalised rows, w has the norm's gain folded in, and the
+    rows of the result are scaled by the norm's 1 / sqrt(mean square + eps) before the bias.
+    `emit` (Emit, with `residual`): the updated residual rows as bfloat16 and the partial sums
+    of their squares, for the next norm. `rope` (RopeWrite): the result is the q/k/v projection;
+    queries and keys are rotated, queries stay in the result, keys and values go to the cache."""
     _require_cuda(a, w, bias, residual)
     (m, k), (n, k2) = a.shape, w.shape
+    if norm is not None:
+        _check_norm(norm, m, k)
+    if emit is not None:
+        if residual is None:
+            raise KernelError("linear: emit needs a residual")
+        emit.check(m, n)
+    fused = norm is not None or emit is not None or rope is not None
     if glu:
         if not glu_fusable(n, k, a.dtype) or bias is not None or residual is not None or a.stride(0) % 8:
             raise KernelError("linear: the gated epilogue needs bfloat16, 2 F rows with F % 16 == 0, "
@@ -311,10 +433,13 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
         _check_out(out, (m, n // 2), a.dtype, "linear")
         result = out if out is not None else torch.empty((m, n // 2), dtype=a.dtype, device=a.device)
         partials, counters = _tc_scratch(a.device, m, n, k)
-        _call("gemm_tc", "llmb_gemm_tc", _ptr(a), _c_int(a.stride(0)), _ptr(w), None, _ptr(result),
+        if emit is not None or rope is not None:
+            raise KernelError("linear: the gated epilogue takes a folded norm only")
+        _call("gemm_tc", "llmb_gemm_tc_ex", _ptr(a), _c_int(a.stride(0)), _ptr(w), None, _ptr(result),
               _c_int(_code(a.dtype)), None, _ptr(partials), ctypes.c_longlong(partials.numel()),
               _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k),
               _c_int(n // 2), _c_int(1), _c_int(0 if tactics.is_disabled("gemm_tc_pair") else 1),
+              ctypes.byref(_fusion_struct(norm, None, None)) if norm is not None else None, None,
               _stream(), kernels=_tc_kernels(m, n, k))
         return result
     if k != k2 or a.dtype != w.dtype:
@@ -331,6 +456,44 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
         result = out if out is not None else torch.empty((m, n), dtype=target_dtype, device=a.device)
     variant = tactics.choose_linear(m, n, k, a.dtype, target_dtype, a.stride(0),
                                     a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+    if fused and a.dtype != torch.bfloat16:
+        raise KernelError("linear: norm, emit and rope ride only with bfloat16 products")
+    if variant == "gemm_tc" and fused:
+        partials, counters = _tc_scratch(a.device, m, n, k)
+        applied = _c_int(0)
+        _call("gemm_tc", "llmb_gemm_tc_ex", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),
+              _ptr(result if residual is None else None), _c_int(_code(target_dtype)),
+              _ptr(residual), _ptr(partials), ctypes.c_longlong(partials.numel()),
+              _ptr(counters), _c_int(counters.numel()), _c_int(m), _c_int(n), _c_int(k), _c_int(n),
+              _c_int(0), _c_int(0 if tactics.is_disabled("gemm_tc_pair") else 1),
+              ctypes.byref(_fusion_struct(norm, emit, rope)), ctypes.byref(applied), _stream(),
+              kernels=_tc_kernels(m, n, k))
+        if emit is not None:
+            if applied.value & FUSED_EMIT:
+                emit.parts = _tc_emit_parts(m, n, k)
+            else:
+                cast_sumsq(residual, emit)
+        if rope is not None and not applied.value & FUSED_ROPE:
+            rope_cache_write(result, rope.table, rope.tok_pos, rope.tok_seq, rope.block_table, rope.ring_pages,
+                             rope.k_cache, rope.v_cache, rope.n_heads, rope.n_kv_heads, rope.head_dim,
+                             rope.interleaved, rope.write_cache)
+        return result
+    if fused:
+        # a variant without the fused epilogues: the plain product, then each part as its own kernel
+        if norm is not None and residual is not None:
+            raise KernelError("linear: a folded norm with a residual has no kernel")
+        result = linear(a, w, None if norm is not None else bias, out_dtype, residual, out)
+        if norm is not None:
+            _call("elementwise", "llmb_scale_rows", _ptr(result), _c_int(_code(result.dtype)), _c_int(m), _c_int(n),
+                  _ptr(norm.sumsq), _c_int(norm.parts), _c_float(norm.eps), _c_float(float(norm.width)),
+                  _ptr(bias), _stream())
+        if emit is not None:
+            cast_sumsq(residual, emit)
+        if rope is not None:
+            rope_cache_write(result, rope.table, rope.tok_pos, rope.tok_seq, rope.block_table, rope.ring_pages,
+                             rope.k_cache, rope.v_cache, rope.n_heads, rope.n_kv_heads, rope.head_dim,
+                             rope.interleaved, rope.write_cache)
+        return result
     if variant == "gemm_tc":
         partials, counters = _tc_scratch(a.device, m, n, k)
         _call("gemm_tc", "llmb_gemm_tc", _ptr(a), _c_int(a.stride(0)), _ptr(w), _ptr(bias),
@@ -426,19 +589,21 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
         lib.llmb_attention_decode_scratch_floats.restype = ctypes.c_longlong
         need = lib.llmb_attention_decode_scratch_floats(_c_int(n), _c_int(n_heads), _c_int(head_dim),
                                                         _c_int(splits))
-        scratch = _attention_scratch.get(qkv.device)
-        if scratch is None or scratch.numel() < need:
-            if scratch is not None:
-                _retired.append(scratch)
-            scratch = torch.empty(max(need, 1 << 23), dtype=torch.float32, device=qkv.device)
-            _attention_scratch[qkv.device] = scratch
+        held = _attention_scratch.get(qkv.device)
+        if held is None or held[0].numel() < need or held[1].numel() < n * n_kv_heads:
+            if held is not None:
+                _retired.append(held)
+            # partial results, and one counter per (sequence, kv head) that is zero between calls
+            held = (torch.empty(max(need, 1 << 23), dtype=torch.float32, device=qkv.device),
+                    torch.zeros(max(n * n_kv_heads, 1 << 14), dtype=torch.int32, device=qkv.device))
+            _attention_scratch[qkv.device] = held
+        scratch, counters = held
         _call("attention_decode", "llmb_attention_decode", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
               _c_int(ring_pages), _ptr(seq_lens), _ptr(seq_order), _ptr(out), _c_int(out.stride(0)),
-              _ptr(scratch),
-              ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
-              _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream(),
-              kernels=2 if splits > 1 else 1)
+              _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters), _c_int(counters.numel()),
+              _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
+              _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream())
     elif variant == "attention_generic":
         _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
@@ -487,6 +652,6 @@ def required_libraries() -> list:
             "attention_decode", "attention_prefill", "attention_prefill_tc", "sampling"]
 
 
-__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
+__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

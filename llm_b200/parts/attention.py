@@ -16,6 +16,7 @@ class AttentionMixer(Mixer):
     of MythEclipse/llm (apps/engine/src/model.rs:930-1040), with the sizes, the
     scale, the window, the biases and the position encoding as parameters."""
     graph_safe = True
+    emits = True
     libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic", "attention_decode", "attention_prefill", "attention_prefill_tc")
 
     def __init__(self, spec):
@@ -52,6 +53,14 @@ class AttentionMixer(Mixer):
             self.b_qkv = torch.cat([to_float32(tensors[t[r + "_bias"]], device) for r in ("q", "k", "v")])
             self.b_o = to_float32(tensors[t["o_bias"]], device)
 
+    def fold_input_norm(self, gain):
+        """bfloat16 runs: the gain goes into the columns of the q/k/v matrix (in 32-bit, rounded
+        once), and the product's epilogue applies the norm's scale (ops.linear with `norm`)."""
+        if self.w_qkv.dtype != torch.bfloat16 or self.spec.hidden % 8:
+            return False
+        self.w_qkv = (self.w_qkv.float() * gain.to(self.w_qkv.device)[None, :]).to(torch.bfloat16).contiguous()
+        return True
+
     def prepare(self, max_positions, device):
         if self.position is not None:
             self.position.prepare(max_positions, device)
@@ -81,26 +90,35 @@ class AttentionMixer(Mixer):
     def kv_request(self):
         return KvRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
 
-    def forward(self, h, ctx, entry, cache_entry, residual):
+    def forward(self, h, ctx, entry, cache_entry, residual, emit=None):
         s = self.spec
         group, keys, values = ctx.cache.layer_view(cache_entry)
         table = ctx.block_tables[group]
         ring = ctx.cache.table_width(group)
+        norm = h if isinstance(h, ops.FoldedNorm) else None
+        if norm is not None:
+            h = norm.rows
         n = h.shape[0]
-        qkv = ops.linear(h, self.w_qkv, self.b_qkv,
-                         out=ctx.scratch("qkv", (n, self.q_width + 2 * self.kv_width), h.dtype))
-        ops.rope_cache_write(
-            qkv, self.position.table if self.position is not None else None, ctx.tok_pos,
-            ctx.tok_seq, table, ring, keys, values, s.n_heads, s.n_kv_heads, s.head_dim,
-            interleaved=self.position.interleaved if self.position is not None else False,
-            write_cache=(entry == cache_entry))
+        angles = self.position.table if self.position is not None else None
+        interleaved = self.position.interleaved if self.position is not None else False
+        out = ctx.scratch("qkv", (n, self.q_width + 2 * self.kv_width), h.dtype)
+        if h.dtype == torch.bfloat16 and (angles is None or angles.shape[1] == s.head_dim):
+            # the rotation and the cache write ride in the product's epilogue where its kernel has them
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv, out=out, norm=norm, rope=ops.RopeWrite(
+                angles, ctx.tok_pos, ctx.tok_seq, table, ring, keys, values, s.n_heads, s.n_kv_heads,
+                s.head_dim, interleaved, entry == cache_entry))
+        else:
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv, out=out, norm=norm)
+            ops.rope_cache_write(qkv, angles, ctx.tok_pos, ctx.tok_seq, table, ring, keys, values, s.n_heads,
+                                 s.n_kv_heads, s.head_dim, interleaved=interleaved,
+                                 write_cache=(entry == cache_entry))
         mixed = ops.attention(qkv, keys, values, table, ring, ctx.tok_pos, ctx.tok_seq, s.n_heads,
                               s.n_kv_heads, s.head_dim, s.scale, s.window, out=ctx.scratch("mixed", (n, self.q_width), h.dtype),
                               decode=ctx.decode,
                               seq_lens=ctx.seq_lens, max_len=ctx.max_len,
                               cu_seqlens=ctx.cu_seqlens, max_new=max(ctx.new_counts),
                               seq_order=ctx.seq_order)
-        ops.linear(mixed, self.w_o, self.b_o, residual=residual)
+        ops.linear(mixed, self.w_o, self.b_o, residual=residual, emit=emit)
 
 
 register_mixer("attention", AttentionMixer)

@@ -61,9 +61,23 @@ class Part:
     #: can be captured in a CUDA graph and replayed
     graph_safe: bool = False
 
+    #: True if `forward` takes `emit=` (an ops.Emit, or None) and then leaves, together with its
+    #: update of the residual stream, the next norm's input there (bfloat16 rows and their sums of
+    #: squares); a block runs ops.cast_sumsq behind parts that do not
+    emits: bool = False
+
     def parameters(self) -> dict:
         """tensor name -> ParamSpec of everything this part binds."""
         return {}
+
+    def fold_input_norm(self, gain) -> bool:
+        """Offered by the block after `bind`, where the norm in front of this part is an RMS norm
+        (y = x / sqrt(mean(x^2) + eps) * gain): take `gain` (float32 [hidden]) into the weights
+        that read the part's input and answer True. `forward` then receives an ops.FoldedNorm (the
+        un-normalised rows as bfloat16, their sums of squares, eps) instead of normalised rows, and
+        scales by the norm's factor itself: y . W^T = rstd(x) * (x . (gain * W)^T). The default
+        keeps the norm as a kernel of its own."""
+        return False
 
     def kernel_shapes(self, dtype, token_counts) -> list:
         """(label, family, chooser arguments) of the kernel choices this part's forward pass makes

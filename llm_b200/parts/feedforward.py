@@ -13,6 +13,7 @@ class GatedMlp(FeedForward):
     """down(silu(gate h) * (up h)) added to the residual stream, gate and up as
     one matrix product (apps/engine/src/model.rs:1180-1216 of MythEclipse/llm)."""
     graph_safe = True
+    emits = True
     libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc")
 
     def __init__(self, spec):
@@ -43,6 +44,13 @@ class GatedMlp(FeedForward):
             self.w_gate_up = torch.cat([gate, up])
         self.w_down = to_run_dtype(tensors[t["down"]], dtype, device)
 
+    def fold_input_norm(self, gain):
+        """bfloat16 runs: the gain goes into the columns of the gate and up matrix."""
+        if self.w_gate_up.dtype != torch.bfloat16 or self.spec.hidden % 8:
+            return False
+        self.w_gate_up = (self.w_gate_up.float() * gain.to(self.w_gate_up.device)[None, :]).to(torch.bfloat16).contiguous()
+        return True
+
     def kernel_shapes(self, dtype, token_counts):
         s, out = self.spec, []
         for n in token_counts:
@@ -62,14 +70,17 @@ class GatedMlp(FeedForward):
             return [act]
         return [BufferRequest("gate_up", (n_tokens, 2 * s.intermediate), dtype, 0, 1), act]
 
-    def forward(self, h, ctx, residual):
+    def forward(self, h, ctx, residual, emit=None):
+        norm = h if isinstance(h, ops.FoldedNorm) else None
+        if norm is not None:
+            h = norm.rows
         n, width = h.shape[0], self.spec.intermediate
         if self.fused:
-            act = ops.linear(h, self.w_gate_up, glu=True, out=ctx.scratch("act", (n, width), h.dtype))
+            act = ops.linear(h, self.w_gate_up, glu=True, out=ctx.scratch("act", (n, width), h.dtype), norm=norm)
         else:
-            gate_up = ops.linear(h, self.w_gate_up, out=ctx.scratch("gate_up", (n, 2 * width), h.dtype))
+            gate_up = ops.linear(h, self.w_gate_up, out=ctx.scratch("gate_up", (n, 2 * width), h.dtype), norm=norm)
             act = ops.swiglu(gate_up, out=ctx.scratch("act", (n, width), h.dtype))
-        ops.linear(act, self.w_down, residual=residual)
+        ops.linear(act, self.w_down, residual=residual, emit=emit)
 
 
 register_feed_forward("gated_mlp", GatedMlp)

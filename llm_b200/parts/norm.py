@@ -11,6 +11,8 @@ class RmsNorm(Norm):
     (apps/engine/src/ops.rs:4-12). The weight is held in 32-bit."""
     graph_safe = True
     libraries = ("elementwise",)
+    #: y = x / sqrt(mean(x^2) + eps) * gain: a part behind this norm may fold it (Part.fold_input_norm)
+    foldable = True
 
     def __init__(self, spec):
         self.spec = spec

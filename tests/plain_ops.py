@@ -14,8 +14,19 @@ import torch
 PAGE = 64
 
 
-def embed(tokens, table, out=None, scale=1.0):
-    return table[tokens.long()].to(torch.float32) * scale
+def embed(tokens, table, out=None, scale=1.0, emit=None):
+    x = table[tokens.long()].to(torch.float32) * scale
+    if emit is not None:
+        cast_sumsq(x, emit)
+    return x
+
+
+def cast_sumsq(x, emit):
+    """The next norm's input: the rows as bfloat16 and their sums of squares (one part)."""
+    emit.rows.copy_(x.to(torch.bfloat16))
+    emit.sumsq[:, 0] = (x.float() * x.float()).sum(dim=-1)
+    emit.parts = 1
+    return emit
 
 
 def scale_(x, scale):
@@ -38,8 +49,21 @@ def swiglu(gate_up, out=None):
     return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
 
 
-def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
+def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False, norm=None, emit=None,
+           rope=None):
     product = a.to(torch.float32) @ w.to(torch.float32).T
+    if norm is not None:
+        # a folded norm: rows scaled by 1 / sqrt(mean square + eps) from the partial sums of squares
+        mean_square = norm.sumsq[:, :norm.parts].sum(dim=-1, keepdim=True) / norm.width
+        product = product / torch.sqrt(mean_square + norm.eps)
+    if rope is not None:
+        if bias is not None:
+            product = product + bias.to(torch.float32)
+        qkv = product.to(out_dtype or a.dtype)
+        rope_cache_write(qkv, rope.table, rope.tok_pos, rope.tok_seq, rope.block_table, rope.ring_pages,
+                         rope.k_cache, rope.v_cache, rope.n_heads, rope.n_kv_heads, rope.head_dim,
+                         rope.interleaved, rope.write_cache)
+        return qkv
     if glu:
         # rows of w alternate 16 gate rows, 16 up rows
         m = product.shape[0]
@@ -50,6 +74,8 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False):
         product = product + bias.to(torch.float32)
     if residual is not None:
         residual += product
+        if emit is not None:
+            cast_sumsq(residual, emit)
         return residual
     return product.to(out_dtype or a.dtype)
 
@@ -234,7 +260,7 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 
 
 
-OPS = {"embed": embed, "scale_": scale_, "rmsnorm": rmsnorm, "swiglu": swiglu, "linear": linear,
+OPS = {"embed": embed, "scale_": scale_, "cast_sumsq": cast_sumsq, "rmsnorm": rmsnorm, "swiglu": swiglu, "linear": linear,
        "rope_cache_write": rope_cache_write, "attention": attention, "argmax_rows": argmax_rows,
        "sample_rows": sample_rows}
 

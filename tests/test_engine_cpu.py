@@ -114,3 +114,30 @@ def test_ids_that_are_still_on_the_device_follow_their_entries_into_every_pass(t
     for b, q in enumerate(seqs):
         expected = plain_llama.forward(config, weights, q)
         assert torch.allclose(logits[b], expected[-1], atol=2e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_folded_norms_change_nothing_beyond_rounding(tmp_path, plain_kernels, monkeypatch, which):
+    """bfloat16 runs fold every layer's norms into the products behind them (the gain into the
+    weights, the scale into the epilogue, the input left by the product before). With the plain
+    kernels in the kernels' place: the folded and the unfolded model agree with each other and
+    with the plain implementation to bfloat16 rounding, in a prefill and in decode steps."""
+    import llm_b200.parts.block as block_module
+    folder = make_folder(tmp_path, which, torch.bfloat16)
+    config, weights = plain_llama.read_model_folder(folder)
+    tokens = random_tokens(40, config["vocab_size"], 5)
+    expected = plain_llama.forward(config, weights, tokens)
+    results = []
+    for fold in (True, False):
+        monkeypatch.setattr(block_module, "FOLD_NORMS", fold)
+        model = load_model(folder, torch.bfloat16, "cpu")
+        assert all(b.folded_mixer == fold and b.folded_ffn == fold for b in model.blocks)
+        engine = Engine(model, max_tokens=256)
+        (slot,) = engine.acquire()
+        rows = [engine.step([Entry(slot, tokens[:36], list(range(36)))])]
+        rows += [engine.step([Entry(slot, [t], [0])]) for t in tokens[36:]]
+        results.append(torch.cat(rows))
+    scale = float(expected.abs().max())
+    for got in results:
+        assert float((got - expected).abs().max()) <= 0.04 * scale
+    assert float((results[0] - results[1]).abs().max()) <= 0.04 * scale

@@ -563,3 +563,141 @@ def test_a_refused_row_stays_flagged_over_later_steps():
     assert status.tolist() == [1, 0] and out.tolist()[0] == 0
     ops().sample_rows(randn(2, 4096, seed=72), f, i, recent, recent_len, rng, out, status)
     assert status.tolist() == [1, 0]
+
+
+# ----------------------------------------------------------------------------- what rides in a product's epilogue
+
+def _sums_in_parts(x, parts, seed):
+    """Sums of squares of the rows of x, spread over `parts` partial sums (as a producer would leave them)."""
+    total = (x.float() * x.float()).sum(dim=-1)
+    weights = torch.rand(x.shape[0], parts, generator=torch.Generator().manual_seed(seed)).to(DEV) + 0.1
+    sums = torch.full((x.shape[0], ops().SUMSQ_LD), 1e30, device=DEV)      # unused parts must not be read
+    sums[:, :parts] = total[:, None] * weights / weights.sum(dim=-1, keepdim=True)
+    return sums
+
+
+@pytest.mark.parametrize("m,n,k,parts", [(8, 6144, 4096, 32), (1, 256, 64, 1), (16, 384, 512, 3),
+                                         (40, 320, 1024, 5), (128, 512, 256, 64), (300, 512, 256, 2),
+                                         (2048, 1024, 256, 16), (700, 200, 72, 1)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_with_a_folded_norm(m, n, k, parts, bias):
+    """The norm folded into the product: un-normalised bfloat16 rows, the gain in the weights, the rows
+    of the result scaled by 1 / sqrt(mean square + eps) in the epilogue (every kernel shape: decode
+    tiles summed by the last block or by the sum kernel, one split, tokens on the 128-row side, pairs
+    of SMs), against normalising first with the plain norm."""
+    x = randn(m, k, seed=140, scale=3.0)
+    x[m // 2] *= 1e-3
+    gain = 1.0 + randn(k, seed=141, scale=0.2)
+    w = randn(n, k, dtype=torch.bfloat16, seed=142, scale=0.1)
+    b = randn(n, seed=143) if bias else None
+    eps = 1e-5
+    folded = (w.float() * gain[None, :]).to(torch.bfloat16)
+    norm = ops().FoldedNorm(x.to(torch.bfloat16), _sums_in_parts(x, parts, 144), parts, eps, k)
+    got = ops().linear(norm.rows, folded, b, norm=norm)
+    want = plain_ops.rmsnorm(x, gain, eps, torch.float32) @ w.float().T + (b if bias else 0.0)
+    assert torch.allclose(got.float(), want, atol=3e-2 * float(want.abs().max()), rtol=3e-2)
+    assert torch.allclose(plain_ops.linear(norm.rows, folded, b, norm=norm).float(), want,
+                          atol=3e-2 * float(want.abs().max()), rtol=3e-2)
+    assert ops().tensor_core_status() == 0
+
+
+@pytest.mark.parametrize("m,f,k", [(8, 14336, 4096), (40, 320, 1024), (300, 1024, 520), (2048, 1024, 256)])
+def test_gated_epilogue_with_a_folded_norm(m, f, k):
+    x = randn(m, k, seed=150, scale=2.0)
+    gain = 1.0 + randn(k, seed=151, scale=0.2)
+    gate = randn(f, k, dtype=torch.bfloat16, seed=152, scale=0.05)
+    up = randn(f, k, dtype=torch.bfloat16, seed=153, scale=0.05)
+    mixed = torch.stack([gate.view(-1, 16, k), up.view(-1, 16, k)], dim=1).reshape(2 * f, k)
+    folded = (mixed.float() * gain[None, :]).to(torch.bfloat16).contiguous()
+    norm = ops().FoldedNorm(x.to(torch.bfloat16), _sums_in_parts(x, 7, 154), 7, 1e-6, k)
+    got = ops().linear(norm.rows, folded, glu=True, norm=norm)
+    h = plain_ops.rmsnorm(x, gain, 1e-6, torch.float32)
+    g, u = h @ gate.float().T, h @ up.float().T
+    want = g / (1 + torch.exp(-g)) * u
+    assert torch.allclose(got.float(), want, atol=3e-2 * float(want.abs().max()), rtol=3e-2)
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 4096, 4096), (1, 4096, 14336), (16, 384, 512), (8, 200, 256),
+                                   (40, 4096, 1024), (64, 520, 256), (300, 512, 256), (5, 64, 64)])
+def test_linear_leaves_the_next_norms_input(m, n, k):
+    """A product that adds into the residual also leaves the updated rows as bfloat16 and the sums of
+    their squares in parts (by the tile's last block, by the sum kernel, or by a kernel behind the
+    product where the shape's kernel has no such epilogue): twice in a row on the same buffers."""
+    a = randn(m, k, dtype=torch.bfloat16, seed=160)
+    w = randn(n, k, dtype=torch.bfloat16, seed=161, scale=0.1)
+    b = randn(n, seed=162)
+    residual = randn(m, n, seed=163, scale=2.0)
+    want = residual.clone()
+    emit = ops().Emit(torch.zeros(m, n, dtype=torch.bfloat16, device=DEV),
+                      torch.full((m, ops().SUMSQ_LD), float("nan"), device=DEV))
+    for _ in range(2):
+        want = want + (a.float() @ w.float().T + b)
+        ops().linear(a, w, b, residual=residual, emit=emit)
+        scale = float(want.abs().max())
+        assert torch.allclose(residual, want, atol=2e-2 * scale, rtol=2e-2)
+        assert 1 <= emit.parts <= ops().SUMSQ_LD
+        assert torch.equal(emit.rows, residual.to(torch.bfloat16))
+        sums = emit.sumsq[:, :emit.parts].sum(dim=-1)
+        assert torch.allclose(sums, (residual * residual).sum(dim=-1), rtol=1e-4)
+    assert ops().tensor_core_status() == 0
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 16, 40, 128, 300])
+@pytest.mark.parametrize("heads,kv_heads,dim,interleaved,bias", [(8, 2, 128, False, False), (4, 4, 64, False, True),
+                                                                 (6, 2, 32, True, True), (3, 1, 128, True, False),
+                                                                 (6, 2, 48, False, False)])
+def test_qkv_product_rotates_and_writes_the_cache(tokens, heads, kv_heads, dim, interleaved, bias):
+    """The q/k/v product with the rotation and the cache write in its epilogue (and a folded norm
+    with it) against the product followed by the plain rope_cache_write: sequences at different
+    positions and pages, head sizes that fit a tile and one that does not (48: a kernel of its own
+    runs behind the product)."""
+    k = 256
+    width = (heads + 2 * kv_heads) * dim
+    counts = [tokens] if tokens < 3 else [tokens - 2, 1, 1]
+    starts = [130, 63, 0][:len(counts)]
+    lens = [s + c for s, c in zip(starts, counts)]
+    table, pages_wide, k_cache, v_cache = make_cache(len(counts), lens, kv_heads, dim, torch.bfloat16, 170)
+    tok_pos = torch.tensor([p for s, c in zip(starts, counts) for p in range(s, s + c)], dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([i for i, c in enumerate(counts) for _ in range(c)], dtype=torch.int32, device=DEV)
+    x = randn(tokens, k, seed=171, scale=2.0)
+    gain = 1.0 + randn(k, seed=172, scale=0.2)
+    w = randn(width, k, dtype=torch.bfloat16, seed=173, scale=0.1)
+    b = randn(width, seed=174) if bias else None
+    folded = (w.float() * gain[None, :]).to(torch.bfloat16)
+    norm = ops().FoldedNorm(x.to(torch.bfloat16), _sums_in_parts(x, 4, 175), 4, 1e-5, k)
+    angle = torch.arange(max(lens) + 1, dtype=torch.float64)[:, None] * (
+        10000.0 ** (-2.0 * torch.arange(dim // 2, dtype=torch.float64) / dim))[None, :]
+    rope = torch.cat([angle.cos(), angle.sin()], 1).float().to(DEV)
+    # plain: normalise, project, round as the unfused path does, rotate, write
+    want_qkv = (plain_ops.rmsnorm(x, gain, 1e-5, torch.float32) @ w.float().T + (b if bias else 0.0)).to(torch.bfloat16)
+    want_k, want_v = k_cache.clone(), v_cache.clone()
+    plain_ops.rope_cache_write(want_qkv, rope, tok_pos, tok_seq, table, pages_wide, want_k, want_v, heads,
+                               kv_heads, dim, interleaved)
+    for write in (True, False):
+        got_k, got_v = k_cache.clone(), v_cache.clone()
+        got = ops().linear(norm.rows, folded, b, norm=norm, rope=ops().RopeWrite(
+            rope, tok_pos, tok_seq, table, pages_wide, got_k, got_v, heads, kv_heads, dim, interleaved, write))
+        q = heads * dim
+        scale = float(want_qkv.float().abs().max())
+        assert torch.allclose(got[:, :q].float(), want_qkv[:, :q].float(), atol=3e-2 * scale, rtol=3e-2)
+        if write:
+            assert torch.allclose(got_k.float(), want_k.float(), atol=3e-2 * scale, rtol=3e-2)    # other rows keep 7.0
+            assert torch.allclose(got_v.float(), want_v.float(), atol=3e-2 * scale, rtol=3e-2)
+        else:
+            assert torch.equal(got_k, k_cache) and torch.equal(got_v, v_cache)
+    assert ops().tensor_core_status() == 0
+
+
+def test_cast_sumsq_and_embedding_leave_the_first_norms_input():
+    x = randn(9, 1000, seed=180, scale=3.0)
+    emit = ops().Emit(torch.empty(9, 1000, dtype=torch.bfloat16, device=DEV), torch.zeros(9, ops().SUMSQ_LD, device=DEV))
+    ops().cast_sumsq(x, emit)
+    assert emit.parts == 1 and torch.equal(emit.rows, x.to(torch.bfloat16))
+    assert torch.allclose(emit.sumsq[:, 0], (x * x).sum(dim=-1), rtol=1e-5)
+    table = randn(301, 72, dtype=torch.bfloat16, seed=181)
+    tokens = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    emit = ops().Emit(torch.empty(5, 72, dtype=torch.bfloat16, device=DEV), torch.zeros(5, ops().SUMSQ_LD, device=DEV))
+    got = ops().embed(tokens, table, scale=2.0, emit=emit)
+    want = plain_ops.embed(tokens, table, scale=2.0)
+    assert torch.equal(got, want) and torch.equal(emit.rows, want.to(torch.bfloat16))
+    assert torch.allclose(emit.sumsq[:, 0], (want * want).sum(dim=-1), rtol=1e-5)
