@@ -4,9 +4,7 @@
 // The structure is attention_split + attention_combine of MythEclipse/llm
 // (apps/engine/kernels/gpu.cu:649-762): blocks take slices of the positions,
 // each writes (weighted values, max, sum) partials, and a second kernel merges
-// them with out = sum_i acc_i e^(m_i - m) / sum_i l_i e^(m_i - m); here the merge is
-// done by the block that finishes last for a (sequence, kv head) instead of a kernel of
-// its own (a counter per pair, which returns to zero). What also differs
+// them with out = sum_i acc_i e^(m_i - m) / sum_i l_i e^(m_i - m). What differs
 // is the inside of a block. The step is bound by reading keys and values once,
 // so a block serves one (sequence, kv head): the Hq/Hkv query heads that share
 // those keys ride along as rows of one tensor-core tile, and the keys and
@@ -58,7 +56,6 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               const int* __restrict__ block_table, int table_stride, int ring_pages,
                               const int* __restrict__ seq_lens, const int* __restrict__ seq_order,
                               float* __restrict__ part_acc, float* __restrict__ part_stats,
-                              unsigned* __restrict__ counters,
                               __nv_bfloat16* __restrict__ out, int out_stride,
                               int n_heads, int n_kv_heads, float scale_log2) {
     constexpr int LDS = D + PAD;
@@ -244,46 +241,40 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             continue;
         }
         size_t slot = ((size_t)seq * n_heads + kv_head * group + head) * n_splits + split;
-        __stcg(&part_acc[slot * D + d], value);
-        if (d == 0) { __stcg(&part_stats[slot * 2], m); __stcg(&part_stats[slot * 2 + 1], sum); }
+        part_acc[slot * D + d] = value;
+        if (d == 0) { part_stats[slot * 2] = m; part_stats[slot * 2 + 1] = sum; }
     }
     LLMB_STAMP(4, 0);                                // the partial result is written
-    if (n_splits == 1) return;
-    // The block that arrives last at the pair's counter merges the slices' partials, in the order
-    // of the slices (the merge of attention_combine, apps/engine/kernels/gpu.cu:721-762).
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        unsigned arrived = atomicAdd(&counters[(size_t)seq * n_kv_heads + kv_head], 1u);
-        is_last = arrived == (unsigned)(n_splits - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    for (int idx = tid; idx < group * D; idx += WARPS * 32) {
-        int head = kv_head * group + idx / D, d = idx % D;
-        size_t base = ((size_t)seq * n_heads + head) * n_splits;
-        float m = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) m = fmaxf(m, __ldcg(&part_stats[(base + s) * 2]));
+}
+
+template <int D>
+__global__ void attention_decode_combine_kernel(const float* __restrict__ part_acc,
+                                                const float* __restrict__ part_stats,
+                                                __nv_bfloat16* __restrict__ out, int out_stride,
+                                                int n_heads, int n_splits) {
+    griddep_launch();
+    griddep_wait();
+    int seq = blockIdx.y, head = blockIdx.x;
+    size_t base = ((size_t)seq * n_heads + head) * n_splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_stats[(base + s) * 2]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float value = 0.f, sum = 0.f;
         for (int s = 0; s < n_splits; ++s) {
-            float ms = __ldcg(&part_stats[(base + s) * 2]);
+            float ms = part_stats[(base + s) * 2];
             float weight = ms == -INFINITY ? 0.f : exp2f(ms - m);
-            value += __ldcg(&part_acc[(base + s) * D + d]) * weight;
-            sum += __ldcg(&part_stats[(base + s) * 2 + 1]) * weight;
+            value += part_acc[(base + s) * D + d] * weight;
+            sum += part_stats[(base + s) * 2 + 1] * weight;
         }
         out[(size_t)seq * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(value / sum);
     }
-    if (tid == 0) counters[(size_t)seq * n_kv_heads + kv_head] = 0u;
-    LLMB_STAMP(5, 0);                                // the last block of the pair has merged
 }
 
 template <int D>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                   const int* block_table, int table_stride, int ring_pages, const int* seq_lens,
-                  const int* seq_order, void* out, int out_stride, float* scratch, unsigned* counters, int n_seqs,
-                  int n_heads, int n_kv_heads, float scale, int n_splits, cudaStream_t stream) {
+                  const int* seq_order, void* out, int out_stride, float* scratch, int n_seqs, int n_heads,
+                  int n_kv_heads, float scale, int n_splits, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
     constexpr int STAGES = stages_for<D>();
     size_t stage_bytes = (size_t)STAGES * pages_per_stage<D>() * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
@@ -301,9 +292,12 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     llmb::launch(attention_decode_split_kernel<D>, grid, WARPS * 32, smem, stream, true,
                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
                  (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order,
-                 part_acc, part_stats, counters, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads,
-                 scale * 1.4426950408889634f);
-    return check_launch("attention_decode");
+                 part_acc, part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f);
+    int code = check_launch("attention_decode_split");
+    if (code || n_splits == 1) return code;
+    llmb::launch(attention_decode_combine_kernel<D>, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, true,
+                 (const float*)part_acc, (const float*)part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_splits);
+    return check_launch("attention_decode_combine");
 }
 
 // The stamps of the last launches in a build with -DLLMB_TRACE (see common.cuh): rows are linear block
@@ -329,8 +323,7 @@ LLMB_EXPORT int llmb_attention_decode_supports(int n_heads, int n_kv_heads, int 
 LLMB_EXPORT int llmb_attention_decode(const void* q, int q_stride, const void* k_cache,
                                       const void* v_cache, const int* block_table, int table_stride,
                                       int ring_pages, const int* seq_lens, const int* seq_order, void* out,
-                                      int out_stride, float* scratch, long long scratch_floats,
-                                      unsigned* counters, int n_counters, int n_seqs,
+                                      int out_stride, float* scratch, long long scratch_floats, int n_seqs,
                                       int n_heads, int n_kv_heads, int head_dim, float scale,
                                       int window, int n_splits, cudaStream_t stream) {
     if (n_seqs == 0) return LLMB_OK;
@@ -343,10 +336,8 @@ LLMB_EXPORT int llmb_attention_decode(const void* q, int q_stride, const void* k
     LLMB_REQUIRE(scratch != nullptr && scratch_floats >= llmb_attention_decode_scratch_floats(
                                                              n_seqs, n_heads, head_dim, n_splits),
                  "attention_decode: scratch too small");
-    LLMB_REQUIRE(n_splits == 1 || (counters != nullptr && n_counters >= n_seqs * n_kv_heads),
-                 "attention_decode: one counter (zero between calls) per sequence and kv head is needed");
 #define ARGS q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order, out, \
-             out_stride, scratch, counters, n_seqs, n_heads, n_kv_heads, scale, n_splits, stream
+             out_stride, scratch, n_seqs, n_heads, n_kv_heads, scale, n_splits, stream
     switch (head_dim) {
         case 32: return launch<32>(ARGS);
         case 64: return launch<64>(ARGS);

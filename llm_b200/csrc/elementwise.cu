@@ -245,10 +245,14 @@ __global__ void scale_rows_kernel(T* __restrict__ out, int width, const float* _
                                   float eps, float norm_width, const float* __restrict__ bias) {
     __shared__ float scale_s;
     int t = blockIdx.x;
-    if (threadIdx.x == 0) {
-        float s = 0.f;
-        for (int i = 0; i < parts; ++i) s += sumsq[(size_t)t * LLMB_SUMSQ_LD + i];
-        scale_s = 1.0f / sqrtf(s / norm_width + eps);
+    if (threadIdx.x < 32) {
+        // the order of the products' epilogues (warp_row_rstd in gemm_tc.cu): lane i takes parts i and
+        // i + 32, then a butterfly over the lanes
+        int lane = threadIdx.x;
+        const float* p = sumsq + (size_t)t * LLMB_SUMSQ_LD;
+        float v = (lane < parts ? p[lane] : 0.f) + (lane + 32 < parts ? p[lane + 32] : 0.f);
+        v = warp_sum(v);
+        if (lane == 0) scale_s = 1.0f / sqrtf(v / norm_width + eps);
     }
     __syncthreads();
     float scale = scale_s;

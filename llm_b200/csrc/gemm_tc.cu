@@ -68,21 +68,27 @@ struct Epilogue {
     llmb_gemm_fusion f;      // what else the epilogue does (fusion.h); all zero: nothing
 };
 
-// 1 / sqrt(mean of squares + eps) of an input row from the partial sums its producer left, added in
-// the order of the parts (every consumer of a row gets the same bits)
-__device__ __forceinline__ float row_rstd(const llmb_gemm_fusion& f, int token) {
+// 1 / sqrt(mean of squares + eps) of an input row from the partial sums its producer left. A whole warp
+// computes it: lane i adds parts i and i + 32, then the lanes are summed as a butterfly, so every
+// consumer of a row gets the same bits, and the loads of a row are in flight together.
+__device__ __forceinline__ float warp_row_rstd(const llmb_gemm_fusion& f, int token) {
+    int lane = threadIdx.x & 31;
     const float* p = f.norm_sumsq + (size_t)token * LLMB_SUMSQ_LD;
-    float s = 0.f;
-    for (int i = 0; i < f.norm_parts; ++i) s += __ldcg(p + i);
-    return 1.0f / sqrtf(s / f.norm_width + f.norm_eps);
+    float v = (lane < f.norm_parts ? __ldcg(p + lane) : 0.f) + (lane + 32 < f.norm_parts ? __ldcg(p + lane + 32) : 0.f);
+    v = warp_sum(v);
+    return 1.0f / sqrtf(v / f.norm_width + f.norm_eps);
 }
 
-// The scales of a tile's token rows into shared memory, by the 128 epilogue threads (local = 0..127),
-// before the tile's accumulator is awaited. The caller synchronises the epilogue warps afterwards.
-__device__ __forceinline__ void tile_rstd(const Epilogue& ep, float* rstd, int local, int first_token, int n_tile_tokens) {
-    if (local < n_tile_tokens) {
-        int token = first_token + local;
-        rstd[local] = token < ep.tokens ? row_rstd(ep.f, token) : 1.f;
+// The scales of a tile's token rows into shared memory, by the four epilogue warps (quarter = 0..3, each
+// takes every fourth row), before the tile's accumulator is awaited. The caller synchronises the epilogue
+// warps afterwards.
+__device__ __forceinline__ void tile_rstd(const Epilogue& ep, float* rstd, int quarter, int first_token, int n_tile_tokens) {
+    int lane = threadIdx.x & 31;
+#pragma unroll 4
+    for (int i = quarter; i < n_tile_tokens; i += 4) {
+        int token = first_token + i;
+        float r = token < ep.tokens ? warp_row_rstd(ep.f, token) : 1.f;
+        if (lane == 0) rstd[i] = r;
     }
 }
 
@@ -260,8 +266,44 @@ __device__ __forceinline__ void finish_emit(const Epilogue& ep, int a_row, int t
 // values into the paged cache (what llmb_rope_cache_write does in a kernel of its own). A head's values
 // lie in one tile (128 % head_dim == 0); pairs (p, p + head_dim/2) are exchanged through shared memory
 // (exch: 16 x 128 floats), interleaved pairs (2p, 2p+1) between neighbouring lanes.
+//
+// What the epilogue needs from global memory besides the products is fetched before the products are
+// awaited (stage_rope, by every block of the tile, since any may be the last): each token's position, the
+// page of its position and its row of angles wait in shared memory. Read in the epilogue itself, these
+// small loads miss the L2 (a layer's weights have passed through it since their last use) and two of
+// them in a chain cost the last block of a tile three microseconds.
+struct RopeStage {
+    float angles[16][BM];          // [token of the tile][head_dim values: cosines, then sines]
+    int pos[16];
+    int page[16];
+};
+
+__device__ __forceinline__ void stage_rope(const Epilogue& ep, RopeStage* stage, int first_token) {
+    const llmb_gemm_fusion& f = ep.f;
+    int local = (int)threadIdx.x - 64;
+    int valid = min(16, ep.tokens - first_token);
+    if (local < 16) {
+        int pos = 0, page = 0;
+        if (local < valid) {
+            pos = f.tok_pos[first_token + local];
+            page = f.block_table[(size_t)f.tok_seq[first_token + local] * f.table_stride + ((pos / LLMB_PAGE) % f.ring_pages)];
+        }
+        stage->pos[local] = pos;
+        stage->page[local] = page;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (f.rope_table) {
+        int dim = f.head_dim;
+        for (int i = local; i < valid * dim; i += 128) {
+            int j = i / dim, e = i - j * dim;
+            stage->angles[j][e] = f.rope_table[(size_t)stage->pos[j] * dim + e];
+        }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
 __device__ __forceinline__ void finish_rope(const Epilogue& ep, int a_row, int tile_row, int first_token, int valid,
-                                            float (&v)[16], float* exch) {
+                                            float (&v)[16], float* exch, const RopeStage* stage) {
     const llmb_gemm_fusion& f = ep.f;
     int dim = f.head_dim, half = dim >> 1;
     int head = a_row / dim, r = a_row - head * dim;
@@ -282,7 +324,6 @@ __device__ __forceinline__ void finish_rope(const Epilogue& ep, int a_row, int t
         for (int j = 0; j < 16; ++j) partner[j] = exch[j * BM + other];
         asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-    if (!live) return;
     bool is_q = head < f.n_heads, is_k = !is_q && head < f.n_heads + f.n_kv_heads;
     bool rotates = f.rope_table != nullptr && (is_q || is_k);
     bool low = f.interleaved ? (r & 1) == 0 : r < half;
@@ -292,22 +333,21 @@ __device__ __forceinline__ void finish_rope(const Epilogue& ep, int a_row, int t
     int kv_head = is_k ? head - f.n_heads : head - f.n_heads - f.n_kv_heads;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-        if (j >= valid) break;
-        int token = first_token + j;
-        int pos = f.tok_pos[token];
+        if (j >= valid || !live) break;
         float value = v[j];
         if (rotates) {
-            float c = f.rope_table[(size_t)pos * dim + pair], s = f.rope_table[(size_t)pos * dim + half + pair];
+            float c = stage->angles[j][pair], s = stage->angles[j][half + pair];
             value = low ? v[j] * c - partner[j] * s : partner[j] * s + v[j] * c;
         }
         if (is_q) {
-            q_out[(size_t)token * ep.ldo + a_row] = __float2bfloat16_rn(value);
+            q_out[(size_t)(first_token + j) * ep.ldo + a_row] = __float2bfloat16_rn(value);
         } else if (f.write_cache) {
-            int page = f.block_table[(size_t)f.tok_seq[token] * f.table_stride + ((pos / LLMB_PAGE) % f.ring_pages)];
-            cache[(((size_t)page * f.n_kv_heads + kv_head) * LLMB_PAGE + (pos % LLMB_PAGE)) * dim + r] =
+            int pos = stage->pos[j];
+            cache[(((size_t)stage->page[j] * f.n_kv_heads + kv_head) * LLMB_PAGE + (pos % LLMB_PAGE)) * dim + r] =
                 __float2bfloat16_rn(value);
         }
     }
+    asm volatile("bar.sync 1, 128;" ::: "memory");      // the staged values are free for the block's next unit
 }
 
 // Persistent: the grid has at most as many blocks as fit on the GPU at once, and block b
@@ -343,12 +383,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
     float* exch = reinterpret_cast<float*>(tmem_slot + 4);      // the fused epilogues' exchange (sized by the host)
+    RopeStage* rope_stage = reinterpret_cast<RopeStage*>(exch + 16 * BM);   // only with a fused rotation
     __shared__ float rstd_s[2][BM];                             // scales of a tile's token rows (a folded norm)
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     LLMB_STAMP(0, 0);                                           // the block has started
+    griddep_launch();                                           // the next kernel of the stream may set itself up
+    uint32_t early = 0;                                         // k-blocks whose weight tile is on its way
 
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -360,6 +405,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the barriers, as the copy engine sees them
+        // Fetch this block's first weight tiles at once (no kernel writes weights): this thread made the
+        // barriers and is the producer, so it need not wait for the block's set-up, and the kernel before
+        // this one may still be running. The activations, the residual and the split-K scratch are
+        // touched only after griddep_wait().
+        if ((int)blockIdx.x < n_units) {
+            Unit w = unit_of(blockIdx.x, tiles_a, splits);
+            int kb_begin = w.split * kblocks_per_split;
+            int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
+            early = (uint32_t)min(stages, kb_end - kb_begin);
+            for (uint32_t i = 0; i < early; ++i) {
+                uint32_t bar = smem_u32(&full_bar[i]);
+                mbar_expect_tx(bar, A_BYTES + B_BYTES);
+                if (swap) tma_load_2d(smem_u32(a_tiles + (size_t)i * A_BYTES), &map_a, bar, (kb_begin + i) * BK, w.tile_a * BM);
+                else tma_load_2d(smem_u32(b_tiles + (size_t)i * B_BYTES), &map_b, bar, (kb_begin + i) * BK, w.tile_b * BN);
+            }
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -370,25 +432,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tcgen05_fence_after();
     uint32_t tmem_base = *tmem_slot;
-
-    // Let the next kernel of the stream set itself up, and fetch this block's first weight tiles
-    // (no kernel writes weights), while the kernel before this one is still running; the
-    // activations, the residual and the split-K scratch are touched only after griddep_wait().
     LLMB_STAMP(1, 0);                                           // barriers and tensor memory are set up
-    griddep_launch();
-    uint32_t early = 0;                                         // k-blocks whose weight tile is on its way
-    if (warp == 0 && lane == 0 && (int)blockIdx.x < n_units) {
-        Unit w = unit_of(blockIdx.x, tiles_a, splits);
-        int kb_begin = w.split * kblocks_per_split;
-        int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
-        early = (uint32_t)min(stages, kb_end - kb_begin);
-        for (uint32_t i = 0; i < early; ++i) {
-            uint32_t bar = smem_u32(&full_bar[i]);
-            mbar_expect_tx(bar, A_BYTES + B_BYTES);
-            if (swap) tma_load_2d(smem_u32(a_tiles + (size_t)i * A_BYTES), &map_a, bar, (kb_begin + i) * BK, w.tile_a * BM);
-            else tma_load_2d(smem_u32(b_tiles + (size_t)i * B_BYTES), &map_b, bar, (kb_begin + i) * BK, w.tile_b * BN);
-        }
-    }
     griddep_wait();
     LLMB_STAMP(2, 0);                                           // the kernel before this one has completed
 
@@ -467,11 +511,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // (two buffers in turn and one barrier a unit: a warp that runs ahead writes the other one)
             const float* rstd = nullptr;
             if (ep.f.norm_sumsq) {
-                tile_rstd(ep, rstd_s[n_done & 1], (int)threadIdx.x - 64, swap ? w.tile_b * BN : w.tile_a * BM,
+                tile_rstd(ep, rstd_s[n_done & 1], quarter, swap ? w.tile_b * BN : w.tile_a * BM,
                           swap ? (BN < BM ? BN : BM) : BM);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 rstd = rstd_s[n_done & 1];
             }
+            // a fused rotation: positions, pages and angles of the tile's tokens into shared memory
+            // (read again only after this unit's epilogue, which ends with a barrier of these warps)
+            if (BN == 16 && swap && splits > 1 && ep.f.rope) stage_rope(ep, rope_stage, w.tile_b * BN);
             ok = mbar_wait(smem_u32(&acc_full_bar[buffer]), use & 1, abort_flag, status, 3);
             if (!ok) break;
             tcgen05_fence_after();
@@ -614,7 +661,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] *= rstd[c + j];
                     }
-                    if (ep.f.rope) finish_rope(ep, a_row, row, w.tile_b * BN + c, valid, v, exch);
+                    if (ep.f.rope) finish_rope(ep, a_row, row, w.tile_b * BN + c, valid, v, exch, rope_stage);
                     else finish_emit(ep, a_row, w.tile_a, w.tile_b * BN + c, valid, v, old, exch);
                 } else {
                     store_columns<BN>(ep, swap, a_row, w.tile_b, c, v, preload ? old : nullptr, rstd, row);
@@ -670,7 +717,10 @@ splitk_sum_kernel(const float* __restrict__ partials, Epilogue ep, int tiles_a, 
     int feature = blockIdx.x * 256 + threadIdx.x;                  // with glu: the activated column
     int n_features = ep.glu ? ep.outs / 2 : ep.outs;
     if (ep.f.norm_sumsq) {
-        if (threadIdx.x == 0) scale_s = row_rstd(ep.f, token);
+        if (threadIdx.x < 32) {
+            float r = warp_row_rstd(ep.f, token);
+            if (threadIdx.x == 0) scale_s = r;
+        }
         __syncthreads();
     }
     float scale = ep.f.norm_sumsq ? scale_s : 1.f;
@@ -723,7 +773,10 @@ splitk_sum_rope_kernel(const float* __restrict__ partials, Epilogue ep, int tile
     int n_items = n_pairs + f.n_kv_heads * dim;
     int item = blockIdx.x * 256 + threadIdx.x;
     if (f.norm_sumsq) {
-        if (threadIdx.x == 0) scale_s = row_rstd(f, token);
+        if (threadIdx.x < 32) {
+            float r = warp_row_rstd(f, token);
+            if (threadIdx.x == 0) scale_s = r;
+        }
         __syncthreads();
     }
     float scale = f.norm_sumsq ? scale_s : 1.f;
@@ -947,7 +1000,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t buffer = n_done & 1, use = n_done >> 1;
             const float* rstd = nullptr;
             if (ep.f.norm_sumsq) {                    // as in gemm_tc_kernel: while the products run
-                tile_rstd(ep, rstd_s[n_done & 1], (int)threadIdx.x - 64, w.tile_a * 2 * BM + (int)rank * BM, BM);
+                tile_rstd(ep, rstd_s[n_done & 1], quarter, w.tile_a * 2 * BM + (int)rank * BM, BM);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 rstd = rstd_s[n_done & 1];
             }
@@ -1037,7 +1090,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
     // the fused decode epilogues exchange values through shared memory behind the control words:
     // 64 floats for the sums of squares, 16 x 128 for rotation pairs that sit half a head apart
     size_t exchange = 256;
-    if (swap && BN == 16 && splits > 1 && ep.f.rope && !ep.f.interleaved) exchange = (size_t)16 * BM * 4;
+    if (swap && BN == 16 && splits > 1 && ep.f.rope) exchange = (size_t)16 * BM * 4 + sizeof(RopeStage);
     if (swap) {                                         // two blocks per SM for the decode stream
         stages = (int)((110 * 1024 - (exchange > 256 ? exchange : 0)) / (A_BYTES + B_BYTES));
         if (stages > 6) stages = 6;

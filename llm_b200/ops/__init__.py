@@ -589,21 +589,19 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
         lib.llmb_attention_decode_scratch_floats.restype = ctypes.c_longlong
         need = lib.llmb_attention_decode_scratch_floats(_c_int(n), _c_int(n_heads), _c_int(head_dim),
                                                         _c_int(splits))
-        held = _attention_scratch.get(qkv.device)
-        if held is None or held[0].numel() < need or held[1].numel() < n * n_kv_heads:
-            if held is not None:
-                _retired.append(held)
-            # partial results, and one counter per (sequence, kv head) that is zero between calls
-            held = (torch.empty(max(need, 1 << 23), dtype=torch.float32, device=qkv.device),
-                    torch.zeros(max(n * n_kv_heads, 1 << 14), dtype=torch.int32, device=qkv.device))
-            _attention_scratch[qkv.device] = held
-        scratch, counters = held
+        scratch = _attention_scratch.get(qkv.device)
+        if scratch is None or scratch.numel() < need:
+            if scratch is not None:
+                _retired.append(scratch)
+            scratch = torch.empty(max(need, 1 << 23), dtype=torch.float32, device=qkv.device)
+            _attention_scratch[qkv.device] = scratch
         _call("attention_decode", "llmb_attention_decode", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
               _c_int(ring_pages), _ptr(seq_lens), _ptr(seq_order), _ptr(out), _c_int(out.stride(0)),
-              _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(counters), _c_int(counters.numel()),
-              _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
-              _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream())
+              _ptr(scratch),
+              ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
+              _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream(),
+              kernels=2 if splits > 1 else 1)
     elif variant == "attention_generic":
         _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),

@@ -129,6 +129,11 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=128)
     p.add_argument("--variant", default=None, help="force a kernel variant by disabling higher ranks")
     p.add_argument("--residual", action="store_true", help="linear: add into a 32-bit residual")
+    p.add_argument("--norm", action="store_true", help="linear: with a folded norm (32 partial sums a row)")
+    p.add_argument("--emit", action="store_true", help="linear (with --residual): leave the next norm's input")
+    p.add_argument("--rope", action="store_true",
+                   help="linear: the q/k/v product with rotation and cache write (n = (heads + 2 kv heads) * head dim)")
+    p.add_argument("--glu", action="store_true", help="linear: the gated epilogue (n = 2 x the feed-forward width)")
     p.add_argument("--temperature", type=float, default=0.0,
                    help="sample: 0 is greedy; above it the default chain (top-k 40, top-p 0.75, min-p 0.25, "
                         "repeat penalty 1.1 over the last 64) runs")
@@ -154,8 +159,26 @@ def main(argv=None) -> int:
         out = None if args.residual else torch.empty(m, n, device=DEV, dtype=bf16)
         turn = [0]
 
+        import llm_b200.ops as ops
+        norm = emit = rope = None
+        if args.norm:
+            norm = ops.FoldedNorm(x, torch.rand(m, ops.SUMSQ_LD, device=DEV) * k / 32, 32, 1e-5, k)
+        if args.emit:
+            emit = ops.Emit(torch.empty(m, n, device=DEV, dtype=bf16), torch.empty(m, ops.SUMSQ_LD, device=DEV))
+        if args.rope:
+            hq, hkv, d = args.heads, args.kv_heads, args.head_dim
+            assert n == (hq + 2 * hkv) * d, "--n must be (heads + 2 kv heads) * head dim"
+            pages = (args.context + 63) // 64
+            kc = torch.zeros(m * pages, hkv, 64, d, device=DEV, dtype=bf16)
+            vc = torch.zeros_like(kc)
+            rope = ops.RopeWrite(torch.rand(args.context, d, device=DEV), torch.full((m,), args.context - 1, dtype=torch.int32, device=DEV),
+                                 torch.arange(m, dtype=torch.int32, device=DEV),
+                                 torch.arange(m * pages, dtype=torch.int32, device=DEV).view(m, pages), pages, kc, vc, hq, hkv, d)
+        if args.glu:
+            out = torch.empty(m, n // 2, device=DEV, dtype=bf16)
+
         def fn():
-            linear(x, ws[turn[0] % copies], residual=res, out=out)
+            linear(x, ws[turn[0] % copies], residual=res, out=out, norm=norm, emit=emit, rope=rope, glu=args.glu)
             turn[0] += 1
         args.reps = max(args.reps, copies * 2) if not args.once else args.reps
         name = tactics.choose_linear(m, n, k, bf16, bf16, k)
