@@ -346,3 +346,6 @@ LLMB_EXPORT int llmb_attention_decode(const void* q, int q_stride, const void* k
     }
 #undef ARGS
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_attention_decode)

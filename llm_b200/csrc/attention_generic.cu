@@ -152,3 +152,6 @@ LLMB_EXPORT int llmb_attention_generic(const void* q, int q_stride, const void* 
 #undef LLMB_GENERIC
     return check_launch("attention_generic");
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_attention_generic)

@@ -275,3 +275,6 @@ LLMB_EXPORT int llmb_attention_prefill(const void* q, int q_stride, const void* 
     }
 #undef ARGS
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_attention_prefill)

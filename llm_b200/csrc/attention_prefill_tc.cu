@@ -422,3 +422,6 @@ LLMB_EXPORT int llmb_attention_prefill_tc(const void* q, int q_stride, int n_tok
     return launch<128>(map_q, map_k, map_v, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, seq_order, out,
                        out_stride, n_seqs, max_new, n_heads, n_kv_heads, scale, stream);
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_attention_prefill_tc)

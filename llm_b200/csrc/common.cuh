@@ -14,6 +14,8 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
+#include <utility>
 
 #define LLMB_OK 0
 #define LLMB_ERR_ARGUMENT 1    // a size or option this kernel refuses
@@ -155,6 +157,38 @@ inline int llmb_read_trace(unsigned long long*, int) { return 1; }
 #endif
 
 #define LLMB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// A second door to every launching entry point: `name`_packed(const llmb_slot* args) takes the same
+// arguments as `name`, one 8-byte slot each in the order of the signature (pointers, and the stream,
+// as addresses; integers widened to 64 bits; floating point as double). A recorded pass is a list
+// of such (function, argument block) pairs that the native host library walks with one call per
+// launch and none of the caller's marshalling (llmh_plan_run in csrc/host/plan_run.cpp), in the way
+// MythEclipse/llm's layer loop calls its kernels from native code (apps/engine/src/model.rs:755-825).
+union llmb_slot {
+    void* p;
+    long long i;
+    double f;
+};
+
+namespace llmb {
+template <typename T>
+inline T slot_as(const llmb_slot& s) {
+    if constexpr (std::is_pointer<T>::value) return reinterpret_cast<T>(s.p);
+    else if constexpr (std::is_floating_point<T>::value) return static_cast<T>(s.f);
+    else return static_cast<T>(s.i);
+}
+template <typename R, typename... A, size_t... I>
+inline R call_packed(R (*fn)(A...), const llmb_slot* a, std::index_sequence<I...>) {
+    return fn(slot_as<A>(a[I])...);
+}
+template <typename R, typename... A>
+inline R call_packed(R (*fn)(A...), const llmb_slot* a) {
+    return call_packed(fn, a, std::index_sequence_for<A...>{});
+}
+}  // namespace llmb
+
+#define LLMB_PACKED(name) \
+    LLMB_EXPORT int name##_packed(const llmb_slot* args) { return llmb::call_packed(name, args); }
 
 // Each .cu file is built into a library of its own and defines its own reader
 // of the calling thread's last error text.

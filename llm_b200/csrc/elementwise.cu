@@ -555,3 +555,12 @@ LLMB_EXPORT int llmb_random_normal(void* out, int dtype, long long n, unsigned l
         return fail(LLMB_ERR_ARGUMENT, "random_normal: unknown dtype %d", dtype);
     return check_launch("random_normal");
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_embed)
+LLMB_PACKED(llmb_rmsnorm)
+LLMB_PACKED(llmb_cast_sumsq)
+LLMB_PACKED(llmb_scale_rows)
+LLMB_PACKED(llmb_rope_cache_write)
+LLMB_PACKED(llmb_scale)
+LLMB_PACKED(llmb_swiglu)

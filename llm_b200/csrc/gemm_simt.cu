@@ -153,3 +153,6 @@ LLMB_EXPORT int llmb_gemm_simt(const void* a, const void* w, const float* bias, 
     }
     return fail(LLMB_ERR_ARGUMENT, "gemm_simt: unknown dtypes %d -> %d", in_dtype, out_dtype);
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_gemm_simt)

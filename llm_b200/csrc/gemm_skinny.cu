@@ -304,3 +304,6 @@ LLMB_EXPORT int llmb_gemm_skinny_static(const void* x, int ldx, const void* w, c
                             (long long)LLMB_GEMM_SKINNY_STATIC_FLOATS * 4, static_counters_at[device],
                             LLMB_GEMM_SKINNY_STATIC_COUNTERS, M, N, K, ldo, stream);
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_gemm_skinny)

@@ -1341,3 +1341,7 @@ LLMB_EXPORT int llmb_gemm_tc(const void* x, int ldx, const void* w, const float*
     return llmb_gemm_tc_ex(x, ldx, w, bias, out, out_dtype, residual, partials, partial_floats, counters,
                            n_counters, M, N, K, ldo, glu, allow_pair, nullptr, nullptr, stream);
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_gemm_tc_ex)
+LLMB_PACKED(llmb_gemm_tc)

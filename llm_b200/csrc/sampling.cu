@@ -422,3 +422,7 @@ LLMB_EXPORT int llmb_sample_rows(float* logits, int stride, int n_rows, int voca
         recent_cap, rng, out, status, record, state_rows);
     return check_launch("sample_rows");
 }
+
+// the packed doors of the launching entry points (common.cuh)
+LLMB_PACKED(llmb_argmax_rows)
+LLMB_PACKED(llmb_sample_rows)

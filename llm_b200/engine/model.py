@@ -76,6 +76,20 @@ class DecoderModel:
         from ..ops import tactics
         return tactics.plan_identity((family, shape) for _, family, shape in self.kernel_shapes(dtype))
 
+    def replay_key(self, step, n_rows: int):
+        """The key under which a pass may be run again from its record (Part.replay_key), or None
+        if a part of the model does not allow it."""
+        keys = []
+        for block in self.blocks:
+            key = block.replay_key(step)
+            if key is None:
+                return None
+            keys.append(key)
+        final = self.final_norm.replay_key(step)
+        if final is None:
+            return None
+        return (step.n_tokens, step.n_seqs, n_rows, tuple(keys), final)
+
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
 

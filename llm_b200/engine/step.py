@@ -28,6 +28,9 @@ from .workspace import Workspace
 
 GRAPH_AFTER_STEPS = 2      # plain steps of a shape before it is captured
 MAX_GRAPHS = 128           # captured shapes (batch size, bucket of pages) an engine keeps
+RECORD_AFTER_PASSES = 1    # plain passes of a shape before the next one is recorded
+MAX_RECORDS = 32           # recorded passes an engine keeps
+MAX_RECORDED_LOGITS = 1 << 25   # a recorded pass holds its logits buffer: none for more values than this
 
 
 @dataclass
@@ -36,6 +39,17 @@ class Entry:
     slot: int
     tokens: list                 # its next tokens (at least one)
     want: list                   # indices into `tokens` whose logits are wanted
+
+
+@dataclass
+class _HostStep:
+    """The host-side fields of a StepContext, known before anything is on the device."""
+    n_tokens: int
+    n_seqs: int
+    decode: bool
+    new_counts: list
+    starts: list
+    max_len: int
 
 
 class _Batch:
@@ -108,6 +122,12 @@ class Engine:
                            and not ops.PROFILING
                            and getattr(model, "graph_safe", lambda: False)())
         self._graphs, self._graph_seen, self._graph_pool = {}, {}, None
+        # passes that are not replayed from a graph (prompts, mixed steps, the first steps of a
+        # decode shape) are recorded per shape and then walked by the native host library
+        self.use_records = (self.device.type == "cuda" and not ops.PROFILING
+                            and os.environ.get("LLMB_NO_RECORDS", "0") in ("", "0"))
+        self._records, self._record_seen = {}, {}
+        self.records_run = 0
         self._ring, self._ring_at = [(None, None)] * 4, 0
 
     # ------------------------------------------------------------------ sequences
@@ -217,8 +237,14 @@ class Engine:
             return ctx, view(0), view(6)
 
         logits = None
-        if self.use_graphs and decode and all(e.want == [0] for e in entries):
+        graphable = self.use_graphs and decode and all(e.want == [0] for e in entries)
+        if graphable:
             logits = self._replay(len(entries), max_len, host, total, context, device_tokens)
+        if logits is None and self.use_records and not graphable:
+            step = _HostStep(n_tokens, batch.n, decode, counts, starts, max_len)
+            key = self.model.replay_key(step, sizes[6])
+            if key is not None and sizes[6] * self.vocab <= MAX_RECORDED_LOGITS:
+                logits = self._run_recorded(key, batch.n, host, total, context, device_tokens)
         if logits is None:
             dev = host[:max(total, 4)].to(self.device, non_blocking=True)
             self._host_done(host)
@@ -229,6 +255,56 @@ class Engine:
         native.check(lib.llmh_step_commit(cache, batch.n, batch.slots, batch.counts))
         self.steps_run += 1
         return logits
+
+    # ------------------------------------------------------------------ recorded passes
+
+    def _run_recorded(self, key, n_seqs, host, total, context, device_tokens):
+        """Run the pass from the record of an earlier pass with the same key (Part.replay_key), or
+        record it while it runs (from the second pass of that key on), or return None (the first).
+        A record is the list of the pass's launches with their arguments; the native host library
+        makes them again in one call (ops.RecordedPass), where the layer loop of
+        apps/engine/src/model.rs:755-825 runs natively as a whole. Every value that differs between
+        two passes of one key (tokens, positions, lengths, slots, pages, wanted rows) lies in the
+        record's own device buffer, which is refreshed before the launches."""
+        from ..ops import tactics
+        stamp = (ops.scratch_generation(), tactics.generation,
+                 self.workspace.arena.data_ptr() if self.workspace.arena is not None else 0)
+        held = self._records.get(key)
+        if held is not None and held[3] != stamp:
+            del self._records[key]
+            held = None
+        if held is None:
+            seen = self._record_seen.get(key, 0) + 1
+            self._record_seen[key] = seen
+            if len(self._record_seen) > 4096:
+                self._record_seen.clear()
+            if seen <= RECORD_AFTER_PASSES:
+                return None
+            meta = torch.zeros(max(total, 4), dtype=torch.int32, device=self.device)
+            meta[:total].copy_(host[:total], non_blocking=True)
+            self._host_done(host)
+            ctx, tokens_dev, rows_dev = context(meta)
+            if device_tokens is not None:
+                tokens_dev.copy_(device_tokens)
+            recording = ops.begin_recording()
+            try:
+                logits = self.model.forward(tokens_dev, ctx, rows_dev)
+            finally:
+                ops.end_recording()
+            # the arena may have grown while this pass was planned: the stamp is taken afterwards
+            stamp = (ops.scratch_generation(), tactics.generation, self.workspace.arena.data_ptr())
+            if len(self._records) >= MAX_RECORDS:
+                self._records.pop(next(iter(self._records)))
+            self._records[key] = (ops.RecordedPass(recording), meta, logits, stamp)
+            return logits.clone()
+        plan, meta, logits, _ = held
+        meta[:total].copy_(host[:total], non_blocking=True)
+        self._host_done(host)
+        if device_tokens is not None:
+            meta[:n_seqs].copy_(device_tokens)               # the tokens are the buffer's first section
+        plan.run()
+        self.records_run += 1
+        return logits.clone()
 
     # ------------------------------------------------------------------ host staging
 

@@ -77,6 +77,10 @@ _SIGNATURES = {
     "llmh_tactics_is_disabled": (c_int, [c_char_p]),
     "llmh_tactics_rows": (c_int, [c_int]),
     "llmh_tactics_row": (c_int, [c_int, c_int, POINTER(c_char_p), _INTS, POINTER(c_char_p)]),
+    "llmh_plan_create": (c_int, [c_int, POINTER(_P), _INTS, _INTS, _P, POINTER(_P)]),
+    "llmh_plan_destroy": (None, [_P]),
+    "llmh_plan_size": (c_int, [_P]),
+    "llmh_plan_run": (c_int, [_P, _P, _INTS]),
     "llmh_random_normal": (c_int, [_P, c_int, c_longlong, ctypes.c_ulonglong, ctypes.c_float, ctypes.c_float]),
     "llmh_safetensors_open": (c_int, [c_char_p, POINTER(_P)]),
     "llmh_safetensors_close": (None, [_P]),

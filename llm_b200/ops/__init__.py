@@ -41,6 +41,8 @@ def _code(dtype) -> int:
 def _ptr(t):
     if t is None:
         return None
+    if _recording is not None:
+        _recording.keep.append(t)          # a recorded pass points at this tensor: it must outlive the record
     return ctypes.c_void_p(t.data_ptr())
 
 
@@ -115,10 +117,108 @@ if PROFILING:
     atexit.register(_report_profile)
 
 
+# ----------------------------------------------------------------------------- recorded passes
+
+_recording = None           # the Recording that launches are being entered into, or None
+_scratch_generation = 0     # grows when a scratch buffer that recorded passes point at is replaced
+
+
+class Recording:
+    """The launches of one pass as they were made: (library, entry point, ctypes arguments)."""
+
+    def __init__(self):
+        self.calls, self.keep, self.kernels = [], [], 0
+
+
+def begin_recording() -> Recording:
+    """From here on every launch of this module is also entered into the returned Recording
+    (it still runs), until end_recording()."""
+    global _recording
+    _recording = Recording()
+    return _recording
+
+
+def end_recording() -> None:
+    global _recording
+    _recording = None
+
+
+class RecordedPass:
+    """A Recording turned into a native plan (csrc/host/plan_run.cpp): `run()` makes the same
+    launches with the same arguments on the current stream through the entry points' packed
+    doors, in one call of the native host library. The tensors the launches point at are kept
+    alive here. Valid while no scratch buffer of this module was replaced
+    (`scratch_generation`)."""
+
+    def __init__(self, recording: Recording):
+        doors, counts, stream_slots, slots = [], [], [], []
+        self._keep = [recording.keep]
+        for lib_name, fn_name, args in recording.calls:
+            lib = load_library(lib_name)
+            door = ctypes.cast(getattr(lib, fn_name + "_packed"), ctypes.c_void_p).value
+            doors.append(door)
+            counts.append(len(args))
+            stream_slots.append(len(args) - 1)            # every launching entry point ends with its stream
+            for a in args:
+                slots.append(self._slot(a))
+        n = len(doors)
+        block = (ctypes.c_ulonglong * max(len(slots), 1))(*slots)
+        handle = ctypes.c_void_p()
+        native.check(native.lib().llmh_plan_create(
+            n, (ctypes.c_void_p * max(n, 1))(*doors), native.ints(counts), native.ints(stream_slots),
+            ctypes.cast(block, ctypes.c_void_p), ctypes.byref(handle)))
+        self._handle = handle
+        self.kernels = recording.kernels
+        self.launches = n
+        self.scratch_generation = _scratch_generation
+        self._libraries = [c[0] for c in recording.calls]
+        self._failed = ctypes.c_int(-1)
+
+    def _slot(self, a) -> int:
+        """The 8-byte slot of a ctypes argument: an address, a widened integer, or a double's bits."""
+        if a is None:
+            return 0
+        if isinstance(a, ctypes.c_void_p):
+            return a.value or 0
+        if isinstance(a, (ctypes.c_int, ctypes.c_longlong, ctypes.c_ulonglong)):
+            return a.value & 0xFFFFFFFFFFFFFFFF
+        if isinstance(a, ctypes.c_float):
+            return ctypes.c_ulonglong.from_buffer_copy(ctypes.c_double(a.value)).value
+        target = getattr(a, "_obj", None)                 # byref(structure): the structure lives on here
+        if target is not None:
+            self._keep.append(target)
+            return ctypes.addressof(target)
+        raise KernelError(f"a launch argument of type {type(a).__name__} cannot be recorded")
+
+    def __del__(self):
+        handle = getattr(self, "_handle", None)
+        if handle and native is not None:                 # (modules are gone when the interpreter ends)
+            native.lib().llmh_plan_destroy(handle)
+            self._handle = None
+
+    def run(self) -> None:
+        global _launches
+        code = native.lib().llmh_plan_run(self._handle, _stream(), ctypes.byref(self._failed))
+        _launches += self.kernels
+        if code != 0:
+            lib_name = self._libraries[self._failed.value]
+            reader = getattr(load_library(lib_name), f"llmb_{lib_name}_last_error")
+            reader.restype = ctypes.c_char_p
+            raise KernelError(f"recorded launch {self._failed.value} ({lib_name}): "
+                              f"{reader().decode('utf-8', 'replace')}")
+
+
+def scratch_generation() -> int:
+    return _scratch_generation
+
+
 def _call(lib_name: str, fn_name: str, *args, kernels: int = 1):
     global _launches
     lib = load_library(lib_name)
     _launches += kernels
+    if _recording is not None:
+        _recording.calls.append((lib_name, fn_name, args))
+        _recording.kernels += kernels
     if PROFILING and not torch.cuda.is_current_stream_capturing():
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
@@ -312,8 +412,10 @@ def _split_scratch(device, floats: int, counters: int):
     if held is None or held[0].numel() < floats or held[1].numel() < counters:
         n_floats = max(floats, held[0].numel() if held else 0, 1 << 23)
         n_counters = max(counters, held[1].numel() if held else 0, 1 << 14)
+        global _scratch_generation
         if held is not None:
             _retired.append(held)
+            _scratch_generation += 1
         held = (torch.empty(n_floats, dtype=torch.float32, device=device),
                 torch.zeros(n_counters, dtype=torch.int32, device=device))
         _scratch[device] = held
@@ -592,7 +694,9 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
         scratch = _attention_scratch.get(qkv.device)
         if scratch is None or scratch.numel() < need:
             if scratch is not None:
+                global _scratch_generation
                 _retired.append(scratch)
+                _scratch_generation += 1
             scratch = torch.empty(max(need, 1 << 23), dtype=torch.float32, device=qkv.device)
             _attention_scratch[qkv.device] = scratch
         _call("attention_decode", "llmb_attention_decode", _ptr(qkv), _c_int(qkv.stride(0)),
@@ -650,6 +754,6 @@ def required_libraries() -> list:
             "attention_decode", "attention_prefill", "attention_prefill_tc", "sampling"]
 
 
-__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
+__all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "begin_recording", "end_recording", "RecordedPass", "scratch_generation", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

@@ -42,17 +42,22 @@ def rows(family: str) -> list:
 
 
 _chosen: dict = {}       # arguments of a choice -> the variant's name, until a variant is switched
+generation = 0           # grows whenever a variant is switched on or off (recorded passes are then stale)
 
 
 def disable(name: str) -> None:
     """Take a variant out of the choice (tests use it to reach a fallback)."""
+    global generation
     native.lib().llmh_tactics_set_disabled(name.encode(), 1)
     _chosen.clear()
+    generation += 1
 
 
 def enable(name: str) -> None:
+    global generation
     native.lib().llmh_tactics_set_disabled(name.encode(), 0)
     _chosen.clear()
+    generation += 1
 
 
 def is_disabled(name: str) -> bool:

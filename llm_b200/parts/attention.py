@@ -90,6 +90,14 @@ class AttentionMixer(Mixer):
     def kv_request(self):
         return KvRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def replay_key(self, step):
+        """The attention kernels size their grids by the most new tokens of a sequence (prefill) or
+        by the slices of the longest sequence (decode); positions, lengths and pages come from
+        device arrays."""
+        if step.decode:
+            return (True, ops.decode_splits(step.n_seqs, self.spec.n_kv_heads, step.max_len))
+        return (False, max(step.new_counts))
+
     def forward(self, h, ctx, entry, cache_entry, residual, emit=None):
         s = self.spec
         group, keys, values = ctx.cache.layer_view(cache_entry)

@@ -70,6 +70,16 @@ class Part:
         """tensor name -> ParamSpec of everything this part binds."""
         return {}
 
+    def replay_key(self, step):
+        """None (the default): a recorded pass must not stand in for a later pass of this part.
+        Else a tuple that holds every host-side value of the step (`step` has the host fields of a
+        StepContext: n_tokens, n_seqs, decode, new_counts, starts, max_len) that the arguments of
+        this part's launches depend on, beyond n_tokens and n_seqs; everything else the part's
+        kernels read from the context's device arrays. Two passes with equal keys then make the
+        same launches with the same arguments, and the engine may run the second from the record
+        of the first, walked by the native host library."""
+        return None
+
     def fold_input_norm(self, gain) -> bool:
         """Offered by the block after `bind`, where the norm in front of this part is an RMS norm
         (y = x / sqrt(mean(x^2) + eps) * gain): take `gain` (float32 [hidden]) into the weights

@@ -66,6 +66,10 @@ class PreNormBlock(Block):
             return False
         return bool(part.fold_input_norm(norm.gain))
 
+    def replay_key(self, step):
+        keys = [p.replay_key(step) for p in self.parts]
+        return None if any(k is None for k in keys) else tuple(keys)
+
     def input_emit(self, ctx, n_tokens: int, device):
         """Where the product that last updates the residual before this block leaves the folded
         mixer norm's input (None: the mixer norm is a kernel of its own)."""

@@ -70,6 +70,9 @@ class GatedMlp(FeedForward):
             return [act]
         return [BufferRequest("gate_up", (n_tokens, 2 * s.intermediate), dtype, 0, 1), act]
 
+    def replay_key(self, step):
+        return ()
+
     def forward(self, h, ctx, residual, emit=None):
         norm = h if isinstance(h, ops.FoldedNorm) else None
         if norm is not None:

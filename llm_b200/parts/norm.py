@@ -24,6 +24,9 @@ class RmsNorm(Norm):
     def bind(self, tensors, dtype, device):
         self.gain = to_float32(tensors[self.spec.weight], device)
 
+    def replay_key(self, step):
+        return ()
+
     def forward(self, x, out_dtype, rows=None, out=None):
         return ops.rmsnorm(x, self.gain, self.spec.eps, out_dtype, rows, out=out)
 

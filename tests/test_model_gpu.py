@@ -437,3 +437,34 @@ def test_family_size_layers_against_the_plain_implementation(tmp_path, dtype):
         assert [int(r.argmax()) for r in want[:-1]] == tokens[64:]
     else:
         assert close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["B", "F"])
+def test_passes_walked_from_their_record_equal_plain_passes(folders, plain, dtype, which):
+    """The second pass of a shape is recorded, later ones are made again by the native host library
+    from that record. Chunks of equal size of different prompts at different positions, on
+    different slots and pages, through a record and without one: bit-equal logits, and equal to
+    the plain implementation. A pass of another shape in between leaves the record valid."""
+    config, weights = plain[which]
+    recorded = engine_for(folders[which], dtype, step_tokens=40)
+    direct = engine_for(folders[which], dtype, step_tokens=40, use_graphs=False)
+    direct.use_records = False
+    seqs = [random_tokens(160, config["vocab_size"], 500 + i) for i in range(3)]
+    for round_index, tokens in enumerate(seqs):
+        expected = plain_llama.forward(config, weights, tokens)
+        if round_index == 1:
+            filler = recorded.acquire(2)                 # other slots and pages for the next round
+        (slot,), (other,) = recorded.acquire(), direct.acquire()
+        want = list(range(0, 160, 3))
+        got = recorded.step([(slot, tokens, want)])      # four passes of 40 tokens
+        same = direct.step([(other, tokens, want)])
+        assert torch.equal(got, same)
+        assert close(got, expected[want], dtype)
+        if round_index == 0:
+            recorded.step([(slot, [tokens[0]] * 7, [6])])        # another shape in between
+            direct.step([(other, [tokens[0]] * 7, [6])])
+        recorded.release([slot])
+        direct.release([other])
+    assert recorded.records_run >= 8 and direct.records_run == 0
+    recorded.cache.check()

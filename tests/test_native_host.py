@@ -211,3 +211,45 @@ def test_json_reader_gives_the_values_python_would(tmp_path):
     (tmp_path / "config.json").write_text('{"architectures": ["LlamaForCausalLM"],')
     with pytest.raises(FormatError, match="not JSON"):
         load_config(tmp_path)
+
+
+def test_a_plan_calls_its_doors_in_order_with_their_slots_and_stops_at_a_failure():
+    """llmh_plan_run (csrc/host/plan_run.cpp) with doors made here: every door gets its own block of
+    8-byte slots, the stream is written into the slot that was named for it, and the first non-zero
+    code ends the walk with the index of the launch that returned it."""
+    import ctypes
+    from llm_b200 import native
+    lib = native.lib()
+    seen = []
+    DOOR = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong))
+
+    def make(n_slots, code=0):
+        def door(slots):
+            seen.append([slots[i] for i in range(n_slots)])
+            return code
+        return DOOR(door)
+
+    doors = [make(3), make(1), make(2)]
+    slots = (ctypes.c_ulonglong * 6)(11, 12, 0, 0, 21, 0)
+    handle = ctypes.c_void_p()
+    native.check(lib.llmh_plan_create(
+        3, (ctypes.c_void_p * 3)(*[ctypes.cast(d, ctypes.c_void_p).value for d in doors]),
+        native.ints([3, 1, 2]), native.ints([2, 0, -1]), ctypes.cast(slots, ctypes.c_void_p), ctypes.byref(handle)))
+    assert lib.llmh_plan_size(handle) == 3
+    failed = ctypes.c_int(7)
+    assert lib.llmh_plan_run(handle, ctypes.c_void_p(0xABC0), ctypes.byref(failed)) == 0 and failed.value == -1
+    assert seen == [[11, 12, 0xABC0], [0xABC0], [21, 0]]
+    lib.llmh_plan_destroy(handle)
+    # a door that fails ends the walk
+    seen.clear()
+    doors = [make(1), make(1, code=5), make(1)]
+    native.check(lib.llmh_plan_create(
+        3, (ctypes.c_void_p * 3)(*[ctypes.cast(d, ctypes.c_void_p).value for d in doors]),
+        native.ints([1, 1, 1]), native.ints([-1, -1, -1]), ctypes.cast((ctypes.c_ulonglong * 3)(1, 2, 3), ctypes.c_void_p),
+        ctypes.byref(handle)))
+    assert lib.llmh_plan_run(handle, None, ctypes.byref(failed)) == 5 and failed.value == 1
+    assert seen == [[1], [2]]
+    lib.llmh_plan_destroy(handle)
+    with pytest.raises(Exception):
+        native.check(lib.llmh_plan_create(1, (ctypes.c_void_p * 1)(None), native.ints([1]), native.ints([0]),
+                                          ctypes.cast(slots, ctypes.c_void_p), ctypes.byref(handle)))
