@@ -874,7 +874,8 @@ constexpr int PAIR_BN = 256;        // columns of the pair's tile; each block lo
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    Epilogue ep, int n_kblocks, int tiles_a, int n_units, int* status, int stages) {
+                    const __grid_constant__ CUtensorMap map_residual, Epilogue ep, int n_kblocks, int tiles_a,
+                    int n_units, int* status, int stages, int residual_by_tma) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = (PAIR_BN / 2) * BK * 2;
     constexpr int TMEM_COLS = 2 * PAIR_BN;
@@ -890,6 +891,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     __shared__ float rstd_s[2][BM];                   // scales of this block's 128 token rows (a folded norm)
+    // Adding into the residual: accumulator pieces of 128 rows x 32 columns leave through two 16 KB
+    // staging buffers behind the ring, and the copy engine adds them into the 32-bit matrix
+    // (cp.reduce.async.bulk.tensor). Reading the old values into registers, 64 bytes a lane and one
+    // chunk after the other, cost the last tile of every block some 16 us of load latency.
+    float* staging = reinterpret_cast<float*>(base + (size_t)stages * (A_BYTES + B_BYTES) + 1024);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t rank = cluster_rank();
@@ -1037,6 +1043,46 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                 }
+            } else if (residual_by_tma) {
+                float scale = rstd ? rstd[row] : 1.f;
+                int tile_row0 = w.tile_a * 2 * BM + (int)rank * BM;
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c, r);
+                    int n0 = w.tile_b * PAIR_BN + c;
+                    float* buffer_s = staging + ((c >> 5) & 1) * (BM * 32);
+                    // the copy that last read this buffer (two pieces ago) must be done with it
+                    if (threadIdx.x == 64) bulk_wait_read<1>();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (n0 < ep.outs) {
+                        // row `row` of the piece: eight 16-byte chunks, chunk q at place q ^ (row % 8)
+                        // (the 128-byte swizzle of the tensor map; also spreads the lanes over the banks)
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            float4 piece;
+                            piece.x = __uint_as_float(r[4 * q]) * scale;
+                            piece.y = __uint_as_float(r[4 * q + 1]) * scale;
+                            piece.z = __uint_as_float(r[4 * q + 2]) * scale;
+                            piece.w = __uint_as_float(r[4 * q + 3]) * scale;
+                            if (ep.bias) {
+                                int n = n0 + 4 * q;
+                                piece.x += n < ep.outs ? ep.bias[n] : 0.f;
+                                piece.y += n + 1 < ep.outs ? ep.bias[n + 1] : 0.f;
+                                piece.z += n + 2 < ep.outs ? ep.bias[n + 2] : 0.f;
+                                piece.w += n + 3 < ep.outs ? ep.bias[n + 3] : 0.f;
+                            }
+                            *reinterpret_cast<float4*>(buffer_s + row * 32 + ((q ^ (row & 7)) << 2)) = piece;
+                        }
+                    }
+                    fence_async_shared();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (threadIdx.x == 64) {
+                        if (n0 < ep.outs && tile_row0 < ep.tokens)
+                            tma_reduce_add_2d(&map_residual, smem_u32(buffer_s), n0, tile_row0);
+                        bulk_commit();
+                    }
+                }
             } else {
 #pragma unroll 1
                 for (int c = 0; c < PAIR_BN; c += 16) {
@@ -1054,6 +1100,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     }
 
+    if (threadIdx.x == 64) bulk_wait<0>();            // the copy engine is done with the staging buffers
     tcgen05_fence_before();
     __syncthreads();
     if (*abort_flag) {
@@ -1133,13 +1180,23 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& ep, int tiles_a,
                 int tiles_b, int n_kblocks, cudaStream_t stream) {
     constexpr int STAGE_BYTES = BM * BK * 2 + (PAIR_BN / 2) * BK * 2;
-    int stages = (200 * 1024) / STAGE_BYTES;
+    int stages = (192 * 1024) / STAGE_BYTES;
     if (stages > 8) stages = 8;
-    size_t smem = 1024 + (size_t)stages * STAGE_BYTES + (2 * stages + 4) * 8 + 16;
+    // ring | 1 KB: barriers and control words | two staging buffers of 128 rows x 32 floats for the
+    // residual epilogue (1024-byte aligned, as the swizzle wants)
+    size_t smem = 1024 + (size_t)stages * STAGE_BYTES + 1024 + 2 * (size_t)BM * 32 * 4;
     static bool configured = false;
     if (!configured) {
         LLMB_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
+    }
+    // the residual through the copy engine where a tensor map can describe it
+    CUtensorMap map_residual = map_a;
+    int residual_by_tma = 0;
+    if (ep.residual && !ep.glu && ep.ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(ep.residual) & 15) == 0) {
+        int code = make_map_2d_f32(&map_residual, ep.residual, ep.tokens, ep.outs, ep.ldo, BM);
+        if (code) return code;
+        residual_by_tma = 1;
     }
     static int n_sms = 0;
     if (n_sms == 0) {
@@ -1152,8 +1209,8 @@ int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilog
     if (status) cudaHostGetDevicePointer((void**)&status_dev, status, 0);
     int n_units = tiles_a * tiles_b;
     int pairs = n_units < n_sms / 2 ? n_units : n_sms / 2;
-    llmb::launch(gemm_tc_pair_kernel, 2 * pairs, THREADS, smem, stream, true, map_a, map_b, ep, n_kblocks, tiles_a,
-                 n_units, status_dev, stages);
+    llmb::launch(gemm_tc_pair_kernel, 2 * pairs, THREADS, smem, stream, true, map_a, map_b, map_residual, ep,
+                 n_kblocks, tiles_a, n_units, status_dev, stages, residual_by_tma);
     return check_launch("gemm_tc_pair");
 }
 

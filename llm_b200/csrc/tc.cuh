@@ -214,5 +214,37 @@ inline int make_map_2d(CUtensorMap* map, const void* ptr, long long rows, long l
     return LLMB_OK;
 }
 
+// float32 [rows, cols] with `ld` elements between rows; boxes of 32 columns (128 bytes) x box_rows,
+// 128-byte swizzle: the target of an epilogue that adds accumulator tiles into a 32-bit matrix
+inline int make_map_2d_f32(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld,
+                           int box_rows) {
+    EncodeTiled encode = encode_fn();
+    if (!encode) return fail(LLMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides,
+                        box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LLMB_ERR_CUDA, "cuTensorMapEncodeTiled (float32) failed with %d", (int)r);
+    return LLMB_OK;
+}
+
+// out[box at (x, y)] += the box in shared memory (element-wise 32-bit add done by the copy engine;
+// rows and columns beyond the tensor are dropped). x must be a multiple of 4 elements.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+        ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until at most `N` of this thread's committed groups are still reading their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 }  // namespace tc
 }  // namespace llmb
