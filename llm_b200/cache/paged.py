@@ -10,8 +10,10 @@ serves a batch:
 * a *slot* is one live sequence with its own length;
 * layers are put in *groups* by what they need: `full` (every earlier key) or
   `window` (the last w keys, kept in a ring of pages). Each group has its own
-  page pool [layers, 2, pages, kv heads, 64, head_dim] and, per slot, its own
-  list of pages: logical page i of a sequence is `pages[i % ring]`;
+  page pool [layers, 2, pages, kv heads, 64, head_dim] (or, for a mixer whose
+  values are wider or narrower than its keys, one tensor for the keys and one
+  for the values) and, per slot, its own list of pages: logical page i of a
+  sequence is `pages[i % ring]`;
 * `state` tensors [slots, ...] hold what a mixer keeps per sequence at a fixed
   size; a slot's rows are zeroed when the slot is taken.
 
@@ -42,10 +44,12 @@ class KvRequest:
     n_kv_heads: int
     head_dim: int
     window: int = 0            # 0: keep every position
+    value_dim: int | None = None   # width of a value, where it differs from a key's (None: head_dim)
 
     @property
     def group_key(self):
-        return ("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window)
+        return ("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window,
+                self.value_dim or self.head_dim)
 
 
 @dataclass(frozen=True)
@@ -84,10 +88,13 @@ class Group:
     n_kv_heads: int
     head_dim: int
     window: int
+    value_dim: int = 0                                # width of a value (== head_dim unless a mixer asks otherwise)
     entries: list = field(default_factory=list)     # schedule positions that own storage here
     ring_pages: int = 0                               # logical pages per sequence
     pool: FreeList | None = None
-    storage: torch.Tensor | None = None               # [entries, 2, pages, Hkv, PAGE, D]
+    storage: torch.Tensor | None = None               # [entries, 2, pages, Hkv, PAGE, D] (keys and values alike)
+    keys: torch.Tensor | None = None                  # [entries, pages, Hkv, PAGE, D] and
+    values: torch.Tensor | None = None                # [entries, pages, Hkv, PAGE, value_dim] where they differ
     slot_pages: _SlotPages | None = None              # slot -> list of physical pages
 
 
@@ -116,7 +123,8 @@ class PagedCache:
             key = request.group_key
             if key not in by_key:
                 by_key[key] = len(self.groups)
-                self.groups.append(Group(key[0], request.n_kv_heads, request.head_dim, request.window))
+                self.groups.append(Group(key[0], request.n_kv_heads, request.head_dim, request.window,
+                                         request.value_dim or request.head_dim))
             g = by_key[key]
             self.entry_group.append((g, len(self.groups[g].entries)))
             self.groups[g].entries.append(entry)
@@ -135,9 +143,14 @@ class PagedCache:
             group.pool = FreeList(n_pages.value, f"page of the {group.kind} group",
                                   _borrowed=lib.llmh_cache_list(handle, g), _owner=self)
             group.slot_pages = _SlotPages(self, g)
-            group.storage = torch.zeros(
-                (len(group.entries), 2, n_pages.value, group.n_kv_heads, PAGE, group.head_dim),
-                dtype=dtype, device=self.device)
+            if group.value_dim == group.head_dim:
+                group.storage = torch.zeros(
+                    (len(group.entries), 2, n_pages.value, group.n_kv_heads, PAGE, group.head_dim),
+                    dtype=dtype, device=self.device)
+            else:
+                shape = (len(group.entries), n_pages.value, group.n_kv_heads, PAGE)
+                group.keys = torch.zeros(shape + (group.head_dim,), dtype=dtype, device=self.device)
+                group.values = torch.zeros(shape + (group.value_dim,), dtype=dtype, device=self.device)
         self.states = []
         for request in states:
             if request is None:
@@ -213,8 +226,10 @@ class PagedCache:
         if where is None:
             return None
         g, i = where
-        storage = self.groups[g].storage
-        return g, storage[i, 0], storage[i, 1]
+        group = self.groups[g]
+        if group.storage is None:
+            return g, group.keys[i], group.values[i]
+        return g, group.storage[i, 0], group.storage[i, 1]
 
     def state_view(self, entry: int):
         return self.states[entry]
@@ -224,7 +239,8 @@ class PagedCache:
         return native.lib().llmh_cache_held_tokens(self._handle)
 
     def bytes(self) -> int:
-        total = sum(g.storage.numel() * g.storage.element_size() for g in self.groups)
+        total = sum(t.numel() * t.element_size() for g in self.groups
+                    for t in (g.storage, g.keys, g.values) if t is not None)
         total += sum(s.numel() * s.element_size() for s in self.states if s is not None)
         return total
 

@@ -124,3 +124,27 @@ def test_can_hold_counts_pages_and_slots():
     assert cache.can_hold([64 * 4]) and not cache.can_hold([64 * 4, 1, 1, 1])
     cache.set_length(s, 130)
     assert cache.held_tokens() == 192
+
+
+def test_keys_and_values_of_different_widths_get_storage_of_their_own():
+    """A mixer may keep values that are wider or narrower than its keys: such runs form a group of
+    their own with one tensor for the keys and one for the values, beside the groups of the rest."""
+    import torch
+    from llm_b200.cache import KvRequest, PagedCache
+    requests = [KvRequest(2, 16), KvRequest(2, 16, value_dim=24), KvRequest(2, 16), KvRequest(2, 16, value_dim=24)]
+    cache = PagedCache(requests, [None] * 4, max_tokens=256, max_seq_len=128, max_slots=2,
+                       dtype=torch.float32, device="cpu")
+    assert len(cache.groups) == 2 and [g.value_dim for g in cache.groups] == [16, 24]
+    g0, k0, v0 = cache.layer_view(0)
+    g1, k1, v1 = cache.layer_view(1)
+    g3, k3, v3 = cache.layer_view(3)
+    assert (g0, g1, g3) == (0, 1, 1)
+    assert k0.shape == v0.shape == (4, 2, 64, 16)
+    assert k1.shape == (4, 2, 64, 16) and v1.shape == (4, 2, 64, 24)
+    assert k1.data_ptr() != k3.data_ptr() and v1.data_ptr() != v3.data_ptr()
+    assert cache.bytes() == 4 * (2 * 2 * 4 * 2 * 64 * 16 + 2 * 4 * 2 * 64 * (16 + 24))
+    slot = cache.acquire()
+    cache.reserve(slot, 100)
+    assert len(cache.groups[1].slot_pages[slot]) == 2
+    cache.release(slot)
+    cache.check()
