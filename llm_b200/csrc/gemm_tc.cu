@@ -1241,6 +1241,7 @@ Plan make_plan(int M, int N, int K) {
         int most = p.n_kblocks / 4 > 0 ? p.n_kblocks / 4 : 1; // at least four k-blocks a block
         if (want > most) want = most;
         if (want > 32) want = 32;
+        if (want == 9 || want == 10) want = 8;      // the last block of a tile sums eight splits in one round of loads
         if (want < 1) want = 1;
         p.per_split = (p.n_kblocks + want - 1) / want;
         p.splits = (p.n_kblocks + p.per_split - 1) / p.per_split;
