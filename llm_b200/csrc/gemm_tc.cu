@@ -943,12 +943,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;
+            int s = 0;
+            uint32_t round = 0;                                 // how often the ring has been walked through
             bool ok = true;
             for (int u = pair; u < n_units && ok; u += n_pairs) {
                 Unit w = unit_of(u, tiles_a, 1);
-                for (int kb = 0; kb < n_kblocks; ++kb, ++it) {
-                    int s = it % stages;
-                    uint32_t round = it / stages;
+                for (int kb = 0; kb < n_kblocks; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), round += (s == 0)) {
                     if (it < early) {                           // armed above, the weight tile is in flight
                         tma_load_2d_pair(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a,
                                          map_to_rank(smem_u32(&full_bar[s]), 0), kb * BK,
@@ -972,7 +972,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // D 32-bit, A and B bfloat16, both K-major, N = 256, M = 256 over the pair
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                        ((uint32_t)(PAIR_BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-            uint32_t it = 0, n_done = 0;
+            // This one thread's instructions are the products' pace: per k-block it waits for a barrier and
+            // issues four instructions and a commit. Nothing in the loop divides, reads a clock or builds a
+            // descriptor from scratch: the stage and its phase are counted, the descriptors of stage 0
+            // are made once and a stage adds a constant, and the first k-block (which overwrites the
+            // accumulator) is peeled off so that the others accumulate unconditionally.
+            uint32_t n_done = 0;
+            int s = 0;
+            uint32_t phase = 0;
+            const uint64_t a_desc0 = smem_desc(smem_u32(a_tiles)), b_desc0 = smem_desc(smem_u32(b_tiles));
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             bool ok = true;
             for (int u = pair; u < n_units && ok; u += n_pairs, ++n_done) {
                 uint32_t buffer = n_done & 1, use = n_done >> 1;
@@ -980,18 +989,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!ok) break;
                 tcgen05_fence_after();
                 uint32_t d_tmem = tmem_base + buffer * PAIR_BN;
-                for (int kb = 0; kb < n_kblocks; ++kb, ++it) {
-                    int s = it % stages;
-                    uint32_t round = it / stages;
-                    ok = mbar_wait(smem_u32(&full_bar[s]), round & 1, abort_flag, status, 2);
+                for (int kb = 0; kb < n_kblocks; ++kb) {
+                    ok = mbar_wait(full0 + 8 * s, phase, abort_flag, status, 2);
                     if (!ok) break;
                     tcgen05_fence_after();
-                    uint64_t a_desc = smem_desc(smem_u32(a_tiles + (size_t)s * A_BYTES));
-                    uint64_t b_desc = smem_desc(smem_u32(b_tiles + (size_t)s * B_BYTES));
+                    uint64_t a_desc = a_desc0 + (uint64_t)(s * (A_BYTES >> 4));
+                    uint64_t b_desc = b_desc0 + (uint64_t)(s * (B_BYTES >> 4));
+                    if (kb == 0) {
+                        tcgen05_mma_pair(d_tmem, a_desc, b_desc, idesc, 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tcgen05_mma_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    tcgen05_commit_pair(smem_u32(&empty_bar[s]));      // frees the stage in both blocks
+                        for (int k = 1; k < BK / UMMA_K; ++k) tcgen05_mma_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1u);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) tcgen05_mma_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1u);
+                    }
+                    tcgen05_commit_pair(empty0 + 8 * s);               // frees the stage in both blocks
+                    if (++s == stages) { s = 0; phase ^= 1; }
                 }
                 if (ok) tcgen05_commit_pair(smem_u32(&acc_full_bar[buffer]));
             }

@@ -38,6 +38,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // abort flag and the status word are set).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;      // the common case costs no clock read
     long long start = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
