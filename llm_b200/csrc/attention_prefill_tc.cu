@@ -163,12 +163,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                           ((uint32_t)(BQ >> 4) << 24);
             constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                           ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+            // the descriptors of the tiles' first bytes are made once; a step inside a tile adds a constant
+            // to the address field (this thread's instructions set the pace of the products)
+            const uint64_t q_desc = smem_desc(smem_u32(q_tile)), k_desc = smem_desc(smem_u32(k_tile));
+            const uint64_t v_desc = smem_desc_mn(smem_u32(v_tile), HALF_BYTES);
             auto issue_qk = [&]() {
-                uint32_t q0 = smem_u32(q_tile), k0 = smem_u32(k_tile);
 #pragma unroll
                 for (int j = 0; j < HD / 16; ++j) {
-                    uint32_t off = (uint32_t)((j >> 2) * HALF_BYTES + (j & 3) * 32);
-                    tcgen05_mma(tmem_base + S_COL, smem_desc(q0 + off), smem_desc(k0 + off), idesc_qk, j > 0 ? 1u : 0u);
+                    uint64_t off = (uint64_t)(((j >> 2) * HALF_BYTES + (j & 3) * 32) >> 4);
+                    tcgen05_mma(tmem_base + S_COL, q_desc + off, k_desc + off, idesc_qk, j > 0 ? 1u : 0u);
                 }
                 tcgen05_commit(smem_u32(s_full));
                 tcgen05_commit(smem_u32(k_empty));
@@ -184,11 +187,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                      mbar_wait(smem_u32(v_full), kb & 1, abort_flag, status, 16);
                 if (!ok) break;
                 tcgen05_fence_after();
-                uint32_t v0 = smem_u32(v_tile);
 #pragma unroll
                 for (int j = 0; j < BKV / 16; ++j)        // 16 keys a step: 8 columns of P, 2048 bytes of V rows
                     tcgen05_mma_ts(tmem_base + O_COL, tmem_base + P_COL + j * 8,
-                                   smem_desc_mn(v0 + j * 2048, HALF_BYTES), idesc_pv, (kb > 0 || j > 0) ? 1u : 0u);
+                                   v_desc + (uint64_t)((j * 2048) >> 4), idesc_pv, (kb > 0 || j > 0) ? 1u : 0u);
                 tcgen05_commit(smem_u32(o_full));
                 tcgen05_commit(smem_u32(v_empty));
                 if (kb + 1 < n_blocks) {

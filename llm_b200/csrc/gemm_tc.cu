@@ -439,14 +439,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;                                    // k-blocks issued so far, over all units
+            int s = 0;                                          // the stage of k-block `it`, and how often
+            uint32_t round = 0;                                 // the ring has been walked through (no division here)
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
                 Unit w = unit_of(u, tiles_a, splits);
                 int kb_begin = w.split * kblocks_per_split;
                 int kb_end = min(n_kblocks, kb_begin + kblocks_per_split);
-                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-                    int s = it % stages;
-                    uint32_t round = it / stages;
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), round += (s == 0)) {
                     uint32_t bar = smem_u32(&full_bar[s]);
                     if (it < early) {                           // armed above, the weight tile is in flight
                         if (swap) tma_load_2d(smem_u32(b_tiles + (size_t)s * B_BYTES), &map_b, bar, kb * BK, w.tile_b * BN);
@@ -466,7 +466,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // instruction descriptor: D 32-bit, A and B bfloat16, both K-major, N = BN, M = 128
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            uint32_t it = 0, n_done = 0;
+            // (this thread's instructions are the products' pace: the stage and its phase are counted, the
+            // descriptors of stage 0 are made once, and the k-block that overwrites the accumulator is
+            // peeled off: see gemm_tc_pair_kernel)
+            uint32_t n_done = 0;
+            int s = 0;
+            uint32_t phase = 0;
+            bool first = true;
+            const uint64_t a_desc0 = smem_desc(smem_u32(a_tiles)), b_desc0 = smem_desc(smem_u32(b_tiles));
+            const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
             bool ok = true;
             for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++n_done) {
                 Unit w = unit_of(u, tiles_a, splits);
@@ -478,22 +486,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!ok) break;
                 tcgen05_fence_after();
                 uint32_t d_tmem = tmem_base + buffer * BN;
-                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-                    int s = it % stages;
-                    uint32_t round = it / stages;
-                    ok = mbar_wait(smem_u32(&full_bar[s]), round & 1, abort_flag, status, 2);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    ok = mbar_wait(full0 + 8 * s, phase, abort_flag, status, 2);
                     if (!ok) break;
-                    if (it == 0) LLMB_STAMP(3, 32);             // the first operand tiles have landed
+                    if (first) { LLMB_STAMP(3, 32); first = false; }    // the first operand tiles have landed
                     tcgen05_fence_after();
-                    uint64_t a_desc = smem_desc(smem_u32(a_tiles + (size_t)s * A_BYTES));
-                    uint64_t b_desc = smem_desc(smem_u32(b_tiles + (size_t)s * B_BYTES));
+                    uint64_t a_desc = a_desc0 + (uint64_t)(s * (A_BYTES >> 4));
+                    uint64_t b_desc = b_desc0 + (uint64_t)(s * (B_BYTES >> 4));
+                    // 16 k-values = 32 bytes further inside the swizzled row: +2 in 16-byte units
+                    if (kb == kb_begin) {
+                        tcgen05_mma(d_tmem, a_desc, b_desc, idesc, 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // 16 k-values = 32 bytes further inside the swizzled row: +2 in 16-byte units
-                        tcgen05_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                    (kb > kb_begin || k > 0) ? 1u : 0u);
+                        for (int k = 1; k < BK / UMMA_K; ++k) tcgen05_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1u);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) tcgen05_mma(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1u);
                     }
-                    tcgen05_commit(smem_u32(&empty_bar[s]));
+                    tcgen05_commit(empty0 + 8 * s);
+                    if (++s == stages) { s = 0; phase ^= 1; }
                 }
                 if (ok) tcgen05_commit(smem_u32(&acc_full_bar[buffer]));
                 LLMB_STAMP(4, 32);                              // the unit's last product is issued
