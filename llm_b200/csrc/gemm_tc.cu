@@ -1253,7 +1253,11 @@ Plan make_plan(int M, int N, int K) {
     Plan p;
     p.n_kblocks = (K + BK - 1) / BK;
     long long pair_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
-    p.swap = M <= SWAP_TOKENS || (M <= SWAP_TOKENS_MOST && pair_tiles * 5 < PAIRS * 3);
+    // (a pair's tile of 64 k-blocks takes 26 us alone, whatever fills the other pairs: with a short K the
+    // pairs win from 24 tiles on, 256 x 6144 x 4096 in 25.9 against 30.5 us, 512 x 4096 x 4096 in 26.1 against 38.3;
+    // with a long K the split products stay ahead until the pairs are well filled)
+    bool few_tiles = p.n_kblocks <= 64 ? pair_tiles < 24 : pair_tiles * 5 < PAIRS * 3;
+    p.swap = M <= SWAP_TOKENS || (M <= SWAP_TOKENS_MOST && few_tiles);
     if (p.swap) {
         p.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
         p.tiles_a = (N + BM - 1) / BM;
