@@ -882,6 +882,28 @@ __device__ __forceinline__ void tcgen05_mma_pair(uint32_t d_tmem, uint64_t a_des
 
 constexpr int PAIR_BN = 256;        // columns of the pair's tile; each block loads half of them
 
+// The order in which the pairs take the tiles. The 74 tiles that run at the same time read their
+// operands' k-blocks at about the same time, so an operand tile that several of them share comes from
+// HBM once. With the token tile running fastest over all tiles (unit_of) a long prompt's 74 tiles
+// share ONE weight tile and read 74 different token tiles: at 65,536 tokens and K = 2,048 that is
+// 74 MB per 10 us, more than HBM delivers (products of a 263,000-token prefill ran at half their
+// rate). So the token tiles are taken in panels of 8: inside a panel the token tile runs fastest,
+// then the weight tile, then the next panel. A round of 74 tiles then reads 8 token tiles and about 9
+// weight tiles.
+constexpr int PANEL = 8;
+__device__ __forceinline__ Unit pair_unit_of(int u, int tiles_a, int tiles_b) {
+    Unit w;
+    w.split = 0;
+    int per_panel = PANEL * tiles_b;
+    int panel = u / per_panel;
+    int first = panel * PANEL;
+    int width = min(PANEL, tiles_a - first);          // the last panel may be narrower
+    int r = u - panel * per_panel;
+    w.tile_b = r / width;
+    w.tile_a = first + (r - w.tile_b * width);
+    return w;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_residual, Epilogue ep, int n_kblocks, int tiles_a,
@@ -939,7 +961,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     griddep_launch();
     uint32_t early = 0;
     if (warp == 0 && lane == 0 && pair < n_units) {
-        Unit w = unit_of(pair, tiles_a, 1);
+        Unit w = pair_unit_of(pair, tiles_a, n_units / tiles_a);
         early = (uint32_t)min(stages, n_kblocks);
         for (uint32_t i = 0; i < early; ++i) {
             if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[i]), 2 * (A_BYTES + B_BYTES));
@@ -957,7 +979,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t round = 0;                                 // how often the ring has been walked through
             bool ok = true;
             for (int u = pair; u < n_units && ok; u += n_pairs) {
-                Unit w = unit_of(u, tiles_a, 1);
+                Unit w = pair_unit_of(u, tiles_a, n_units / tiles_a);
                 for (int kb = 0; kb < n_kblocks; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), round += (s == 0)) {
                     if (it < early) {                           // armed above, the weight tile is in flight
                         tma_load_2d_pair(smem_u32(a_tiles + (size_t)s * A_BYTES), &map_a,
@@ -1025,7 +1047,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t n_done = 0;
         bool ok = true;
         for (int u = pair; u < n_units && ok; u += n_pairs, ++n_done) {
-            Unit w = unit_of(u, tiles_a, 1);
+            Unit w = pair_unit_of(u, tiles_a, n_units / tiles_a);
             uint32_t buffer = n_done & 1, use = n_done >> 1;
             const float* rstd = nullptr;
             if (ep.f.norm_sumsq) {                    // as in gemm_tc_kernel: while the products run
