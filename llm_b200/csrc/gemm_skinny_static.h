@@ -31,7 +31,14 @@
 // First call on a device. It looks the two arrays' device addresses up with
 // cudaGetSymbolAddress (with that device current) and clears the counters once; make
 // this first call before any stream capture begins on that device. Later calls only
-// launch the kernel.
+// launch the kernel. The clearing repeats what loading the library has done already
+// (`__device__` arrays start as zeros): it is there so that the counters' starting value
+// does not rest on that, and it is the only reason why the first call has to come before
+// a capture. The set-up is not guarded against two host threads making a device's first
+// call at the same moment: both would look up the same two addresses, store the same
+// values and clear the same counters, which is harmless as long as neither has a kernel
+// of this entry point in flight yet; callers that share a device between threads should
+// make the first call from one of them.
 //
 // Sharing. All calls on a device use the same arrays, and the arrays keep whatever the
 // last call left: the partial sums are overwritten before they are read, and the

@@ -134,6 +134,9 @@ def main(argv=None) -> int:
     p.add_argument("--rope", action="store_true",
                    help="linear: the q/k/v product with rotation and cache write (n = (heads + 2 kv heads) * head dim)")
     p.add_argument("--glu", action="store_true", help="linear: the gated epilogue (n = 2 x the feed-forward width)")
+    p.add_argument("--yardstick", action="store_true",
+                   help="linear: also time torch.matmul (cuBLAS) on the same operands in the same harness: a "
+                        "yardstick only, the library never calls it")
     p.add_argument("--temperature", type=float, default=0.0,
                    help="sample: 0 is greedy; above it the default chain (top-k 40, top-p 0.75, min-p 0.25, "
                         "repeat penalty 1.1 over the last 64) runs")
@@ -185,6 +188,13 @@ def main(argv=None) -> int:
         if args.timeline:
             return timeline(fn, f"linear {name} M={m} N={n} K={k}")
         run(fn, args, n * k * 2, 2.0 * m * n * k, f"linear {name} M={m} N={n} K={k}")
+        if args.yardstick and not args.once:
+            plain_out = torch.empty(m, n, device=DEV, dtype=bf16)
+
+            def library():
+                torch.matmul(x, ws[turn[0] % copies].t(), out=plain_out)
+                turn[0] += 1
+            run(library, args, n * k * 2, 2.0 * m * n * k, f"torch.matmul (cuBLAS) M={m} N={n} K={k}")
     elif args.op in ("attention_decode", "attention_prefill"):
         hq, hkv, d = args.heads, args.kv_heads, args.head_dim
         decode = args.op == "attention_decode"
