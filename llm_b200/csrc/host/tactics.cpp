@@ -94,8 +94,9 @@ const std::vector<Row>& table(int family) {
         {"gemm_tc", 30, tc_guard,
          "tcgen05.mma with the accumulator in tensor memory, operands by TMA; weights on the 128-row side and "
          "split K while the output has few tiles (always up to 128 tokens), pairs of SMs on 256 x 256 tiles "
-         "above. Measured on a B200 at Llama-3.1-8B layer sizes: about 1,200 TFLOP/s at 2,048 tokens, 3.1 to "
-         "5.9 TB/s of weights at 8 tokens, 16 us for 128 x 4096 x 4096"},
+         "above; a folded norm's scale, the next norm's input and the rotation with the cache write ride in its "
+         "epilogues. Measured on a B200 at Llama-3.1-8B layer sizes: 1,400 TFLOP/s at 2,048 tokens (73.6 us for "
+         "2048 x 6144 x 4096), 2.9 to 5.9 TB/s of weights at 8 tokens"},
         {"gemm_skinny", 20, skinny_guard,
          "decode product for up to 64 rows: W streamed once with 128-bit loads into mma.sync fragments, K split "
          "over warps with an ordered last-arriver sum; within a few percent of gemm_tc at 8 rows, behind it from 16"},
@@ -106,12 +107,12 @@ const std::vector<Row>& table(int family) {
         {"attention_decode", 20, decode_guard,
          "split-KV decode attention: pages through shared memory with cp.async (a ring sized by the head size), "
          "the query heads of a group as rows of mma.sync tiles, partials merged by a second kernel. Measured: "
-         "45 us for 8 sequences of 8,192 keys with 8 kv heads of 128 (5.9 TB/s), 27 us with heads of 64"},
+         "45.2 us for 8 sequences of 8,192 keys with 8 kv heads of 128 (5.94 TB/s)"},
         {"attention_prefill_tc", 15, prefill_tc_guard,
          "flash attention with both products on tcgen05 (accumulators in tensor memory, K and V pages by TMA), "
          "one thread per query row for the softmax, two blocks an SM; head sizes 64 and 128. Measured with 32/8 "
-         "heads of 128: 79 us at 2,048 tokens, 730 us at 8,192 (436 and 753 TFLOP/s of causal work); with heads "
-         "of 64: 71 and 668 us"},
+         "heads of 128: 53.0 us at 2,048 tokens, 573 us at 8,192 (648 and 959 TFLOP/s of causal work); with heads "
+         "of 64: 45.1 us at 2,048 tokens"},
         {"attention_prefill", 10, prefill_guard,
          "flash attention over the paged cache for steps with several new tokens a sequence: 64-query tiles, "
          "mma.sync, online softmax, heaviest tile first; head sizes 32, 64, 96, 128. Measured: 170 us at 2,048 "

@@ -20,6 +20,23 @@ def test_every_row_states_its_evidence_and_ranks_differ():
         assert min(r.rank for r in rows) == 0                      # a row without conditions ends each table
 
 
+def test_measured_figures_in_the_evidence_are_those_of_the_profiles():
+    """A row's evidence quotes measurements; each quoted figure must stand in the summary under
+    profiles/ that covers the kernel, so that a table that was not refreshed after a kernel change
+    shows up here."""
+    import re
+    from pathlib import Path
+    profiles = Path(__file__).resolve().parent.parent / "profiles"
+    evidence = {r.name: r.evidence for family in ("linear", "attention") for r in tactics.rows(family)}
+    checks = [("gemm_tc", "gemm_tc_pair__prefill_2048x6144x4096.txt", r"(\d+\.\d) us for 2048 x 6144 x 4096"),
+              ("attention_prefill_tc", "attention_prefill_tc__2048_tokens_32x8x128.txt", r"(\d+\.\d) us at 2,048 tokens"),
+              ("attention_decode", "attention_decode__batch8_context8192_32x8x128.txt", r"(\d+\.\d) us for 8 sequences")]
+    for name, file_name, pattern in checks:
+        found = re.search(pattern, evidence[name])
+        assert found, (name, evidence[name])
+        assert f"{found.group(1)} us" in (profiles / file_name).read_text(), (name, found.group(1), file_name)
+
+
 def test_switched_off_rows_are_never_chosen():
     args = dict(m=8, n=4096, k=4096, in_dtype=BF16, out_dtype=BF16, lda=4096)
     assert tactics.choose_linear(**args) == "gemm_tc"
