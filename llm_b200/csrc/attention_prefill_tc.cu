@@ -8,24 +8,36 @@
 // left operand of the second product, heaviest query tile first), for head sizes 64 and 128.
 //
 // One block serves 128 queries of one head of one sequence and walks the visible keys in
-// blocks of 128 (two cache pages):
+// blocks of 64 (one cache page):
 //
-// * warp 0, one lane: TMA. Q once; per key block the two pages of K and the two pages of V for
-//   the block's kv head, 64 x 64 boxes. K and V have one buffer each with barriers of their
-//   own: K is free again as soon as S is complete, V as soon as O is, so the next block's K
-//   arrives under this block's softmax and its V under the next S.
-// * warp 1, one lane: issues the products. S[128 q, 128 keys] = Q K^T (K=16 steps over the head
-//   dimension, both operands K-major in shared memory) into tensor-memory columns 0-127; then
-//   O[128 q, d] += P V with P read from tensor memory and V from shared memory as an MN-major
-//   operand (its rows are keys, the contiguous direction is d), accumulating in columns 128...
-// * warps 2-5: thread r owns query row r. It reads its row of S twice from tensor memory
-//   (first the maximum, then the exponentials: nothing of the row is kept in registers) and
-//   writes P over the scores it has read. O stays in tensor memory over all key blocks; when a
-//   row's maximum outgrows the exponent's reference by 2^8, its warp rescales O in place before P
-//   is released (rare after the first blocks).
-//   Rows need no exchange between threads.
-// * 96 KB of shared memory, 256 columns of tensor memory and under 170 registers a thread let two
-//   blocks share an SM: one's softmax runs under the other's products.
+// * warp 0, one lane: TMA for Q (once) and for the keys; warp 6, one lane: TMA for the values. 64 x 64
+//   boxes, two buffers each for K and V with barriers of their own, so that a buffer is requested
+//   again as soon as the product that read it is complete.
+// * warp 1, one lane: issues the products. S[128 q, 64 keys] = Q K^T (K=16 steps over the head
+//   dimension, both operands K-major in shared memory) into one of TWO score buffers in tensor memory
+//   (columns 0-63 and 64-127); then O[128 q, d] += P V with P read from tensor memory and V from shared
+//   memory as an MN-major operand (its rows are keys, the contiguous direction is d), accumulating in
+//   columns 128... The scores of key block kb + 2 are issued right behind P V of key block kb, into the
+//   buffer whose probabilities that product has just consumed: while the softmax works on one buffer,
+//   the products fill the other, so neither side waits for the other's whole turn.
+// * warps 2-5: thread r owns query row r. It reads its 64 scores from tensor memory once (both loads in
+//   flight), keeps them in registers for the maximum and the exponentials, and writes P over the
+//   buffer's first 32 columns. O stays in tensor memory over all key blocks; when a row's maximum
+//   outgrows the exponent's reference by 2^8, its warp rescales O in place, behind the exponentials
+//   and before P is released (rare after the first blocks). Rows need no exchange between threads.
+// * 96 KB of shared memory, 256 columns of tensor memory and 120 registers a thread let two
+//   blocks share an SM.
+//
+// How it got here, on a B200 at 2,048 / 8,192 tokens, 32 heads over 8 kv heads of 128: one score buffer
+// of 128 keys read twice by the softmax threads, 53.0 / 573 us; a build with phase counters
+// (-DLLMB_TRACE, microbench.py attention_prefill --timeline) showed each side idle for the other's
+// whole turn (softmax threads 2,000 of 4,500 cycles a key block waiting for S, the product thread
+// 3,000 waiting for P), and two blocks an SM did not fill the gaps. Two threads a row (8 softmax
+// warps), one read of all 128 scores into registers, and half of the exponentials as a polynomial on
+// the multiply-add units each measured slower (56.7, 60.2 and 55.9 us): the softmax is not short of
+// threads or of special-function throughput, every added instruction costs issue slots that the
+// product and TMA threads share. Two score buffers of 64 keys: 50.6 / 510 us; the values' TMA in a
+// warp of its own (one lane waiting for two kinds of buffers delayed the keys): 46.2 / 498 us.
 //
 // The key block's keys beyond a query's own position are masked by value (-inf), so the
 // diagonal needs no special path; blocks wholly above the tile's diagonal are never loaded.
@@ -40,13 +52,33 @@ LLMB_DEFINE_LAST_ERROR(llmb_attention_prefill_tc)
 namespace {
 
 constexpr int BQ = 128;                 // queries per block = lanes of tensor memory
-constexpr int BKV = 128;                // keys per step = two pages
-constexpr int THREADS = 192;
-constexpr int HALF_BYTES = 128 * 64 * 2;          // a [128 rows, 64 columns] piece: 16 KB
-constexpr int BOX_BYTES = 64 * 64 * 2;            // one page, one 64-column piece: 8 KB
-// tensor memory: S (128 columns of 32-bit scores) is overwritten in place by P (64 columns of
-// bfloat16 pairs, written behind the reading position); O (head_dim columns) accumulates beside it
-constexpr uint32_t S_COL = 0, P_COL = 0, O_COL = 128, TMEM_COLS = 256;
+constexpr int BKV = 64;                 // keys per step = one cache page
+constexpr int THREADS = 224;             // keys by TMA, products, four softmax warps, values by TMA
+constexpr int Q_PIECE = 128 * 64 * 2;             // 128 query rows, 64 columns of the head: 16 KB
+constexpr int KV_PIECE = 64 * 64 * 2;             // one page, 64 columns of the head: 8 KB
+// tensor memory: two buffers of scores (64 columns of 32-bit values each), each overwritten in place
+// by its probabilities (32 columns of bfloat16 pairs); O (head_dim columns) accumulates beside them
+constexpr uint32_t S_COL = 0, O_COL = 128, TMEM_COLS = 256;
+
+// A build with -DLLMB_TRACE adds up, per block, the SM clock cycles that one softmax thread and the
+// product thread spend in each phase of the loop over key blocks (llmb_attention_prefill_tc_trace).
+#ifdef LLMB_TRACE
+#define LAPS_BEGIN long long lap_t = clock64(); long long laps[6] = {0, 0, 0, 0, 0, 0};
+#define LAP(i) do { long long now_ = clock64(); laps[i] += now_ - lap_t; lap_t = now_; } while (0)
+#define LAPS_END(first_slot, count, n_blocks)                                                       \
+    do {                                                                                            \
+        unsigned block_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;            \
+        if (block_ < LLMB_TRACE_BLOCKS) {                                                           \
+            for (int i_ = 0; i_ < (count); ++i_)                                                    \
+                llmb_trace_buffer[block_ * LLMB_TRACE_SLOTS + (first_slot) + i_] = laps[i_];         \
+            llmb_trace_buffer[block_ * LLMB_TRACE_SLOTS + LLMB_TRACE_SLOTS - 1] = (n_blocks);       \
+        }                                                                                           \
+    } while (0)
+#else
+#define LAPS_BEGIN
+#define LAP(i) do { } while (0)
+#define LAPS_END(first_slot, count, n_blocks) do { } while (0)
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -68,10 +100,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
-
 // HD: head dimension, 64 or 128 (one or two 64-column pieces per tile). Two blocks fit on an SM
-// (96 KB of shared memory, 256 columns of tensor memory, at most 168 registers), so that one
-// block's softmax runs under the other's products.
+// (96 KB of shared memory, 256 columns of tensor memory, at most 168 registers).
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -81,23 +111,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             __nv_bfloat16* __restrict__ out, int out_stride,
                             int n_heads, int n_kv_heads, float scale_log2, int* status) {
     constexpr int PIECES = HD / 64;
-    constexpr int TILE_BYTES = PIECES * HALF_BYTES;   // Q, or the K or V of one key block
+    constexpr int Q_BYTES = PIECES * Q_PIECE;         // the block's queries
+    constexpr int KV_BYTES = PIECES * KV_PIECE;       // the K or the V of one key block
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile = base;
-    unsigned char* k_tile = base + TILE_BYTES;        // one buffer each: K is free again as soon as
-    unsigned char* v_tile = k_tile + TILE_BYTES;      // S is complete, V as soon as O is
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_tile + TILE_BYTES);
+    unsigned char* k_tile = base + Q_BYTES;           // two buffers each: the next key block's K arrives
+    unsigned char* v_tile = k_tile + 2 * KV_BYTES;    // under this block's products, its V under the softmax
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_tile + 2 * KV_BYTES);
     uint64_t* q_full = bars;
-    uint64_t* k_full = bars + 1;
-    uint64_t* k_empty = bars + 2;
-    uint64_t* v_full = bars + 3;
-    uint64_t* v_empty = bars + 4;
-    uint64_t* s_full = bars + 5;              // S is complete
-    uint64_t* p_full = bars + 6;              // P is written and O has been rescaled
-    uint64_t* o_full = bars + 7;              // the block's P V has been added to O
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* k_full = bars + 1;              // [2]
+    uint64_t* k_empty = bars + 3;             // [2]
+    uint64_t* v_full = bars + 5;              // [2]
+    uint64_t* v_empty = bars + 7;             // [2]
+    uint64_t* s_full = bars + 9;              // [2] a buffer's scores are complete
+    uint64_t* p_full = bars + 11;             // [2] its probabilities are written and O has been rescaled
+    uint64_t* o_full = bars + 13;             // a key block's P V has been added to O
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     griddep_launch();            // the next kernel may set itself up; this one needs the one before it whole
@@ -119,7 +150,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int* pages = block_table + (size_t)seq * table_stride;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&bars[i]), i == 6 ? 128 : 1);
+        for (int i = 0; i < 14; ++i) mbar_init(smem_u32(&bars[i]), (i == 11 || i == 12) ? 128 : 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -133,73 +164,88 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tcgen05_fence_after();
     uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    if (warp == 0 || warp == 6) {
+        // warp 0 brings Q and the keys, warp 6 the values: each waits only for its own buffers
         if (lane == 0) {
-            auto load_pages = [&](unsigned char* tile_smem, const CUtensorMap* map, uint32_t bar, int kb) {
-                mbar_expect_tx(bar, TILE_BYTES);
-                for (int p = 0; p < 2; ++p) {
-                    int page = pages[(kb * 2 + p) % ring_pages];
-                    int row = (page * n_kv_heads + kv_head) * LLMB_PAGE;
-                    for (int h = 0; h < PIECES; ++h)      // piece h holds 128 key rows: page 0, then page 1
-                        tma_load_2d(smem_u32(tile_smem + h * HALF_BYTES + p * BOX_BYTES), map, bar, h * 64, row);
-                }
-            };
-            uint32_t bar = smem_u32(q_full);
-            mbar_expect_tx(bar, TILE_BYTES);
-            for (int h = 0; h < PIECES; ++h)
-                tma_load_2d(smem_u32(q_tile + h * HALF_BYTES), &map_q, bar, head * HD + h * 64,
-                            first_token + tile * BQ);
+            bool keys = warp == 0;
+            if (keys) {
+                uint32_t bar = smem_u32(q_full);
+                mbar_expect_tx(bar, Q_BYTES);
+                for (int h = 0; h < PIECES; ++h)
+                    tma_load_2d(smem_u32(q_tile + h * Q_PIECE), &map_q, bar, head * HD + h * 64,
+                                first_token + tile * BQ);
+            }
+            const CUtensorMap* map = keys ? &map_k : &map_v;
+            unsigned char* tiles = keys ? k_tile : v_tile;
+            uint64_t* full = keys ? k_full : v_full;
+            uint64_t* empty = keys ? k_empty : v_empty;
             for (int kb = 0; kb < n_blocks; ++kb) {
-                if (kb > 0 && !mbar_wait(smem_u32(k_empty), (kb - 1) & 1, abort_flag, status, 11)) break;
-                load_pages(k_tile, &map_k, smem_u32(k_full), kb);
-                if (kb > 0 && !mbar_wait(smem_u32(v_empty), (kb - 1) & 1, abort_flag, status, 12)) break;
-                load_pages(v_tile, &map_v, smem_u32(v_full), kb);
+                int b = kb & 1;
+                if (kb >= 2 && !mbar_wait(smem_u32(&empty[b]), ((kb >> 1) - 1) & 1, abort_flag, status, keys ? 11 : 12))
+                    break;
+                uint32_t bar = smem_u32(&full[b]);
+                mbar_expect_tx(bar, KV_BYTES);
+                int page = pages[kb % ring_pages];
+                int row = (page * n_kv_heads + kv_head) * LLMB_PAGE;
+                for (int h = 0; h < PIECES; ++h)
+                    tma_load_2d(smem_u32(tiles + b * KV_BYTES + h * KV_PIECE), map, bar, h * 64, row);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // D 32-bit, A and B bfloat16, M = 128; S has N = 128 keys, O has N = HD with B MN-major
+            // D 32-bit, A and B bfloat16, M = 128; S has N = 64 keys, O has N = HD with B MN-major
             constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) |
                                           ((uint32_t)(BQ >> 4) << 24);
             constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                           ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
             // the descriptors of the tiles' first bytes are made once; a step inside a tile adds a constant
             // to the address field (this thread's instructions set the pace of the products)
-            const uint64_t q_desc = smem_desc(smem_u32(q_tile)), k_desc = smem_desc(smem_u32(k_tile));
-            const uint64_t v_desc = smem_desc_mn(smem_u32(v_tile), HALF_BYTES);
-            auto issue_qk = [&]() {
+            const uint64_t q_desc = smem_desc(smem_u32(q_tile));
+            const uint64_t k_desc0 = smem_desc(smem_u32(k_tile)), v_desc0 = smem_desc_mn(smem_u32(v_tile), KV_PIECE);
+            constexpr uint64_t BUFFER = (uint64_t)(KV_BYTES >> 4);       // the second buffer, in the address field
+            // S[buffer kb & 1] = Q K(kb)^T; the buffer's last probabilities have been consumed by a
+            // product that this thread issued earlier (products run in the order of their issue)
+            auto issue_qk = [&](int kb) -> bool {
+                int b = kb & 1;
+                if (!mbar_wait(smem_u32(&k_full[b]), (kb >> 1) & 1, abort_flag, status, 14)) return false;
+                tcgen05_fence_after();
 #pragma unroll
                 for (int j = 0; j < HD / 16; ++j) {
-                    uint64_t off = (uint64_t)(((j >> 2) * HALF_BYTES + (j & 3) * 32) >> 4);
-                    tcgen05_mma(tmem_base + S_COL, q_desc + off, k_desc + off, idesc_qk, j > 0 ? 1u : 0u);
+                    uint64_t q_off = (uint64_t)(((j >> 2) * Q_PIECE + (j & 3) * 32) >> 4);
+                    uint64_t k_off = (uint64_t)(((j >> 2) * KV_PIECE + (j & 3) * 32) >> 4);
+                    tcgen05_mma(tmem_base + S_COL + b * BKV, q_desc + q_off, k_desc0 + b * BUFFER + k_off, idesc_qk,
+                                j > 0 ? 1u : 0u);
                 }
-                tcgen05_commit(smem_u32(s_full));
-                tcgen05_commit(smem_u32(k_empty));
+                tcgen05_commit(smem_u32(&s_full[b]));
+                tcgen05_commit(smem_u32(&k_empty[b]));
+                return true;
             };
-            bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, status, 13) &&
-                      mbar_wait(smem_u32(k_full), 0, abort_flag, status, 14);
-            if (ok) {
-                tcgen05_fence_after();
-                issue_qk();
-            }
+            LAPS_BEGIN
+            bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, status, 13) && issue_qk(0);
+            if (ok && n_blocks > 1) ok = issue_qk(1);
+            LAP(4);
             for (int kb = 0; kb < n_blocks && ok; ++kb) {
-                ok = mbar_wait(smem_u32(p_full), kb & 1, abort_flag, status, 15) &&
-                     mbar_wait(smem_u32(v_full), kb & 1, abort_flag, status, 16);
+                int b = kb & 1, phase = (kb >> 1) & 1;
+                ok = mbar_wait(smem_u32(&p_full[b]), phase, abort_flag, status, 15);
+                LAP(0);
+                ok = ok && mbar_wait(smem_u32(&v_full[b]), phase, abort_flag, status, 16);
+                LAP(1);
                 if (!ok) break;
                 tcgen05_fence_after();
 #pragma unroll
                 for (int j = 0; j < BKV / 16; ++j)        // 16 keys a step: 8 columns of P, 2048 bytes of V rows
-                    tcgen05_mma_ts(tmem_base + O_COL, tmem_base + P_COL + j * 8,
-                                   v_desc + (uint64_t)((j * 2048) >> 4), idesc_pv, (kb > 0 || j > 0) ? 1u : 0u);
+                    tcgen05_mma_ts(tmem_base + O_COL, tmem_base + S_COL + b * BKV + j * 8,
+                                   v_desc0 + b * BUFFER + (uint64_t)((j * 2048) >> 4), idesc_pv,
+                                   (kb > 0 || j > 0) ? 1u : 0u);
                 tcgen05_commit(smem_u32(o_full));
-                tcgen05_commit(smem_u32(v_empty));
-                if (kb + 1 < n_blocks) {
-                    ok = mbar_wait(smem_u32(k_full), (kb + 1) & 1, abort_flag, status, 14);
-                    if (!ok) break;
-                    tcgen05_fence_after();
-                    issue_qk();
-                }
+                tcgen05_commit(smem_u32(&v_empty[b]));
+                LAP(2);
+                // the scores of the key block after the next go where these probabilities were: the
+                // softmax of the next key block runs meanwhile on the other buffer
+                if (kb + 2 < n_blocks) ok = issue_qk(kb + 2);
+                LAP(3);
             }
+            LAPS_END(6, 5, n_blocks);
         }
     } else {
         int quarter = warp & 3;
@@ -209,15 +255,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         float run_max = -INFINITY, run_sum = 0.f;
         bool ok = true;
+        LAPS_BEGIN
         for (int kb = 0; kb < n_blocks && ok; ++kb) {
-            ok = mbar_wait(smem_u32(s_full), kb & 1, abort_flag, status, 17);
+            int b = kb & 1;
+            ok = mbar_wait(smem_u32(&s_full[b]), (kb >> 1) & 1, abort_flag, status, 17);
+            LAP(0);
             if (!ok) break;
             __syncwarp();
             tcgen05_fence_after();
             int key0 = kb * BKV;
             bool whole = key0 + BKV - 1 <= pos;              // no key of the block is hidden from this row
-            // first reading of the row: its maximum over the visible keys. The next 32 columns are
-            // on their way from tensor memory while the last 32 are compared.
+            // The row's 64 scores are read from tensor memory once, both loads in flight, and stay in
+            // registers for the maximum and for the exponentials.
+            uint32_t s_addr = lane_addr + S_COL + b * BKV;
+            uint32_t ra[32], rb[32];
+            tmem_ld32_start(s_addr, ra);
+            tmem_ld32_start(s_addr + 32, rb);
             float block_max = -INFINITY;
             auto row_max = [&](const uint32_t (&r)[32], int c) {
                 if (whole) {
@@ -230,49 +283,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         if (key0 + c + j <= pos) block_max = fmaxf(block_max, __uint_as_float(r[j]));
                 }
             };
-            {
-                uint32_t ra[32], rb[32];
-                tmem_ld32_start(lane_addr + S_COL, ra);
-                tmem_ld32_wait(ra);
-                tmem_ld32_start(lane_addr + S_COL + 32, rb);
-                row_max(ra, 0);
-                tmem_ld32_wait(rb);
-                tmem_ld32_start(lane_addr + S_COL + 64, ra);
-                row_max(rb, 32);
-                tmem_ld32_wait(ra);
-                tmem_ld32_start(lane_addr + S_COL + 96, rb);
-                row_max(ra, 64);
-                tmem_ld32_wait(rb);
-                row_max(rb, 96);
-            }
+            tmem_ld32_wait(ra);
+            tmem_ld32_wait(rb);
+            row_max(ra, 0);
+            row_max(rb, 32);
+            LAP(1);
             // The exponent's reference moves only when the block's maximum exceeds it by more than
             // 2^8 (softmax does not depend on the reference; probabilities up to 256 are as exact in
             // bfloat16 as those up to 1). O, which holds the sum in units of 2^-reference, is then
             // rescaled in place. The tensor-memory accesses are warp-wide, so the warp rescales when
-            // any of its rows moves; the others multiply by one.
+            // any of its rows moves; the others multiply by one. A row that sees no key of this block
+            // (the upper rows of a tile in its last key block) has the maximum -inf and never moves.
             bool move = kb == 0 || (block_max - run_max) * scale_log2 > 8.f;
             float new_max = move ? block_max : run_max;      // finite for a real row: key 0 is visible
             float alpha = (move && kb > 0) ? fast_exp2((run_max - new_max) * scale_log2) : 1.f;
             float shift = new_max * scale_log2;
-            if (kb > 0) {
-                ok = mbar_wait(smem_u32(o_full), (kb - 1) & 1, abort_flag, status, 18);
-                if (!ok) break;
-                __syncwarp();
-                tcgen05_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-                    for (int c = 0; c < HD; c += 32) {
-                        uint32_t r[32];
-                        tmem_ld32(lane_addr + O_COL + c, r);
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-                        tmem_st32(lane_addr + O_COL + c, r);
-                    }
-                }
-            }
             run_max = new_max;
-            // second reading: probabilities, written back over the scores as bfloat16 pairs (a chunk's
-            // probabilities land on columns that have been read already), again one chunk ahead
+            // probabilities, written over the scores' first columns as bfloat16 pairs (every score of
+            // the buffer is in a register by now)
             float add = 0.f;
             auto to_probabilities = [&](const uint32_t (&r)[32], int c) {
                 uint32_t packed[16];
@@ -293,28 +321,39 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         packed[j >> 1] = pack2(p0, p1);
                     }
                 }
-                tmem_st16(lane_addr + P_COL + (c >> 1), packed);
+                tmem_st16(s_addr + (c >> 1), packed);
             };
-            {
-                uint32_t ra[32], rb[32];
-                tmem_ld32_start(lane_addr + S_COL, ra);
-                tmem_ld32_wait(ra);
-                tmem_ld32_start(lane_addr + S_COL + 32, rb);
-                to_probabilities(ra, 0);             // writes columns 0-15: read already
-                tmem_ld32_wait(rb);
-                tmem_ld32_start(lane_addr + S_COL + 64, ra);
-                to_probabilities(rb, 32);            // writes columns 16-31
-                tmem_ld32_wait(ra);
-                tmem_ld32_start(lane_addr + S_COL + 96, rb);
-                to_probabilities(ra, 64);            // writes columns 32-47
-                tmem_ld32_wait(rb);
-                to_probabilities(rb, 96);            // writes columns 48-63
-            }
+            to_probabilities(ra, 0);
+            to_probabilities(rb, 32);
             run_sum = run_sum * alpha + add;
+            LAP(4);
+            // O is rescaled behind the exponentials: the product before this one, which has to be
+            // complete first, has had their time to finish, and the next one waits for the release below
+            if (kb > 0) {
+                ok = mbar_wait(smem_u32(o_full), (kb - 1) & 1, abort_flag, status, 18);
+                if (!ok) break;
+                __syncwarp();
+                tcgen05_fence_after();
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(lane_addr + O_COL + c, r);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                        tmem_st32(lane_addr + O_COL + c, r);
+                    }
+                }
+            }
+            LAP(3);
             tmem_st_wait();
             tcgen05_fence_before();
-            mbar_arrive(smem_u32(p_full));
+            mbar_arrive(smem_u32(&p_full[b]));
+            LAP(5);
         }
+#ifdef LLMB_TRACE
+        if (threadIdx.x == 64) LAPS_END(0, 6, n_blocks);
+#endif
         if (ok) ok = mbar_wait(smem_u32(o_full), (n_blocks - 1) & 1, abort_flag, status, 19);
         if (ok) {
             __syncwarp();
@@ -354,6 +393,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 }  // namespace
 
+// The phase sums of the last launch's first blocks (a build with -DLLMB_TRACE): LLMB_TRACE_BLOCKS rows of
+// LLMB_TRACE_SLOTS values: SM clock cycles of a softmax thread in slots 0-5 (waiting for S, reading it
+// and its maximum, unused, waiting for O and rescaling, exponentials and P, releasing P), of the product
+// thread in slots 6-10 (waiting for P, for V, issuing P V, waiting for K and issuing Q K^T, the first two
+// Q K^T), and the block's number of key blocks in the last slot. Returns 1 in a build without.
+LLMB_EXPORT int llmb_attention_prefill_tc_trace(unsigned long long* out, int clear) { return llmb_read_trace(out, clear); }
+
 LLMB_EXPORT int llmb_attention_prefill_tc_status() {
     int* s = status_word();
     if (!s) return -1;
@@ -376,9 +422,9 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap
            const int* block_table, int table_stride, int ring_pages, const int* cu_seqlens,
            const int* seq_lens, const int* seq_order, void* out, int out_stride, int n_seqs, int max_new, int n_heads,
            int n_kv_heads, float scale, cudaStream_t stream) {
-    constexpr int TILE_BYTES = (HD / 64) * HALF_BYTES;
+    constexpr int Q_BYTES = (HD / 64) * Q_PIECE, KV_BYTES = (HD / 64) * KV_PIECE;
     // never less than 80 KB, so that no third block lands on an SM and waits for tensor memory
-    size_t smem = 1024 + (size_t)3 * TILE_BYTES + 16 * 8 + 16;
+    size_t smem = 1024 + (size_t)Q_BYTES + 4 * KV_BYTES + 16 * 8 + 16;
     if (smem < 80 * 1024) smem = 80 * 1024;
     static bool configured = false;
     if (!configured) {

@@ -110,9 +110,9 @@ const std::vector<Row>& table(int family) {
          "45.2 us for 8 sequences of 8,192 keys with 8 kv heads of 128 (5.94 TB/s)"},
         {"attention_prefill_tc", 15, prefill_tc_guard,
          "flash attention with both products on tcgen05 (accumulators in tensor memory, K and V pages by TMA), "
-         "one thread per query row for the softmax, two blocks an SM; head sizes 64 and 128. Measured with 32/8 "
-         "heads of 128: 53.0 us at 2,048 tokens, 573 us at 8,192 (648 and 959 TFLOP/s of causal work); with heads "
-         "of 64: 45.1 us at 2,048 tokens"},
+         "two score buffers of 64 keys so that Q K^T runs under the softmax, one thread per query row, two "
+         "blocks an SM; head sizes 64 and 128. Measured with 32/8 heads of 128: 46.3 us at 2,048 tokens, 497.7 us "
+         "at 8,192 (742 and 1,105 TFLOP/s of causal work); with heads of 64: 40.5 us at 2,048 tokens"},
         {"attention_prefill", 10, prefill_guard,
          "flash attention over the paged cache for steps with several new tokens a sequence: 64-query tiles, "
          "mma.sync, online softmax, heaviest tile first; head sizes 32, 64, 96, 128. Measured: 170 us at 2,048 "

@@ -114,6 +114,37 @@ def timeline(fn, label: str, library: str = "gemm_tc") -> int:
     return 0
 
 
+def phase_sums(fn, label: str) -> int:
+    """attention_prefill, a build with -DLLMB_TRACE: mean SM clock cycles per key block that a softmax
+    thread and the product thread of a block spend in each phase (over the launch's first 296 blocks)."""
+    import ctypes
+    from llm_b200.ops.build import load_library
+    lib = load_library("attention_prefill_tc")
+    rows, slots = 296, 12
+    sums = (ctypes.c_ulonglong * (rows * slots))()
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    if lib.llmb_attention_prefill_tc_trace(sums, 1) != 0:
+        print("this build has no phase sums: set LLMB_NVCC_FLAGS=-DLLMB_TRACE", file=sys.stderr)
+        return 1
+    fn()
+    torch.cuda.synchronize()
+    lib.llmb_attention_prefill_tc_trace(sums, 0)
+    table = torch.tensor(list(sums), dtype=torch.float64).view(rows, slots)
+    table = table[table[:, slots - 1] > 0]
+    key_blocks = table[:, slots - 1].sum()
+    names = ["softmax thread: waiting for S", "  reading S, the row's maximum", None,
+             "  waiting for O, rescaling", "  exponentials, writing P", "  releasing P",
+             "product thread: waiting for P", "  waiting for V", "  issuing P V", "  waiting for K, issuing Q K^T",
+             "  the first two Q K^T"]
+    print(f"{label}: {table.shape[0]} blocks, {int(key_blocks)} key blocks; mean SM cycles per key block")
+    for slot, name in enumerate(names):
+        if name:
+            print(f"  {name:36s}{float(table[:, slot].sum() / key_blocks):9.0f}")
+    return 0
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     p.add_argument("op", choices=["linear", "attention_decode", "attention_prefill", "rmsnorm",
@@ -142,7 +173,9 @@ def main(argv=None) -> int:
                         "repeat penalty 1.1 over the last 64) runs")
     p.add_argument("--reps", type=int, default=20)
     p.add_argument("--once", action="store_true")
-    p.add_argument("--timeline", action="store_true", help="linear, attention_decode: phases of the last launch's blocks")
+    p.add_argument("--timeline", action="store_true",
+                   help="linear, attention_decode: phases of the last launch's blocks; attention_prefill: cycles "
+                        "per key block and phase (builds with -DLLMB_TRACE)")
     args = p.parse_args(argv)
     torch.manual_seed(0)
     bf16 = torch.bfloat16
@@ -225,6 +258,8 @@ def main(argv=None) -> int:
             fn = lambda: attention(qkv, kc, vc, table, pages_per, pos, seq, hq, hkv, d, d ** -0.5, 0,
                                    seq_lens=lens, max_len=ctx, cu_seqlens=cu, max_new=ctx)
             args.reps = min(args.reps, 5)
+            if args.timeline:
+                return phase_sums(fn, f"attention_prefill tokens={ctx} heads={hq}/{hkv} D={d}")
             run(fn, args, 0.0, 2.0 * 2.0 * ctx * ctx / 2 * d * hq,
                 f"attention_prefill tokens={ctx} heads={hq}/{hkv} D={d} (causal flops)")
     elif args.op == "sample":
