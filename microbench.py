@@ -204,12 +204,23 @@ def main(argv=None) -> int:
         if args.rope:
             hq, hkv, d = args.heads, args.kv_heads, args.head_dim
             assert n == (hq + 2 * hkv) * d, "--n must be (heads + 2 kv heads) * head dim"
-            pages = (args.context + 63) // 64
-            kc = torch.zeros(m * pages, hkv, 64, d, device=DEV, dtype=bf16)
-            vc = torch.zeros_like(kc)
-            rope = ops.RopeWrite(torch.rand(args.context, d, device=DEV), torch.full((m,), args.context - 1, dtype=torch.int32, device=DEV),
-                                 torch.arange(m, dtype=torch.int32, device=DEV),
-                                 torch.arange(m * pages, dtype=torch.int32, device=DEV).view(m, pages), pages, kc, vc, hq, hkv, d)
+            if m <= 64:                      # a decode step: m sequences, each at its context's last position
+                pages = (args.context + 63) // 64
+                kc = torch.zeros(m * pages, hkv, 64, d, device=DEV, dtype=bf16)
+                vc = torch.zeros_like(kc)
+                rope = ops.RopeWrite(torch.rand(args.context, d, device=DEV),
+                                     torch.full((m,), args.context - 1, dtype=torch.int32, device=DEV),
+                                     torch.arange(m, dtype=torch.int32, device=DEV),
+                                     torch.arange(m * pages, dtype=torch.int32, device=DEV).view(m, pages), pages,
+                                     kc, vc, hq, hkv, d)
+            else:                            # a prefill: one sequence of m tokens
+                pages = (m + 63) // 64
+                kc = torch.zeros(pages, hkv, 64, d, device=DEV, dtype=bf16)
+                vc = torch.zeros_like(kc)
+                rope = ops.RopeWrite(torch.rand(m, d, device=DEV), torch.arange(m, dtype=torch.int32, device=DEV),
+                                     torch.zeros(m, dtype=torch.int32, device=DEV),
+                                     torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages), pages,
+                                     kc, vc, hq, hkv, d)
         if args.glu:
             out = torch.empty(m, n // 2, device=DEV, dtype=bf16)
 

@@ -642,7 +642,7 @@ def test_linear_leaves_the_next_norms_input(m, n, k):
     assert ops().tensor_core_status() == 0
 
 
-@pytest.mark.parametrize("tokens", [1, 8, 16, 40, 128, 300])
+@pytest.mark.parametrize("tokens", [1, 8, 16, 40, 128, 300, 1100])
 @pytest.mark.parametrize("heads,kv_heads,dim,interleaved,bias", [(8, 2, 128, False, False), (4, 4, 64, False, True),
                                                                  (6, 2, 32, True, True), (3, 1, 128, True, False),
                                                                  (6, 2, 48, False, False)])
@@ -650,7 +650,8 @@ def test_qkv_product_rotates_and_writes_the_cache(tokens, heads, kv_heads, dim, 
     """The q/k/v product with the rotation and the cache write in its epilogue (and a folded norm
     with it) against the product followed by the plain rope_cache_write: sequences at different
     positions and pages, head sizes that fit a tile and one that does not (48: a kernel of its own
-    runs behind the product)."""
+    runs behind the product). 1,100 tokens run 256 x 256 tiles on pairs of SMs, which leave the
+    rotation to the kernel behind them."""
     k = 256
     width = (heads + 2 * kv_heads) * dim
     counts = [tokens] if tokens < 3 else [tokens - 2, 1, 1]
