@@ -79,11 +79,46 @@ __device__ __forceinline__ float warp_row_rstd(const llmb_gemm_fusion& f, int to
     return 1.0f / sqrtf(v / f.norm_width + f.norm_eps);
 }
 
-// The scales of a tile's token rows into shared memory, by the four epilogue warps (quarter = 0..3, each
-// takes every fourth row), before the tile's accumulator is awaited. The caller synchronises the epilogue
-// warps afterwards.
+// The same value, bit for bit, computed by ONE thread: v[i] = part i + part i + 32 as lane i has it, then
+// the butterfly's levels as a tree (lane i's sum after the level of offset w is v[i] + v[i + w] for
+// i < w; additions commute). A thread has all of its row's loads in flight at once, so the rows of a
+// wide tile take one trip to L2 together instead of one trip each.
+__device__ __forceinline__ float thread_row_rstd(const llmb_gemm_fusion& f, int token) {
+    const float4* p = reinterpret_cast<const float4*>(f.norm_sumsq + (size_t)token * LLMB_SUMSQ_LD);
+    int parts = f.norm_parts;
+    float v[32];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        float4 lo = 4 * g < parts ? __ldcg(p + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 hi = 32 + 4 * g < parts ? __ldcg(p + 8 + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float l[4] = {lo.x, lo.y, lo.z, lo.w}, h[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int i = 4 * g + j;
+            v[i] = (i < parts ? l[j] : 0.f) + (i + 32 < parts ? h[j] : 0.f);
+        }
+    }
+#pragma unroll
+    for (int w = 16; w > 0; w >>= 1) {
+#pragma unroll
+        for (int i = 0; i < w; ++i) v[i] += v[i + w];
+    }
+    return 1.0f / sqrtf(v[0] / f.norm_width + f.norm_eps);
+}
+static_assert(LLMB_SUMSQ_LD == 64, "thread_row_rstd and warp_row_rstd read a row of 64 partial sums");
+
+// The scales of a tile's token rows into shared memory, by the four epilogue warps, before the tile's
+// accumulator is awaited: up to 16 rows a warp a row (quarter = 0..3 takes every fourth), more rows a
+// thread a row. The caller synchronises the epilogue warps afterwards.
 __device__ __forceinline__ void tile_rstd(const Epilogue& ep, float* rstd, int quarter, int first_token, int n_tile_tokens) {
     int lane = threadIdx.x & 31;
+    if (n_tile_tokens > 16) {
+        for (int i = quarter * 32 + lane; i < n_tile_tokens; i += 128) {
+            int token = first_token + i;
+            rstd[i] = token < ep.tokens ? thread_row_rstd(ep.f, token) : 1.f;
+        }
+        return;
+    }
 #pragma unroll 4
     for (int i = quarter; i < n_tile_tokens; i += 4) {
         int token = first_token + i;
