@@ -391,6 +391,7 @@ def main() -> int:
         llm.generate(prompts, max_tokens=4, temperature=0.0, stop_tokens=[])      # warm-up
         stamps = []
         mark = clocks.mark()
+        replays_before = llm.engine.graph_replays
         results = llm.generate(prompts, max_tokens=e2e_new, temperature=0.0, stop_tokens=[], details=True,
                                on_token=lambda index, token: stamps.append(time.perf_counter()) if index == 0 else None)
         e2e_clock = clocks.summary(mark, clocks.mark())
@@ -398,12 +399,16 @@ def main() -> int:
         generated = sum(r.generated_tokens - 1 for r in results)
         steady_s = stamps[-1] - stamps[64]
         steady_steps = len(stamps) - 1 - 64
+        gaps = sorted((b - a) * 1e3 for a, b in zip(stamps[64:], stamps[65:]))
         table_ints = sum(llm.engine.cache.table_width(g) for g in range(len(llm.engine.cache.groups)))
         e2e = {"value": round(generated / decode_s, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": 4 * args.batch * (7 + table_ints),
                "d2h_bytes_per_step": 4 * args.batch, "prompt_tokens": prompt_len, "new_tokens": e2e_new,
                "steady_value": round(args.batch * steady_steps / steady_s, 1),
                "steady_ms_per_step": round(steady_s / steady_steps * 1e3, 4), "steady_after_steps": 64,
+               "steady_step_ms_p10": round(gaps[len(gaps) // 10], 3), "steady_step_ms_p50": round(gaps[len(gaps) // 2], 3),
+               "steady_step_ms_p90": round(gaps[len(gaps) * 9 // 10], 3),
+               "graph_replays": llm.engine.graph_replays - replays_before,
                "sm_mhz": e2e_clock["sm_mhz"],
                "ms_x_ghz": round(steady_s / steady_steps * 1e3 * (e2e_clock["sm_mhz"] or 0) / 1e3, 3)}
     clocks.stop()

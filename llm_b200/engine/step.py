@@ -122,6 +122,7 @@ class Engine:
                            and not ops.PROFILING
                            and getattr(model, "graph_safe", lambda: False)())
         self._graphs, self._graph_seen, self._graph_pool = {}, {}, None
+        self.graph_replays = 0            # decode steps run from a captured graph so far
         # passes that are not replayed from a graph (prompts, mixed steps, the first steps of a
         # decode shape) are recorded per shape and then walked by the native host library
         self.use_records = (self.device.type == "cuda" and not ops.PROFILING
@@ -338,7 +339,7 @@ class Engine:
         by the kernels from one device buffer that is refreshed before the
         replay."""
         pages = max(1, (max_len + PAGE - 1) // PAGE)
-        key = (n_seqs, pages.bit_length())
+        key = (n_seqs, (pages - 1).bit_length())        # buckets (2^(k-1), 2^k] pages: a context of 2^k pages ends in its bucket
         graph = self._graphs.get(key)
         if graph is None:
             seen = self._graph_seen.get(key, 0) + 1
@@ -368,5 +369,6 @@ class Engine:
         if device_tokens is not None:
             meta[:n_seqs].copy_(device_tokens)           # the tokens are the buffer's first section
         cuda_graph.replay()
+        self.graph_replays += 1
         ops.count_launches(kernels)
         return out.clone()

@@ -645,7 +645,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     if os.environ.get("LLMB_DECODE_SPLITS"):             # for measurements: force a slice count
         return int(os.environ["LLMB_DECODE_SPLITS"])
     pages = max(1, (max_len + PAGE - 1) // PAGE)
-    floor_pages = 1 << (pages.bit_length() - 1)
+    floor_pages = max(1, 1 << max(0, (pages - 1).bit_length() - 1))      # the bucket is (floor, 2 floor] pages
     pairs = max(1, n_seqs * n_kv_heads)
     want = 296 // pairs if pairs < 296 else min(4, max(1, floor_pages // 16))
     splits = 1
