@@ -324,6 +324,28 @@ def test_captured_steps_are_dropped_and_captured_again(folders, plain, monkeypat
     engine.cache.check()
 
 
+def test_a_context_of_a_power_of_two_ends_in_the_bucket_it_decodes_in(folders, plain):
+    """Captured decode steps are keyed by the batch size and a bucket of pages (2^(k-1), 2^k]: a
+    sequence that decodes from position 130 (three pages) to 256 (four pages, a whole power of two)
+    is captured once, every later step is a replay, and the logits are right on both sides of the
+    page edge."""
+    from llm_b200.engine import Entry, step
+    config, weights = plain["C"]
+    engine = engine_for(folders["C"], torch.bfloat16, max_slots=1)
+    tokens = random_tokens(256, config["vocab_size"], 77)
+    expected = plain_llama.forward(config, weights, tokens)
+    slot, = engine.acquire(1)
+    engine.step([Entry(slot, tokens[:130], [])])
+    for k in range(130, 256):
+        logits = engine.step([Entry(slot, [tokens[k]], [0])])
+        if k in (130, 191, 192, 193, 255):
+            assert close(logits[0], expected[k], torch.bfloat16), k
+    assert len(engine._graphs) == 1
+    assert engine.graph_replays == 126 - step.GRAPH_AFTER_STEPS
+    engine.release([slot])
+    engine.cache.check()
+
+
 def test_the_device_generator_equals_its_plain_statement_bit_for_bit():
     import numpy as np
     import plain_random
