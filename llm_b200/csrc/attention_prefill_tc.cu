@@ -38,6 +38,11 @@
 // threads or of special-function throughput, every added instruction costs issue slots that the
 // product and TMA threads share. Two score buffers of 64 keys: 50.6 / 510 us; the values' TMA in a
 // warp of its own (one lane waiting for two kinds of buffers delayed the keys): 46.2 / 498 us.
+// One block an SM with two score buffers of 128 keys (all 512 columns of tensor memory) and two threads a
+// row: 57.7 / 582 us. The two warps of a row sit on the same SM partition and reach their exponentials
+// together (1,276 cycles for 64 of them a thread, the special-function unit's rate), and nothing runs
+// under the reading of S and the meeting of the halves; two blocks an SM drift apart and fill each
+// other's gaps.
 //
 // The key block's keys beyond a query's own position are masked by value (-inf), so the
 // diagonal needs no special path; blocks wholly above the tile's diagonal are never loaded.
