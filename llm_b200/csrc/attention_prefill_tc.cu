@@ -42,7 +42,10 @@
 // row: 57.7 / 582 us. The two warps of a row sit on the same SM partition and reach their exponentials
 // together (1,276 cycles for 64 of them a thread, the special-function unit's rate), and nothing runs
 // under the reading of S and the meeting of the halves; two blocks an SM drift apart and fill each
-// other's gaps.
+// other's gaps. The same block with the two warps of a quarter taking the key blocks in turns (128
+// scores a thread, the reference told through shared memory): 62.5 / 604 us, since each warp then has
+// one of the two score buffers and waits through both products of its key block again. Two threads a
+// row on the present layout (32 scores each): 48.9 / 513 us.
 //
 // The key block's keys beyond a query's own position are masked by value (-inf), so the
 // diagonal needs no special path; blocks wholly above the tile's diagonal are never loaded.
