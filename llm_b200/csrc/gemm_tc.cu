@@ -284,7 +284,8 @@ __device__ __forceinline__ void finish_emit(const Epilogue& ep, int a_row, int t
         sq[j] = here ? updated * updated : 0.f;
     }
 #pragma unroll
-    for (int j = 0; j < 16; ++j) sq[j] = warp_sum(sq[j]);
+    for (int j = 0; j < 16; ++j)
+        if (j < valid) sq[j] = warp_sum(sq[j]);          // (valid is the same for the whole block)
     if (lane == 0) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) exch[quarter * 16 + j] = sq[j];
@@ -622,12 +623,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // split K: park the partial tile [BN columns][128 rows], free the accumulator, and
             // let the block that arrives last add all partials in split order
             float* mine = partials + (tile_id * splits + w.split) * (size_t)(BN * BM);
+            int cols = swap ? min(BN, ep.tokens - w.tile_b * BN) : BN;      // columns that hold tokens: the rest is padding that nobody reads
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c, r);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) __stcg(mine + (size_t)(c + j) * BM + row, __uint_as_float(r[j]));
+                for (int j = 0; j < 16; ++j)
+                    if (c + j < cols) __stcg(mine + (size_t)(c + j) * BM + row, __uint_as_float(r[j]));
             }
             tcgen05_fence_before();
             __syncwarp();
