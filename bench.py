@@ -365,7 +365,9 @@ def main() -> int:
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            r = time_decode(b, args.context, max(16, args.steps // 2), 5)
+            # (the prefill before these ran at the power cap; the clock comes back over some tenths of a
+            # second, so the warm-up here is a quarter of a second of steps)
+            r = time_decode(b, args.context, max(16, args.steps // 2), 80 if b == 1 else 20)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / peak["hbm_gbs"], 3)
         # the baseline's own decode workload: prompts of 512 tokens, 256 new tokens (contexts 512 to 768)
