@@ -6,6 +6,7 @@
     python microbench.py rmsnorm --m 8 --k 4096
     python microbench.py sample --batch 8 --n 128256 [--temperature 0.7]
     LLMB_NVCC_FLAGS=-DLLMB_TRACE python microbench.py linear --m 8 --n 6144 --k 4096 --timeline
+    LLMB_NVCC_FLAGS=-DLLMB_TRACE python microbench.py attention_prefill --tokens 2048 --timeline
 
 Each call is timed inside a CUDA graph of `--reps` back-to-back launches (so that
 the host's launch cost is not in the number), with CUDA events, after warm-up.
@@ -15,7 +16,9 @@ Default sizes are those of a Llama-3.1-8B layer. The per-kernel table that
 MythEclipse/llm prints with LLM_PROFILE=1 (apps/engine/src/cuda/mod.rs:1917-1972)
 is the precedent; this tool isolates one kernel instead of wrapping every launch.
 `--timeline` (tcgen05 product and decode attention, a build with -DLLMB_TRACE) prints when
-the blocks of the last launch passed the phases the kernel stamps with the GPU's global timer.
+the blocks of the last launch passed the phases the kernel stamps with the GPU's global timer;
+for attention_prefill it prints the SM clock cycles that a softmax thread and the product thread
+spend in each phase of a key block (the phases are too short for the global timer's steps).
 """
 from __future__ import annotations
 
