@@ -966,6 +966,92 @@ splitk_sum_rope_kernel(const float* __restrict__ partials, Epilogue ep, int tile
     }
 }
 
+// The same with four neighbouring rotation pairs (or four values of a v head) a thread and four tokens a
+// block, as splitk_sum4_kernel (head sizes that are multiples of 8, rows that allow 8-byte stores).
+__global__ void __launch_bounds__(256)
+splitk_sum_rope4_kernel(const float* __restrict__ partials, Epilogue ep, int tiles_a, int splits, int bn) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float scale_s[4];
+    const llmb_gemm_fusion& f = ep.f;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int slot = threadIdx.x >> 6;
+    int token = blockIdx.y * 4 + slot;
+    int dim = f.head_dim, half = dim >> 1;
+    int n_pair_quads = (f.n_heads + f.n_kv_heads) * half / 4;
+    int n_quads = n_pair_quads + f.n_kv_heads * dim / 4;
+    int quad = blockIdx.x * 64 + (threadIdx.x & 63);
+    if (f.norm_sumsq) {
+        if (warp < 4) {
+            int t = blockIdx.y * 4 + warp;
+            float r = t < ep.tokens ? warp_row_rstd(f, t) : 1.f;
+            if (lane == 0) scale_s[warp] = r;
+        }
+        __syncthreads();
+    }
+    float scale = f.norm_sumsq ? scale_s[slot] : 1.f;
+    if (token >= ep.tokens || quad >= n_quads) return;
+    int pos = f.tok_pos[token];
+    size_t cache_row = 0;
+    if (f.write_cache) {
+        int page = f.block_table[(size_t)f.tok_seq[token] * f.table_stride + ((pos / LLMB_PAGE) % f.ring_pages)];
+        cache_row = ((size_t)page * f.n_kv_heads) * LLMB_PAGE + (pos % LLMB_PAGE);      // + kv_head * 64, times dim
+    }
+    auto biased = [&](float4 v, int row) {
+        float4 b = ep.bias ? *reinterpret_cast<const float4*>(ep.bias + row) : make_float4(0.f, 0.f, 0.f, 0.f);
+        return make_float4(v.x * scale + b.x, v.y * scale + b.y, v.z * scale + b.z, v.w * scale + b.w);
+    };
+    __nv_bfloat16* q_out = reinterpret_cast<__nv_bfloat16*>(ep.out) + (size_t)token * ep.ldo;
+    if (quad < n_pair_quads) {
+        int item = quad * 4;                                         // the first of four pairs of one head
+        int head = item / half, pair = item - head * half;
+        // rows of the four pairs: (pair .. pair + 3) and the same half a head on, or 2 pair .. 2 pair + 7
+        int row0 = head * dim + (f.interleaved ? 2 * pair : pair);
+        int row1 = f.interleaved ? row0 + 4 : row0 + half;
+        float4 a = biased(split_sum4(partials, tiles_a, splits, bn, token, row0), row0);
+        float4 b = biased(split_sum4(partials, tiles_a, splits, bn, token, row1), row1);
+        float lo[4], hi[4];
+        if (f.interleaved) {
+            lo[0] = a.x; hi[0] = a.y; lo[1] = a.z; hi[1] = a.w;
+            lo[2] = b.x; hi[2] = b.y; lo[3] = b.z; hi[3] = b.w;
+        } else {
+            lo[0] = a.x; lo[1] = a.y; lo[2] = a.z; lo[3] = a.w;
+            hi[0] = b.x; hi[1] = b.y; hi[2] = b.z; hi[3] = b.w;
+        }
+        if (f.rope_table) {
+            float4 c4 = *reinterpret_cast<const float4*>(f.rope_table + (size_t)pos * dim + pair);
+            float4 s4 = *reinterpret_cast<const float4*>(f.rope_table + (size_t)pos * dim + half + pair);
+            const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float x = lo[i] * c[i] - hi[i] * sn[i], y = lo[i] * sn[i] + hi[i] * c[i];
+                lo[i] = x;
+                hi[i] = y;
+            }
+        }
+        __nv_bfloat16* dst = nullptr;
+        if (head < f.n_heads) dst = q_out + (size_t)head * dim;
+        else if (f.write_cache)
+            dst = reinterpret_cast<__nv_bfloat16*>(f.k_cache) + (cache_row + (size_t)(head - f.n_heads) * LLMB_PAGE) * dim;
+        if (dst) {
+            if (f.interleaved) {
+                *reinterpret_cast<uint2*>(dst + 2 * pair) = pack4(lo[0], hi[0], lo[1], hi[1]);
+                *reinterpret_cast<uint2*>(dst + 2 * pair + 4) = pack4(lo[2], hi[2], lo[3], hi[3]);
+            } else {
+                *reinterpret_cast<uint2*>(dst + pair) = pack4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint2*>(dst + half + pair) = pack4(hi[0], hi[1], hi[2], hi[3]);
+            }
+        }
+    } else if (f.write_cache) {
+        int rest = (quad - n_pair_quads) * 4;
+        int kv_head = rest / dim, e = rest - kv_head * dim;
+        int row = (f.n_heads + f.n_kv_heads + kv_head) * dim + e;
+        float4 v = biased(split_sum4(partials, tiles_a, splits, bn, token, row), row);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(f.v_cache) + (cache_row + (size_t)kv_head * LLMB_PAGE) * dim + e) =
+            pack4(v.x, v.y, v.z, v.w);
+    }
+}
+
 // ------------------------------------------------------------------------- two SMs on one tile
 // For large token counts the 128 x 256 tile above is held back by shared-memory fill: per
 // k-block it loads 48 KB for 524 tensor-core cycles. Two blocks of a cluster (a CTA pair on
@@ -1348,14 +1434,20 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Epilogue& e
                  splits, tiles_a, n_units, partials, counters, status_dev, stages, sum_later);
     int code = check_launch("gemm_tc");
     if (code || !sum_later) return code;
+    auto aligned = [](const void* p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0; };
     if (ep.f.rope) {
         int n_items = (ep.f.n_heads + ep.f.n_kv_heads) * (ep.f.head_dim / 2) + ep.f.n_kv_heads * ep.f.head_dim;
+        if (ep.f.head_dim % 8 == 0 && ep.ldo % 4 == 0 && aligned(ep.out, 8) && aligned(ep.bias, 16) &&
+            aligned(ep.f.k_cache, 8) && aligned(ep.f.v_cache, 8) && aligned(ep.f.rope_table, 16)) {
+            llmb::launch(splitk_sum_rope4_kernel, dim3((n_items / 4 + 63) / 64, (ep.tokens + 3) / 4), 256, 0, stream, true,
+                         (const float*)partials, ep, tiles_a, splits, BN);
+            return check_launch("gemm_tc (split-K sum with rotation, four pairs a thread)");
+        }
         llmb::launch(splitk_sum_rope_kernel, dim3((n_items + 255) / 256, ep.tokens), 256, 0, stream, true,
                      (const float*)partials, ep, tiles_a, splits, BN);
         return check_launch("gemm_tc (split-K sum with rotation)");
     }
     int n_features = ep.glu ? ep.outs / 2 : ep.outs;
-    auto aligned = [](const void* p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) == 0; };
     bool by_fours = n_features % 4 == 0 && ep.ldo % 4 == 0 && aligned(ep.out, ep.out_is_bf16 ? 8 : 16) &&
                     aligned(ep.residual, 16) && aligned(ep.bias, 16) && aligned(ep.f.emit_rows, 8);
     if (by_fours) {
